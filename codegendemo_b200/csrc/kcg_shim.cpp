@@ -1,0 +1,749 @@
+// Host side of libkcg_b200.so: the C ABI declared in include/kcg_b200.h.
+//
+//   compile : tuning config -> kernel name -> `nvcc -cubin` of kernels/gemm_entry.cu
+//             with the config as macros -> cubin in the cache directory
+//   load    : cubin -> CUmodule / CUfunction through the CUDA driver API
+//   launch  : tensor maps (cuTensorMapEncodeTiled) + one `__grid_constant__`
+//             parameter block -> cuLaunchKernelEx on the caller's stream
+//
+// libcuda.so.1 is resolved with dlopen on first use, so this library loads on a
+// machine without a GPU (the compile entry needs none). Nothing here computes a
+// GEMM on the host: without a driver, load/launch fail with KCG_E_NO_DRIVER.
+#include <cuda.h>
+#include <dlfcn.h>
+#include <fcntl.h>
+#include <spawn.h>
+#include <sys/stat.h>
+#include <sys/wait.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/kcg_b200.h"
+#include "kernels/gemm_params.h"
+
+extern char** environ;
+
+namespace {
+
+// --------------------------------------------------------------------- errors
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[4096];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = "KCG Error[CUDA]: Code: " + std::to_string(code) + ", Messsage: " + buf;
+  return code;
+}
+
+// --------------------------------------------------------- driver API binding
+#define KCG_STR2(x) #x
+#define KCG_STR(x) KCG_STR2(x)
+#define KCG_DRV_FUNCS(X)                                                                       \
+  X(cuInit) X(cuDeviceGet) X(cuDeviceGetCount) X(cuDeviceGetAttribute) X(cuGetErrorString)     \
+  X(cuDevicePrimaryCtxRetain) X(cuCtxGetCurrent) X(cuCtxSetCurrent) X(cuModuleLoadData)        \
+  X(cuModuleGetFunction) X(cuModuleUnload) X(cuFuncSetAttribute) X(cuFuncGetAttribute)         \
+  X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) X(cuMemAlloc) X(cuMemFree) X(cuMemsetD32)      \
+  X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoH) X(cuMemcpyHtoD)                    \
+  X(cuStreamSynchronize)
+
+struct Driver {
+  void* handle = nullptr;
+  bool ok = false;
+  std::string why;
+#define X(f) decltype(&f) p_##f = nullptr;
+  KCG_DRV_FUNCS(X)
+#undef X
+};
+
+Driver& driver() {
+  static Driver d;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    d.handle = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    if (!d.handle) {
+      d.why = std::string("cannot open libcuda.so.1: ") + dlerror();
+      return;
+    }
+    bool all = true;
+#define X(f)                                                                  \
+  d.p_##f = reinterpret_cast<decltype(&f)>(dlsym(d.handle, KCG_STR(f)));      \
+  if (!d.p_##f) {                                                             \
+    all = false;                                                              \
+    d.why += std::string("missing driver symbol ") + KCG_STR(f) + "; ";       \
+  }
+    KCG_DRV_FUNCS(X)
+#undef X
+    if (!all) return;
+    CUresult r = d.p_cuInit(0);
+    if (r != CUDA_SUCCESS) {
+      d.why = "cuInit failed with CUresult " + std::to_string(static_cast<int>(r));
+      return;
+    }
+    d.ok = true;
+  });
+  return d;
+}
+
+int drv_fail(CUresult r, const char* what) {
+  const char* s = nullptr;
+  Driver& d = driver();
+  if (d.p_cuGetErrorString) d.p_cuGetErrorString(r, &s);
+  return fail(static_cast<int>(r), "%s: %s", what, s ? s : "unknown CUDA error");
+}
+
+#define DRV(call)                                             \
+  do {                                                        \
+    CUresult _r = driver().p_##call;                          \
+    if (_r != CUDA_SUCCESS) return drv_fail(_r, #call);       \
+  } while (0)
+
+int need_driver() {
+  Driver& d = driver();
+  if (!d.ok) return fail(KCG_E_NO_DRIVER, "CUDA driver unavailable (%s)", d.why.c_str());
+  return 0;
+}
+
+// ------------------------------------------------------------- per-device state
+struct DeviceState {
+  bool init = false;
+  CUcontext ctx = nullptr;
+  CUdeviceptr status = 0;      // 4 x u32
+  CUdeviceptr ws = 0;          // split-K partials
+  size_t ws_bytes = 0;
+  CUdeviceptr counters = 0;    // split-K tile counters
+  size_t counters_n = 0;
+  CUdeviceptr hbuf[3] = {0, 0, 0};  // device copies for kcg_matmul_host
+  size_t hbuf_bytes[3] = {0, 0, 0};
+  std::unordered_map<std::string, CUtensorMap> tmaps;
+};
+constexpr int kMaxDevices = 16;
+DeviceState g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
+std::atomic<uint64_t> g_launches{0};
+
+int ensure_device(int device, DeviceState** out) {
+  if (int e = need_driver()) return e;
+  if (device < 0 || device >= kMaxDevices) return fail(KCG_E_BAD_ARG, "device %d out of range", device);
+  DeviceState& s = g_dev[device];
+  if (!s.init) {
+    CUdevice dev;
+    DRV(cuDeviceGet(&dev, device));
+    DRV(cuDevicePrimaryCtxRetain(&s.ctx, dev));
+  }
+  CUcontext cur = nullptr;
+  DRV(cuCtxGetCurrent(&cur));
+  if (cur != s.ctx) DRV(cuCtxSetCurrent(s.ctx));
+  if (!s.init) {
+    DRV(cuMemAlloc(&s.status, 16));
+    DRV(cuMemsetD32(s.status, 0, 4));
+    s.init = true;
+  }
+  *out = &s;
+  return 0;
+}
+
+int grow(CUdeviceptr* p, size_t* have, size_t need) {
+  if (*have >= need) return 0;
+  if (*p) DRV(cuMemFree(*p));
+  *p = 0;
+  *have = 0;
+  DRV(cuMemAlloc(p, need));
+  *have = need;
+  return 0;
+}
+
+// ----------------------------------------------------------------- config logic
+struct Cfg {
+  int v[KCG_NUM_CFG_KEYS];
+  int operator[](int i) const { return v[i]; }
+};
+
+const char* dtype_str(int dt) {
+  switch (dt) {
+    case KCG_DTYPE_FLOAT16: return "float16";
+    case KCG_DTYPE_FLOAT32: return "float32";
+    case KCG_DTYPE_BFLOAT16: return "bfloat16";
+    default: return nullptr;
+  }
+}
+
+struct Resolved {
+  int kernel = 0;
+  int stages = 0;
+  int num_sms = 148;
+};
+
+// The reference's KernelArgMatmul.check() (Operators/matmul.py:180-194) for the
+// thread-level keys; the SIMT kernel consumes all of them.
+int check_simt(const Cfg& c) {
+  const int bm = c[KCG_CFG_BLOCK_SIZE_M], bn = c[KCG_CFG_BLOCK_SIZE_N], bk = c[KCG_CFG_BLOCK_SIZE_K];
+  const int tm = c[KCG_CFG_THREAD_SIZE_M], tn = c[KCG_CFG_THREAD_SIZE_N];
+  if (tm <= 0 || tn <= 0 || bm % tm || bn % tn) return fail(KCG_E_BAD_CONFIG, "BLOCK_SIZE_M/N not divisible by THREAD_SIZE_M/N");
+  if (c[KCG_CFG_BLOCK_LAYOUT_M] * c[KCG_CFG_WARP_LAYOUT_M] != bm / tm ||
+      c[KCG_CFG_BLOCK_LAYOUT_N] * c[KCG_CFG_WARP_LAYOUT_N] != bn / tn)
+    return fail(KCG_E_BAD_CONFIG, "BLOCK_LAYOUT x WARP_LAYOUT does not cover BLOCK_SIZE / THREAD_SIZE");
+  if (c[KCG_CFG_WARP_LAYOUT_M] * c[KCG_CFG_WARP_LAYOUT_N] != c[KCG_CFG_WARP_SIZE])
+    return fail(KCG_E_BAD_CONFIG, "WARP_LAYOUT_M * WARP_LAYOUT_N != WARP_SIZE");
+  const int lsu = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
+  const int threads = (bm / tm) * (bn / tn) * lsu;
+  if (threads > 1024) return fail(KCG_E_BAD_CONFIG, "%d threads per block exceed 1024", threads);
+  if (bk % lsu) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U must divide BLOCK_SIZE_K");
+  auto pos = [](int x) { return x > 0 ? x : 1; };
+  const int wswa = pos(c[KCG_CFG_WARP_SCATTER_WIDTH_A]), wswb = pos(c[KCG_CFG_WARP_SCATTER_WIDTH_B]);
+  const int tswa = pos(c[KCG_CFG_THREAD_SCATTER_WIDTH_A]), tswb = pos(c[KCG_CFG_THREAD_SCATTER_WIDTH_B]);
+  if (tm % wswa || wswa % tswa || tn % wswb || wswb % tswb)
+    return fail(KCG_E_BAD_CONFIG, "scatter widths must nest: THREAD_SIZE %% WARP_SCATTER %% THREAD_SCATTER");
+  const int glwa = pos(c[KCG_CFG_GLOB_LOAD_WIDTH_A]), glwb = pos(c[KCG_CFG_GLOB_LOAD_WIDTH_B]);
+  if ((bm * bk) % (threads * glwa) || (bn * bk) % (threads * glwb))
+    return fail(KCG_E_BAD_CONFIG, "tile loads do not split evenly over %d threads", threads);
+  if ((c[KCG_CFG_IS_ATRANS] ? bm : bk) % glwa || bn % glwb)
+    return fail(KCG_E_BAD_CONFIG, "GLOB_LOAD_WIDTH does not divide the contiguous tile extent");
+  const int gsw = pos(c[KCG_CFG_GLOB_STORE_WIDTH]);
+  if (lsu > 1 ? ((bm * bn) % (threads * gsw) != 0 && (bm * bn) % gsw != 0) : (tswb % (gsw < tswb ? gsw : tswb) != 0))
+    return fail(KCG_E_BAD_CONFIG, "GLOB_STORE_WIDTH incompatible with the tile");
+  if (lsu > 1 && bn % gsw) return fail(KCG_E_BAD_CONFIG, "GLOB_STORE_WIDTH must divide BLOCK_SIZE_N");
+  return 0;
+}
+
+int simt_smem_bytes(const Cfg& c) {
+  const int bm = c[KCG_CFG_BLOCK_SIZE_M], bn = c[KCG_CFG_BLOCK_SIZE_N], bk = c[KCG_CFG_BLOCK_SIZE_K];
+  const int lsu = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
+  const int ab = (c[KCG_CFG_SHARED_PREFETCH] ? 2 : 1) * (bm + bn) * bk;
+  const int cc = lsu > 1 ? lsu * bm * bn : 0;
+  return 4 * (ab > cc ? ab : cc);
+}
+
+int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
+  const int dt = c[KCG_CFG_DATATYPE_A];
+  if (!dtype_str(dt)) return fail(KCG_E_BAD_CONFIG, "unsupported DATATYPE_A %d (2 float16, 4 float32, 62 bfloat16)", dt);
+  if (c[KCG_CFG_DATATYPE_B] != dt || c[KCG_CFG_DATATYPE_C] != dt)
+    return fail(KCG_E_BAD_CONFIG, "DATATYPE_A/B/C must be equal");
+  const int bm = c[KCG_CFG_BLOCK_SIZE_M], bn = c[KCG_CFG_BLOCK_SIZE_N], bk = c[KCG_CFG_BLOCK_SIZE_K];
+  const int M = c[KCG_CFG_M_SIZE], N = c[KCG_CFG_N_SIZE], K = c[KCG_CFG_K_SIZE];
+  if (bm <= 0 || bn <= 0 || bk <= 0 || M <= 0 || N <= 0 || K <= 0)
+    return fail(KCG_E_BAD_CONFIG, "sizes must be positive");
+  // problem-size check of KernelArgMatmul.check()
+  if (M % bm || N % bn || K % bk)
+    return fail(KCG_E_BAD_CONFIG, "M,N,K = %d,%d,%d not divisible by BLOCK_SIZE_M,N,K = %d,%d,%d", M, N, K, bm, bn, bk);
+  r->num_sms = (opts && opts->num_sms > 0) ? opts->num_sms : 148;
+  int want = opts ? opts->kernel : KCG_KERNEL_AUTO;
+  const int x3 = (want == KCG_KERNEL_TF32X1) ? 0 : 1;
+  auto pick_stages = [&](int x3v) {
+    if (opts && opts->num_stages > 0) return opts->num_stages;
+    if (!c[KCG_CFG_SHARED_PREFETCH]) return 2;
+    int s = 2;
+    while (s < 6 && kcg::tc_config_error(dt, bm, bn, bk, s + 1, x3v) == 0) ++s;
+    return s;
+  };
+  if (want == KCG_KERNEL_AUTO) {
+    const int st = pick_stages(1);
+    want = (kcg::tc_config_error(dt, bm, bn, bk, st, 1) == 0) ? KCG_KERNEL_TCGEN05 : KCG_KERNEL_SIMT;
+  }
+  r->kernel = want;
+  if (want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TF32X1) {
+    if (want == KCG_KERNEL_TF32X1 && dt != KCG_DTYPE_FLOAT32)
+      return fail(KCG_E_BAD_CONFIG, "the single-pass TF32 kernel needs float32 data");
+    r->stages = pick_stages(x3);
+    const int e = kcg::tc_config_error(dt, bm, bn, bk, r->stages, x3);
+    if (e) return fail(KCG_E_BAD_CONFIG, "tile %dx%dx%d / %d stages not buildable by the tcgen05 kernel (rule %d)", bm, bn, bk, r->stages, e);
+    if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
+    const int splitk = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
+    if (splitk > K / bk) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U %d exceeds the %d K blocks", splitk, K / bk);
+  } else if (want == KCG_KERNEL_SIMT) {
+    if (int e = check_simt(c)) return e;
+    r->stages = c[KCG_CFG_SHARED_PREFETCH] ? 2 : 1;
+    if (simt_smem_bytes(c) > 227 * 1024) return fail(KCG_E_BAD_CONFIG, "shared memory %d B exceeds 227 KiB", simt_smem_bytes(c));
+  } else if (want == KCG_KERNEL_NAIVE) {
+    r->stages = 1;
+  } else {
+    return fail(KCG_E_BAD_CONFIG, "unknown kernel family %d", want);
+  }
+  return 0;
+}
+
+// Same scheme as MatmulParams::getKernelName (src/main.cc:119-145) plus the two
+// keys this library adds (stages, kernel family).
+std::string kernel_name(const Cfg& c, const Resolved& r) {
+  std::ostringstream ss;
+  ss << "GEMM_MNK" << c[KCG_CFG_M_SIZE] << "x" << c[KCG_CFG_N_SIZE] << "x" << c[KCG_CFG_K_SIZE] << "_";
+  ss << "DTabc" << dtype_str(c[KCG_CFG_DATATYPE_A]) << "x" << dtype_str(c[KCG_CFG_DATATYPE_B]) << "x"
+     << dtype_str(c[KCG_CFG_DATATYPE_C]) << "_";
+  ss << "AT" << (c[KCG_CFG_IS_ATRANS] ? 1 : 0) << "_";
+  ss << "TTmn" << c[KCG_CFG_THREAD_SIZE_M] << "x" << c[KCG_CFG_THREAD_SIZE_N] << "_";
+  ss << "BTmnk" << c[KCG_CFG_BLOCK_SIZE_M] << "x" << c[KCG_CFG_BLOCK_SIZE_N] << "x" << c[KCG_CFG_BLOCK_SIZE_K] << "_";
+  ss << "BLmn" << c[KCG_CFG_BLOCK_LAYOUT_M] << "x" << c[KCG_CFG_BLOCK_LAYOUT_N] << "_";
+  ss << "WLmn" << c[KCG_CFG_WARP_LAYOUT_M] << "x" << c[KCG_CFG_WARP_LAYOUT_N] << "_";
+  ss << "GLWab" << c[KCG_CFG_GLOB_LOAD_WIDTH_A] << "x" << c[KCG_CFG_GLOB_LOAD_WIDTH_B] << "_";
+  ss << "GSW" << c[KCG_CFG_GLOB_STORE_WIDTH] << "_";
+  ss << "WSWab" << c[KCG_CFG_WARP_SCATTER_WIDTH_A] << "x" << c[KCG_CFG_WARP_SCATTER_WIDTH_B] << "_";
+  ss << "TSWab" << c[KCG_CFG_THREAD_SCATTER_WIDTH_A] << "x" << c[KCG_CFG_THREAD_SCATTER_WIDTH_B] << "_";
+  ss << "LSU" << c[KCG_CFG_LOCAL_SPLIT_U] << "_";
+  ss << "BM" << c[KCG_CFG_BLOCK_MAPPING] << "_";
+  ss << "UNROLL" << c[KCG_CFG_UNROLL_NUM] << "_";
+  ss << "REGP" << c[KCG_CFG_REG_PREFETCH] << "_";
+  ss << "SHMP" << c[KCG_CFG_SHARED_PREFETCH] << "_";
+  ss << "LC" << c[KCG_CFG_LOAD_CONTINUOUS] << "_";
+  ss << "RC" << c[KCG_CFG_REDUCE_C_CONTINUOUS] << "_";
+  ss << "ST" << r.stages << "_V" << r.kernel;
+  return ss.str();
+}
+
+std::string lib_dir() {
+  Dl_info info;
+  if (dladdr(reinterpret_cast<void*>(&lib_dir), &info) && info.dli_fname) {
+    std::string p = info.dli_fname;
+    const size_t slash = p.rfind('/');
+    if (slash != std::string::npos) return p.substr(0, slash);
+  }
+  return ".";
+}
+
+std::string cache_dir() {
+  const char* e = getenv("KCG_CACHE_DIR");
+  std::string d = (e && *e) ? std::string(e) : lib_dir() + "/_cache";
+  mkdir(d.c_str(), 0755);
+  return d;
+}
+
+std::string kernel_src_dir() {
+  const char* e = getenv("KCG_KERNEL_SRC_DIR");
+  return (e && *e) ? std::string(e) : lib_dir() + "/csrc/kernels";
+}
+
+std::string find_nvcc() {
+  const char* e = getenv("KCG_NVCC");
+  if (e && *e) return e;
+  if (access("/usr/local/cuda/bin/nvcc", X_OK) == 0) return "/usr/local/cuda/bin/nvcc";
+  const char* path = getenv("PATH");
+  if (path) {
+    std::stringstream ss(path);
+    std::string dir;
+    while (std::getline(ss, dir, ':')) {
+      const std::string cand = dir + "/nvcc";
+      if (access(cand.c_str(), X_OK) == 0) return cand;
+    }
+  }
+  return "";
+}
+
+bool file_exists(const std::string& p) {
+  struct stat st;
+  return stat(p.c_str(), &st) == 0 && st.st_size > 0;
+}
+
+std::string tail_of(const std::string& path, size_t n) {
+  std::ifstream f(path);
+  std::stringstream ss;
+  ss << f.rdbuf();
+  std::string s = ss.str();
+  return s.size() > n ? s.substr(s.size() - n) : s;
+}
+
+std::vector<std::string> macro_flags(const Cfg& c, const Resolved& r, const std::string& name) {
+  auto pos = [](int x) { return x > 0 ? x : 1; };
+  std::vector<std::string> f;
+  auto D = [&](const char* k, int v) { f.push_back(std::string("-DKCG_") + k + "=" + std::to_string(v)); };
+  f.push_back("-DKCG_KERNEL_NAME=" + name);
+  D("VARIANT", r.kernel);
+  D("DTYPE", c[KCG_CFG_DATATYPE_A]);
+  D("BM", c[KCG_CFG_BLOCK_SIZE_M]);
+  D("BN", c[KCG_CFG_BLOCK_SIZE_N]);
+  D("BK", c[KCG_CFG_BLOCK_SIZE_K]);
+  D("STAGES", r.stages);
+  D("ATRANS", c[KCG_CFG_IS_ATRANS] ? 1 : 0);
+  D("SPLITK", pos(c[KCG_CFG_LOCAL_SPLIT_U]));
+  D("GROUP", c[KCG_CFG_BLOCK_MAPPING] > 0 ? c[KCG_CFG_BLOCK_MAPPING] : 0);
+  if (r.kernel == KCG_KERNEL_SIMT) {
+    D("TM", c[KCG_CFG_THREAD_SIZE_M]);
+    D("TN", c[KCG_CFG_THREAD_SIZE_N]);
+    D("BLM", c[KCG_CFG_BLOCK_LAYOUT_M]);
+    D("BLN", c[KCG_CFG_BLOCK_LAYOUT_N]);
+    D("WLM", c[KCG_CFG_WARP_LAYOUT_M]);
+    D("WLN", c[KCG_CFG_WARP_LAYOUT_N]);
+    D("WSWA", pos(c[KCG_CFG_WARP_SCATTER_WIDTH_A]));
+    D("WSWB", pos(c[KCG_CFG_WARP_SCATTER_WIDTH_B]));
+    D("TSWA", pos(c[KCG_CFG_THREAD_SCATTER_WIDTH_A]));
+    D("TSWB", pos(c[KCG_CFG_THREAD_SCATTER_WIDTH_B]));
+    D("GLWA", pos(c[KCG_CFG_GLOB_LOAD_WIDTH_A]));
+    D("GLWB", pos(c[KCG_CFG_GLOB_LOAD_WIDTH_B]));
+    D("GSW", pos(c[KCG_CFG_GLOB_STORE_WIDTH]));
+    D("SHMP", c[KCG_CFG_SHARED_PREFETCH] ? 1 : 0);
+    D("REGP", c[KCG_CFG_REG_PREFETCH] ? 1 : 0);
+  }
+  return f;
+}
+
+int run_nvcc(const std::string& nvcc, const std::vector<std::string>& flags, const std::string& out,
+             const std::string& log) {
+  std::vector<std::string> args = {nvcc, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-O3",
+                                   "-std=c++17", "-lineinfo", "-I" + kernel_src_dir()};
+  args.insert(args.end(), flags.begin(), flags.end());
+  args.push_back("-o");
+  args.push_back(out);
+  args.push_back(kernel_src_dir() + "/gemm_entry.cu");
+  std::vector<char*> argv;
+  for (auto& a : args) argv.push_back(const_cast<char*>(a.c_str()));
+  argv.push_back(nullptr);
+  posix_spawn_file_actions_t fa;
+  posix_spawn_file_actions_init(&fa);
+  posix_spawn_file_actions_addopen(&fa, 1, log.c_str(), O_WRONLY | O_CREAT | O_TRUNC, 0644);
+  posix_spawn_file_actions_adddup2(&fa, 1, 2);
+  pid_t pid;
+  const int rc = posix_spawn(&pid, nvcc.c_str(), &fa, nullptr, argv.data(), environ);
+  posix_spawn_file_actions_destroy(&fa);
+  if (rc != 0) return -1;
+  int status = 0;
+  if (waitpid(pid, &status, 0) < 0) return -1;
+  return (WIFEXITED(status) && WEXITSTATUS(status) == 0) ? 0 : 1;
+}
+
+int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const std::string& path,
+              kcg_kernel_info* out) {
+  memset(out, 0, sizeof(*out));
+  if (path.size() >= sizeof(out->path) || name.size() >= sizeof(out->name))
+    return fail(KCG_E_TOO_LARGE, "path or kernel name too long");
+  strcpy(out->path, path.c_str());
+  strcpy(out->name, name.c_str());
+  const int bm = c[KCG_CFG_BLOCK_SIZE_M], bn = c[KCG_CFG_BLOCK_SIZE_N], bk = c[KCG_CFG_BLOCK_SIZE_K];
+  const int M = c[KCG_CFG_M_SIZE], N = c[KCG_CFG_N_SIZE], K = c[KCG_CFG_K_SIZE];
+  const int lsu = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
+  const int tiles = (M / bm) * (N / bn);
+  out->grid[1] = out->grid[2] = out->block[1] = out->block[2] = 1;
+  out->cluster[0] = out->cluster[1] = out->cluster[2] = 1;
+  if (r.kernel == KCG_KERNEL_TCGEN05 || r.kernel == KCG_KERNEL_TF32X1) {
+    const int x3 = (r.kernel == KCG_KERNEL_TCGEN05) ? 1 : 0;
+    const int units = tiles * lsu;
+    out->grid[0] = units < r.num_sms ? units : r.num_sms;  // persistent CTAs
+    out->block[0] = 192 + ((c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 128 : 0);
+    out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm, bn, bk, r.stages, x3);
+  } else if (r.kernel == KCG_KERNEL_SIMT) {
+    // grid/block as the reference derives them (Optimizer.cc:20,336; Rewriter.cc:726-761)
+    out->grid[0] = tiles;
+    out->block[0] = (bm / c[KCG_CFG_THREAD_SIZE_M]) * (bn / c[KCG_CFG_THREAD_SIZE_N]) * lsu;
+    out->smem_bytes = simt_smem_bytes(c);
+  } else {
+    out->grid[0] = (N + 15) / 16;
+    out->grid[1] = (M + 15) / 16;
+    out->block[0] = 16;
+    out->block[1] = 16;
+    out->smem_bytes = 0;
+  }
+  out->kernel = r.kernel;
+  out->dtype = c[KCG_CFG_DATATYPE_A];
+  out->bm = bm;
+  out->bn = bn;
+  out->bk = bk;
+  out->stages = r.stages;
+  out->splitk = (r.kernel == KCG_KERNEL_NAIVE) ? 1 : lsu;
+  out->group = c[KCG_CFG_BLOCK_MAPPING];
+  out->atrans = c[KCG_CFG_IS_ATRANS] ? 1 : 0;
+  out->m = M;
+  out->n = N;
+  out->k = K;
+  (void)K;
+  return 0;
+}
+
+int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64_t inner, uint64_t outer,
+               uint64_t row_bytes, int box_inner, int box_outer, int swizzle) {
+  char key[160];
+  snprintf(key, sizeof(key), "%d:%llx:%llu:%llu:%llu:%d:%d:%d", dtype, (unsigned long long)ptr,
+           (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_bytes, box_inner,
+           box_outer, swizzle);
+  {
+    std::lock_guard<std::mutex> g(g_dev_mutex);
+    auto it = s->tmaps.find(key);
+    if (it != s->tmaps.end()) {
+      *out = it->second;
+      return 0;
+    }
+  }
+  const CUtensorMapDataType dt = dtype == KCG_DTYPE_FLOAT32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == KCG_DTYPE_FLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cuuint64_t gdim[2] = {inner, outer};
+  cuuint64_t gstride[1] = {row_bytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  if (ptr % 16 || row_bytes % 16)
+    return fail(KCG_E_BAD_ARG, "TMA needs 16-byte aligned base (%llx) and row pitch (%llu)", (unsigned long long)ptr,
+                (unsigned long long)row_bytes);
+  DRV(cuTensorMapEncodeTiled(out, dt, 2, reinterpret_cast<void*>(ptr), gdim, gstride, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(swizzle),
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  std::lock_guard<std::mutex> g(g_dev_mutex);
+  if (s->tmaps.size() > 4096) s->tmaps.clear();
+  s->tmaps[key] = *out;
+  return 0;
+}
+
+}  // namespace
+
+// ============================================================================ C ABI
+extern "C" {
+
+const char* kcg_last_error(void) { return g_last_error.c_str(); }
+const char* kcg_version(void) { return "kcg-b200 0.1 (sm_100a)"; }
+uint64_t kcg_launch_count(void) { return g_launches.load(); }
+
+const char* kcg_cache_dir(void) {
+  static thread_local std::string d;
+  d = cache_dir();
+  return d.c_str();
+}
+
+int kcg_kernel_name(const int32_t cfg[KCG_NUM_CFG_KEYS], const kcg_compile_opts* opts, char* buf, int buf_len) {
+  if (!cfg || !buf || buf_len <= 0) return fail(KCG_E_BAD_ARG, "null argument");
+  Cfg c;
+  memcpy(c.v, cfg, sizeof(c.v));
+  Resolved r;
+  if (int e = resolve(c, opts, &r)) return e;
+  const std::string n = kernel_name(c, r);
+  if (static_cast<int>(n.size()) >= buf_len) return fail(KCG_E_TOO_LARGE, "buffer too small for kernel name");
+  strcpy(buf, n.c_str());
+  return 0;
+}
+
+int kcg_compile_matmul_ex(const int32_t cfg[KCG_NUM_CFG_KEYS], const kcg_compile_opts* opts, kcg_kernel_info* out) {
+  if (!cfg || !out) return fail(KCG_E_BAD_ARG, "null argument");
+  Cfg c;
+  memcpy(c.v, cfg, sizeof(c.v));
+  Resolved r;
+  if (int e = resolve(c, opts, &r)) return e;
+  const std::string name = kernel_name(c, r);
+  const std::string dir = cache_dir();
+  const std::string path = dir + "/" + name + ".cubin";
+  if (int e = fill_info(c, r, name, path, out)) return e;
+  if (file_exists(path) && !(opts && opts->force)) return 0;
+  const std::string nvcc = find_nvcc();
+  if (nvcc.empty())
+    return fail(KCG_E_COMPILE, "no nvcc found (set KCG_NVCC) and no prebuilt cubin %s", path.c_str());
+  const std::string tmp = dir + "/" + name + "." + std::to_string(getpid()) + ".tmp.cubin";
+  const std::string log = dir + "/" + name + "." + std::to_string(getpid()) + ".log";
+  const int rc = run_nvcc(nvcc, macro_flags(c, r, name), tmp, log);
+  if (rc != 0) {
+    const std::string t = tail_of(log, 1500);
+    unlink(tmp.c_str());
+    return fail(KCG_E_COMPILE, "nvcc failed for %s:\n%s", name.c_str(), t.c_str());
+  }
+  unlink(log.c_str());
+  if (rename(tmp.c_str(), path.c_str()) != 0) return fail(KCG_E_IO, "cannot move cubin to %s", path.c_str());
+  return 0;
+}
+
+int kcg_compile_matmul(const int32_t cfg[KCG_NUM_CFG_KEYS], kcg_kernel_info* out) {
+  return kcg_compile_matmul_ex(cfg, nullptr, out);
+}
+
+int kcg_device_properties(int device, kcg_device_props* out) {
+  if (!out) return fail(KCG_E_BAD_ARG, "null argument");
+  if (int e = need_driver()) return e;
+  CUdevice dev;
+  DRV(cuDeviceGet(&dev, device));
+  int v = 0;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_MAX_SHARED_MEMORY_PER_BLOCK_OPTIN, dev));
+  out->max_shared_mem = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, dev));
+  out->multiprocessor_count = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_CLOCK_RATE, dev));
+  out->sm_clock_rate = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_MEMORY_CLOCK_RATE, dev));
+  out->mem_clock_rate = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_GLOBAL_MEMORY_BUS_WIDTH, dev));
+  out->mem_bus_width = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_L2_CACHE_SIZE, dev));
+  out->l2_cache_bytes = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, dev));
+  out->cc_major = v;
+  DRV(cuDeviceGetAttribute(&v, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR, dev));
+  out->cc_minor = v;
+  return 0;
+}
+
+int kcg_load_binary(const char* name, const char* path, int shared, int device, uint64_t* module,
+                    uint64_t* function, int* n_regs, int* n_spills) {
+  if (!name || !path || !module || !function) return fail(KCG_E_BAD_ARG, "null argument");
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  std::ifstream f(path, std::ios::binary);
+  if (!f) return fail(KCG_E_IO, "cannot open cubin %s", path);
+  std::vector<char> image((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+  if (image.empty()) return fail(KCG_E_IO, "empty cubin %s", path);
+  image.push_back(0);
+  CUmodule mod;
+  CUfunction fn;
+  DRV(cuModuleLoadData(&mod, image.data()));
+  CUresult r = driver().p_cuModuleGetFunction(&fn, mod, name);
+  if (r != CUDA_SUCCESS) {
+    driver().p_cuModuleUnload(mod);
+    return drv_fail(r, "cuModuleGetFunction");
+  }
+  if (shared > 48 * 1024) {
+    r = driver().p_cuFuncSetAttribute(fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, shared);
+    if (r != CUDA_SUCCESS) {
+      driver().p_cuModuleUnload(mod);
+      return drv_fail(r, "cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES)");
+    }
+  }
+  int regs = 0, local = 0;
+  driver().p_cuFuncGetAttribute(&regs, CU_FUNC_ATTRIBUTE_NUM_REGS, fn);
+  driver().p_cuFuncGetAttribute(&local, CU_FUNC_ATTRIBUTE_LOCAL_SIZE_BYTES, fn);
+  if (n_regs) *n_regs = regs;
+  if (n_spills) *n_spills = local / 4;
+  *module = reinterpret_cast<uint64_t>(mod);
+  *function = reinterpret_cast<uint64_t>(fn);
+  return 0;
+}
+
+int kcg_unload(uint64_t module) {
+  if (int e = need_driver()) return e;
+  DRV(cuModuleUnload(reinterpret_cast<CUmodule>(module)));
+  return 0;
+}
+
+int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                    uint64_t B, uint64_t C) {
+  if (!function || !info || !A || !B || !C) return fail(KCG_E_BAD_ARG, "null argument");
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  KcgGemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int M = info->m, N = info->n, K = info->k;
+  const int eb = (info->dtype == KCG_DTYPE_FLOAT32) ? 4 : 2;
+  p.A = reinterpret_cast<const void*>(A);
+  p.B = reinterpret_cast<const void*>(B);
+  p.C = reinterpret_cast<void*>(C);
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.lda = info->atrans ? M : K;
+  p.ldb = N;
+  p.ldc = N;
+  p.status = reinterpret_cast<unsigned int*>(s->status);
+  if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1) {
+    const kcg::TcLayout L = kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
+    if (info->atrans) {
+      if (int e = encode_map(s, &p.tmA, info->dtype, A, M, K, static_cast<uint64_t>(M) * eb, L.a_box_inner,
+                             L.a_box_outer, L.a_tma_swizzle))
+        return e;
+    } else {
+      if (int e = encode_map(s, &p.tmA, info->dtype, A, K, M, static_cast<uint64_t>(K) * eb, L.a_box_inner,
+                             L.a_box_outer, L.a_tma_swizzle))
+        return e;
+    }
+    if (int e = encode_map(s, &p.tmB, info->dtype, B, N, K, static_cast<uint64_t>(N) * eb, L.b_box_inner,
+                           L.b_box_outer, L.b_tma_swizzle))
+      return e;
+    if (info->splitk > 1) {
+      std::lock_guard<std::mutex> g(g_dev_mutex);
+      const size_t need = static_cast<size_t>(info->splitk) * M * N * sizeof(float);
+      if (int e = grow(&s->ws, &s->ws_bytes, need)) return e;
+      const size_t tiles = static_cast<size_t>(M / info->bm) * (N / info->bn);
+      if (s->counters_n < tiles) {
+        size_t have = s->counters_n * 4;
+        if (int e = grow(&s->counters, &have, tiles * 4)) return e;
+        s->counters_n = tiles;
+        DRV(cuMemsetD32(s->counters, 0, tiles));
+      }
+      p.splitk_ws = reinterpret_cast<float*>(s->ws);
+      p.tile_counters = reinterpret_cast<unsigned int*>(s->counters);
+    }
+  }
+  void* args[1] = {&p};
+  CUlaunchConfig cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDimX = info->grid[0];
+  cfg.gridDimY = info->grid[1];
+  cfg.gridDimZ = info->grid[2];
+  cfg.blockDimX = info->block[0];
+  cfg.blockDimY = info->block[1];
+  cfg.blockDimZ = info->block[2];
+  cfg.sharedMemBytes = info->smem_bytes;
+  cfg.hStream = reinterpret_cast<CUstream>(stream);
+  CUlaunchAttribute attr[1];
+  cfg.numAttrs = 0;
+  if (info->cluster[0] * info->cluster[1] * info->cluster[2] > 1) {
+    attr[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr[0].value.clusterDim.x = info->cluster[0];
+    attr[0].value.clusterDim.y = info->cluster[1];
+    attr[0].value.clusterDim.z = info->cluster[2];
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  }
+  DRV(cuLaunchKernelEx(&cfg, reinterpret_cast<CUfunction>(function), args, nullptr));
+  g_launches.fetch_add(1);
+  return 0;
+}
+
+int kcg_check_status(int device, uint64_t stream) {
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  DRV(cuStreamSynchronize(reinterpret_cast<CUstream>(stream)));
+  unsigned int st[4] = {0, 0, 0, 0};
+  DRV(cuMemcpyDtoH(st, s->status, sizeof(st)));
+  if (st[0] != 0) {
+    DRV(cuMemsetD32(s->status, 0, 4));
+    // a timed-out split-K launch may leave counters mid-count
+    if (s->counters) DRV(cuMemsetD32(s->counters, 0, s->counters_n));
+    static const char* role[] = {"", "TMA producer", "MMA issuer", "epilogue", "splitter", "shape"};
+    return fail(KCG_E_DEVICE_TIMEOUT, "kernel gave up in a bounded wait: role %s (code %u), block %u, detail %u/%u",
+                st[0] < 6 ? role[st[0]] : "?", st[0], st[1], st[2], st[3]);
+  }
+  return 0;
+}
+
+int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                    const void* hostA, const void* hostB, void* hostC) {
+  if (!info || !hostA || !hostB || !hostC) return fail(KCG_E_BAD_ARG, "null argument");
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  const size_t eb = (info->dtype == KCG_DTYPE_FLOAT32) ? 4 : 2;
+  const size_t bytes[3] = {static_cast<size_t>(info->m) * info->k * eb, static_cast<size_t>(info->k) * info->n * eb,
+                           static_cast<size_t>(info->m) * info->n * eb};
+  {
+    std::lock_guard<std::mutex> g(g_dev_mutex);
+    for (int i = 0; i < 3; ++i)
+      if (int e = grow(&s->hbuf[i], &s->hbuf_bytes[i], bytes[i])) return e;
+  }
+  CUstream st = reinterpret_cast<CUstream>(stream);
+  DRV(cuMemcpyHtoDAsync(s->hbuf[0], hostA, bytes[0], st));
+  DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], st));
+  if (int e = kcg_launch_gemm(function, info, device, stream, s->hbuf[0], s->hbuf[1], s->hbuf[2])) return e;
+  DRV(cuMemcpyDtoHAsync(hostC, s->hbuf[2], bytes[2], st));
+  DRV(cuStreamSynchronize(st));
+  return 0;
+}
+
+int kcg_shutdown(void) {
+  Driver& d = driver();
+  if (!d.ok) return 0;
+  std::lock_guard<std::mutex> g(g_dev_mutex);
+  for (int i = 0; i < kMaxDevices; ++i) {
+    DeviceState& s = g_dev[i];
+    if (!s.init) continue;
+    d.p_cuCtxSetCurrent(s.ctx);
+    if (s.status) d.p_cuMemFree(s.status);
+    if (s.ws) d.p_cuMemFree(s.ws);
+    if (s.counters) d.p_cuMemFree(s.counters);
+    for (int j = 0; j < 3; ++j)
+      if (s.hbuf[j]) d.p_cuMemFree(s.hbuf[j]);
+    s = DeviceState();
+  }
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,51 @@
+// One translation unit = one kernel. The compile entry (kcg_compile_matmul) runs
+// nvcc on this file once per tuning config, passing the config as -DKCG_* macros
+// and the kernel's symbol as -DKCG_KERNEL_NAME, and loads the resulting cubin
+// with the driver API. This replaces the reference's per-config MLIR -> AMDGCN ->
+// hsaco pipeline (src/main.cc:250-305) for the GEMM path.
+#include <type_traits>
+
+#include "gemm_params.h"
+
+#ifndef KCG_KERNEL_NAME
+#error "KCG_KERNEL_NAME must be defined"
+#endif
+#ifndef KCG_VARIANT
+#error "KCG_VARIANT must be defined"
+#endif
+
+#if KCG_DTYPE == KCG_DT_F32
+#define KCG_T float
+#elif KCG_DTYPE == KCG_DT_F16
+#define KCG_T __half
+#elif KCG_DTYPE == KCG_DT_BF16
+#define KCG_T __nv_bfloat16
+#else
+#error "unsupported KCG_DTYPE"
+#endif
+
+#if KCG_VARIANT == KCG_VARIANT_TCGEN05 || KCG_VARIANT == KCG_VARIANT_TF32X1
+#include "gemm_tcgen05.cuh"
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK,
+                         KCG_GROUP, (KCG_VARIANT == KCG_VARIANT_TCGEN05) ? 1 : 0>;
+extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
+#elif KCG_VARIANT == KCG_VARIANT_SIMT
+#include "gemm_simt.cuh"
+using Gemm = kcg::SimtGemm<KCG_T, KCG_BM, KCG_BN, KCG_BK, KCG_TM, KCG_TN, KCG_BLM, KCG_BLN, KCG_WLM,
+                           KCG_WLN, KCG_WSWA, KCG_WSWB, KCG_TSWA, KCG_TSWB, KCG_SPLITK, KCG_GROUP,
+                           KCG_GLWA, KCG_GLWB, KCG_GSW, KCG_SHMP, KCG_REGP, KCG_ATRANS>;
+extern "C" __global__ void __launch_bounds__(Gemm::THREADS)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
+#elif KCG_VARIANT == 100  // naive one-thread-per-element device reference
+#include "gemm_simt.cuh"
+extern "C" __global__ void KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  kcg::naive_gemm<KCG_T, KCG_ATRANS>(p);
+}
+#else
+#error "unknown KCG_VARIANT"
+#endif

@@ -1,0 +1,145 @@
+// Kernel-argument block and compile-time layout rules shared by the device
+// kernels and the host shim. Plain C++ (no torch, no CUDA runtime types beyond
+// CUtensorMap), so the host library and every JIT-compiled cubin agree on the
+// byte layout of one `__grid_constant__` parameter.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+// DATATYPE_* values of the tuning config. 2/4/8 are the reference's
+// EnumKernelDType byte-size codes (Runtime/python/kcg/Utils.py:198-203);
+// 62 is this library's bfloat16 (62 % 30 == 2 bytes keeps the reference's
+// sizeof() rule, Utils.py:219-221).
+#define KCG_DT_F16 2
+#define KCG_DT_F32 4
+#define KCG_DT_F64 8
+#define KCG_DT_BF16 62
+
+// KERNEL_VARIANT
+#define KCG_VARIANT_AUTO 0
+#define KCG_VARIANT_SIMT 1     // FFMA register-tiled kernel (fp32)
+#define KCG_VARIANT_TCGEN05 2  // TMA + tcgen05/TMEM kernel (bf16, fp16, fp32 as 3xTF32)
+#define KCG_VARIANT_TF32X1 3   // tcgen05 single-pass TF32 (fp32 in, reduced accuracy; comparison only)
+
+// Device status word values (status[0]); 0 = ok.
+#define KCG_ST_OK 0u
+#define KCG_ST_TIMEOUT_PRODUCER 1u
+#define KCG_ST_TIMEOUT_MMA 2u
+#define KCG_ST_TIMEOUT_EPILOGUE 3u
+#define KCG_ST_TIMEOUT_SPLITTER 4u
+#define KCG_ST_BAD_SHAPE 5u
+
+struct alignas(64) KcgGemmParams {
+  CUtensorMap tmA;  // tcgen05 variants: tiled map of A (or of A^T when IS_ATRANS=1)
+  CUtensorMap tmB;  // tiled map of B (K x N row-major)
+  CUtensorMap tmC;  // reserved for a TMA-store epilogue
+  const void* A;
+  const void* B;
+  void* C;
+  float* splitk_ws;             // [SPLITK][M][N] fp32 partials (split-K only)
+  unsigned int* tile_counters;  // one per output tile, zero between launches (split-K only)
+  unsigned int* status;         // 4 words: code, blockIdx.x, detail0, detail1
+  int M, N, K;
+  int lda, ldb, ldc;  // leading dimensions in elements (row-major storage)
+};
+
+namespace kcg {
+
+constexpr int kc_min(int a, int b) { return a < b ? a : b; }
+constexpr int kc_pow2_ceil(int v) {
+  int p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// Shared-memory / TMA layout of one pipeline stage of the tcgen05 kernels.
+// Host (tensor-map construction) and device (descriptors) both derive it from
+// the same five config values.
+struct TcLayout {
+  int eb;          // element bytes
+  int umma_k;      // K extent of one MMA instruction
+  int atom;        // elements per 128-byte swizzle row
+  // A operand
+  int a_box_inner, a_box_outer;  // TMA box in elements {contiguous, strided}
+  int a_boxes, a_box_bytes, a_bytes;
+  int a_tma_swizzle;   // CUtensorMapSwizzle value
+  int a_desc_swizzle;  // UMMA descriptor layout type
+  int a_lbo, a_sbo;
+  // B operand (always MN-major: K x N row-major)
+  int b_box_inner, b_box_outer;
+  int b_boxes, b_box_bytes, b_bytes;
+  int b_tma_swizzle, b_desc_swizzle;
+  int b_lbo, b_sbo;
+  int stage_hi_bytes;  // one copy of A+B
+};
+
+constexpr TcLayout make_tc_layout(int dtype, int BM, int BN, int BK, int atrans) {
+  TcLayout L{};
+  L.eb = (dtype == KCG_DT_F32) ? 4 : 2;
+  L.umma_k = 32 / L.eb;
+  L.atom = 128 / L.eb;
+  // MN-major operands: boxes of {atom elements along MN, BK rows of K}.
+  // 16-bit: 128B swizzle of 16B units, 8-row repeat; 32-bit: 128B swizzle of
+  // 32B units, 4-row repeat (the only MN-major form kind::tf32 accepts).
+  const int mn_tma = (L.eb == 4) ? 4 /*128B_ATOM_32B*/ : 3 /*128B*/;
+  const int mn_desc = (L.eb == 4) ? 1 : 2;
+  const int mn_sbo = (L.eb == 4) ? 512 : 1024;
+  if (atrans) {
+    L.a_box_inner = L.atom;
+    L.a_box_outer = BK;
+    L.a_boxes = BM / L.atom;
+    L.a_box_bytes = BK * 128;
+    L.a_tma_swizzle = mn_tma;
+    L.a_desc_swizzle = mn_desc;
+    L.a_lbo = BK * 128;
+    L.a_sbo = mn_sbo;
+  } else {
+    const int swb = kc_min(128, BK * L.eb);  // swizzle span = bytes of one K row
+    L.a_box_inner = swb / L.eb;
+    L.a_box_outer = BM;
+    L.a_boxes = (BK * L.eb) / swb;
+    L.a_box_bytes = BM * swb;
+    L.a_tma_swizzle = (swb == 128) ? 3 : (swb == 64) ? 2 : 1;
+    L.a_desc_swizzle = (swb == 128) ? 2 : (swb == 64) ? 4 : 6;
+    L.a_lbo = 16;
+    L.a_sbo = 8 * swb;
+  }
+  L.a_bytes = BM * BK * L.eb;
+  L.b_box_inner = L.atom;
+  L.b_box_outer = BK;
+  L.b_boxes = BN / L.atom;
+  L.b_box_bytes = BK * 128;
+  L.b_bytes = BN * BK * L.eb;
+  L.b_tma_swizzle = mn_tma;
+  L.b_desc_swizzle = mn_desc;
+  L.b_lbo = BK * 128;
+  L.b_sbo = mn_sbo;
+  L.stage_hi_bytes = L.a_bytes + L.b_bytes;
+  return L;
+}
+
+// Shape rules of the tcgen05 kernels; returns 0 when the config is buildable.
+constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int x3) {
+  const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
+  if (!(dtype == KCG_DT_F32 || dtype == KCG_DT_F16 || dtype == KCG_DT_BF16)) return 1;
+  if (!(BM == 128 || BM == 256)) return 2;
+  if (BN < 128 / eb || BN > 256 || (BN % (128 / eb)) != 0 || (BN % 16) != 0) return 3;
+  if ((BM / 128) * BN > 512) return 4;
+  const int rowb = BK * eb;
+  if (!(rowb == 32 || rowb == 64 || (rowb % 128) == 0) || rowb > 512) return 5;
+  if ((BK % (32 / eb)) != 0 || (BK % 8) != 0) return 6;
+  if (eb == 2 && (BK % 16) != 0) return 6;
+  if (stages < 2 || stages > 12) return 7;
+  const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
+  if (stage * stages + 2048 > 227 * 1024) return 8;
+  return 0;
+}
+
+constexpr int tc_smem_bytes(int dtype, int BM, int BN, int BK, int stages, int x3) {
+  const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
+  const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
+  // +1024 alignment slack, +1024 barriers / TMEM holder / flags
+  return stage * stages + 2048;
+}
+
+}  // namespace kcg

@@ -1,0 +1,442 @@
+// Persistent, warp-specialised GEMM for sm_100a: C[M,N] = A[M,K] * B[K,N].
+//
+//   warp 0        TMA producer: fills a kStages-deep ring of {A tile, B tile}
+//                 in shared memory (cp.async.bulk.tensor, no multicast), one
+//                 mbarrier pair (full/empty) per stage.
+//   warp 1        MMA issuer: one elected thread issues tcgen05.mma from the
+//                 shared-memory descriptors into fp32 accumulators in TMEM and
+//                 releases stages / publishes accumulators with tcgen05.commit.
+//                 The warp also owns the TMEM allocation.
+//   warps 2..5    epilogue: tcgen05.ld the accumulator (one TMEM lane = one C
+//                 row per thread), convert, vectorised global stores. With two
+//                 accumulator buffers it overlaps the next tile's main loop.
+//   warps 6..9    (fp32 3xTF32 only) splitter: rewrites each landed stage as
+//                 hi = tf32(x) in place and lo = tf32(x - hi) in a twin buffer,
+//                 so the MMA warp can issue lo*hi + hi*lo + hi*hi.
+//
+// Config keys -> template parameters (reference meaning: Optimizer.cc:285-469):
+//   BLOCK_SIZE_M/N/K -> kBM (128 | 256 = two M=128 accumulators), kBN, kBK
+//   SHARED_PREFETCH / NUM_STAGES -> kStages;  LOCAL_SPLIT_U -> kSplitK (K split
+//   across CTAs, fp32 partials in a workspace, last arriver reduces in split
+//   order so the result is deterministic);  BLOCK_MAPPING -> kGroup (rows of
+//   tiles per raster group);  IS_ATRANS -> A stored K x M.
+//
+// Every mbarrier wait is bounded; on a timeout the role records a status code,
+// raises the CTA-wide abort flag and all roles fall through to the common exit
+// where TMEM is freed.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_params.h"
+#include "ptx_sm100.cuh"
+
+namespace kcg {
+
+template <int kDType, int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK,
+          int kGroup, int kX3>
+struct TcGemm {
+  static_assert(tc_config_error(kDType, kBM, kBN, kBK, kStages, kX3) == 0,
+                "config not buildable by the tcgen05 kernel");
+  static constexpr TcLayout L = make_tc_layout(kDType, kBM, kBN, kBK, kATrans);
+  static constexpr int EB = L.eb;
+  static constexpr bool kTf32 = (EB == 4);
+  static constexpr bool kSplit3 = kTf32 && (kX3 != 0);
+  static constexpr int UMMA_K = L.umma_k;
+  static constexpr int MT = kBM / 128;
+  static constexpr int ACC_COLS = MT * kBN;
+  static constexpr int NACC = (2 * ACC_COLS <= 512) ? 2 : 1;
+  static constexpr int TMEM_COLS = kc_pow2_ceil(NACC * ACC_COLS);
+  static constexpr int STAGE_HI = L.stage_hi_bytes;
+  static constexpr int STAGE_BYTES = kSplit3 ? 2 * STAGE_HI : STAGE_HI;
+  static constexpr int KSTEPS = kBK / UMMA_K;
+  static constexpr int NUM_EPI_THREADS = 128;
+  static constexpr int NUM_SPLIT_THREADS = 128;
+  static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS + (kSplit3 ? NUM_SPLIT_THREADS : 0);
+  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, kBM, kBN, kBK, kStages, kX3);
+  static constexpr uint32_t FMT = (kDType == KCG_DT_F32)    ? FMT_TF32
+                                  : (kDType == KCG_DT_BF16) ? FMT_BF16
+                                                            : FMT_F16;
+  static constexpr uint32_t IDESC = make_instr_desc(FMT, kATrans ? 1u : 0u, 1u, 128u, kBN);
+
+  struct Barriers {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t split_full[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+    uint32_t last_flag;
+  };
+  static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
+
+  struct Unit {
+    int m0, n0, tile, split, kb0, kbn;
+  };
+
+  // Work unit u -> output tile (grouped raster, matmul.cpp:79-86 semantics:
+  // groups of kGroup tile-rows walk N first so a wave shares A and B in L2)
+  // and K range of this split.
+  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb) {
+    Unit w;
+    w.tile = u / kSplitK;
+    w.split = u - w.tile * kSplitK;
+    int mb, nb;
+    if constexpr (kGroup > 1) {
+      const int per_group = kGroup * tiles_n;
+      const int g = w.tile / per_group;
+      const int first_m = g * kGroup;
+      const int gsz = (tiles_m - first_m < kGroup) ? (tiles_m - first_m) : kGroup;
+      const int r = w.tile - g * per_group;
+      mb = first_m + (r % gsz);
+      nb = r / gsz;
+    } else {
+      mb = w.tile / tiles_n;
+      nb = w.tile - mb * tiles_n;
+    }
+    w.m0 = mb * kBM;
+    w.n0 = nb * kBN;
+    const int per = (num_kb + kSplitK - 1) / kSplitK;
+    w.kb0 = w.split * per;
+    int kb1 = w.kb0 + per;
+    if (kb1 > num_kb) kb1 = num_kb;
+    w.kbn = (kb1 > w.kb0) ? (kb1 - w.kb0) : 0;
+    return w;
+  }
+
+  __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
+                                                uint32_t code, uint32_t d0, uint32_t d1) {
+    bars->abort_flag = 1u;
+    if (atomicCAS(p.status, 0u, code) == 0u) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = d0;
+      p.status[3] = d1;
+    }
+  }
+
+  template <typename OutT>
+  __device__ static __forceinline__ void store_chunk(OutT* dst, const float (&v)[32]) {
+    if constexpr (sizeof(OutT) == 4) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = v[8 * i + 2 * j], hi = v[8 * i + 2 * j + 1];
+          if constexpr (kDType == KCG_DT_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(lo, hi);
+            w[j] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  }
+
+  __device__ static void run(const KcgGemmParams& p) {
+    using OutT = typename std::conditional<kTf32, float,
+                 typename std::conditional<kDType == KCG_DT_BF16, __nv_bfloat16, __half>::type>::type;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // Tiles need 1024-byte alignment (128B swizzle repeat); the launch asks for 1 KiB of slack.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tiles_n = (p.N + kBN - 1) / kBN;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+    const int num_units = tiles_m * tiles_n * kSplitK;
+
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(&bars->full[s], 1);
+        mbar_init(&bars->empty[s], 1);
+        mbar_init(&bars->split_full[s], NUM_SPLIT_THREADS);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&bars->tmem_full[a], 1);
+        mbar_init(&bars->tmem_empty[a], NUM_EPI_THREADS);
+      }
+      bars->abort_flag = 0u;
+      bars->last_flag = 0u;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------ producer
+      if (lane == 0) {
+        tma_prefetch_desc(&p.tmA);
+        tma_prefetch_desc(&p.tmB);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_PRODUCER, it, s);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = smem + s * STAGE_BYTES;
+            uint8_t* sb = sa + L.a_bytes;
+            mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
+            const int k0 = (w.kb0 + kb) * kBK;
+#pragma unroll
+            for (int j = 0; j < L.a_boxes; ++j) {
+              if constexpr (kATrans) {
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.m0 + j * L.atom, k0);
+              } else {
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s],
+                            k0 + j * L.a_box_inner, w.m0);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < L.b_boxes; ++j) {
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, k0);
+            }
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        uint32_t it = 0, acc_it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++acc_it) {
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          const uint32_t ab = acc_it % NACC;
+          const uint32_t aph = (acc_it / NACC) & 1u;
+          if (!mbar_wait(&bars->tmem_empty[ab], aph ^ 1u, &bars->abort_flag)) {
+            report(p, bars, KCG_ST_TIMEOUT_MMA, 0x100u + ab, acc_it);
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
+          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            uint64_t* ready = kSplit3 ? &bars->split_full[s] : &bars->full[s];
+            if (!mbar_wait(ready, ph, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_MMA, it, s);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint32_t sb = sa + L.a_bytes;
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+              uint32_t a_off, b_off;
+              if constexpr (kATrans) {
+                a_off = ks * UMMA_K * 128;
+              } else {
+                constexpr int swb = (kBK * EB < 128) ? kBK * EB : 128;
+                a_off = ((ks * 32) / swb) * L.a_box_bytes + ((ks * 32) % swb);
+              }
+              b_off = ks * UMMA_K * 128;
+              const uint32_t acc_flag = (kb > 0 || ks > 0) ? 1u : 0u;
+#pragma unroll
+              for (int t = 0; t < MT; ++t) {
+                // second accumulator: A rows 128..255 of the tile
+                const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
+                                             : t * 128 * (L.a_box_bytes / kBM);
+                const uint64_t bdesc = make_smem_desc(sb + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
+                const uint64_t adesc =
+                    make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
+                const uint32_t d = tmem_acc + t * kBN;
+                if constexpr (kSplit3) {
+                  const uint64_t adesc_lo = make_smem_desc(sa + STAGE_HI + a_t + a_off, L.a_lbo,
+                                                           L.a_sbo, L.a_desc_swizzle);
+                  const uint64_t bdesc_lo = make_smem_desc(sb + STAGE_HI + b_off, L.b_lbo, L.b_sbo,
+                                                           L.b_desc_swizzle);
+                  umma_ss<true>(d, adesc_lo, bdesc, IDESC, acc_flag);
+                  umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
+                  umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
+                } else {
+                  umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
+                }
+              }
+            }
+            umma_commit(&bars->empty[s]);  // stage reusable once these MMAs retire
+          }
+          if (ok) umma_commit(&bars->tmem_full[ab]);
+        }
+      }
+    } else if (warp < 6) {
+      // ------------------------------------------------------------ epilogue
+      const int q = warp & 3;  // TMEM lane quarter this warp may read
+      const int epi_tid = (warp - 2) * 32 + lane;
+      const int row_in_acc = q * 32 + lane;
+      uint32_t acc_it = 0;
+      OutT* Cout = reinterpret_cast<OutT*>(p.C);
+      for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++acc_it) {
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        const uint32_t ab = acc_it % NACC;
+        const uint32_t aph = (acc_it / NACC) & 1u;
+        // The warp must leave the wait as one: tcgen05.ld below is warp-collective.
+        const bool got = mbar_wait(&bars->tmem_full[ab], aph, &bars->abort_flag);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, acc_it, ab);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+        for (int t = 0; t < MT; ++t) {
+          const int row = w.m0 + t * 128 + row_in_acc;
+#pragma unroll 1
+          for (int c = 0; c < kBN / 32; ++c) {
+            float v[32];
+            if (w.kbn > 0) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tmem_acc + t * kBN + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            }
+            const int col = w.n0 + c * 32;
+            if (row < p.M && col < p.N) {
+              if constexpr (kSplitK > 1) {
+                float* dst = p.splitk_ws + (static_cast<size_t>(w.split) * p.M + row) * p.N + col;
+                store_chunk<float>(dst, v);
+              } else {
+                store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&bars->tmem_empty[ab]);
+
+        if constexpr (kSplitK > 1) {
+          // Publish this split's partial tile; the last split to arrive sums all
+          // partials in split order (bitwise reproducible) and writes C.
+          __threadfence();
+          named_bar_sync(1, NUM_EPI_THREADS);
+          if (epi_tid == 0) {
+            const unsigned int old = atomicAdd(&p.tile_counters[w.tile], 1u);
+            bars->last_flag = (old == static_cast<unsigned int>(kSplitK - 1)) ? 1u : 0u;
+            if (old == static_cast<unsigned int>(kSplitK - 1)) p.tile_counters[w.tile] = 0u;
+          }
+          named_bar_sync(1, NUM_EPI_THREADS);
+          const bool last = bars->last_flag != 0u;
+          if (last) {
+            __threadfence();
+            for (int t = 0; t < MT; ++t) {
+              const int row = w.m0 + t * 128 + row_in_acc;
+              if (row >= p.M) continue;
+              for (int c = 0; c < kBN / 32; ++c) {
+                const int col = w.n0 + c * 32;
+                if (col >= p.N) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                for (int s = 0; s < kSplitK; ++s) {
+                  const float4* src = reinterpret_cast<const float4*>(
+                      p.splitk_ws + (static_cast<size_t>(s) * p.M + row) * p.N + col);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 x = __ldcg(src + i);
+                    v[4 * i] += x.x;
+                    v[4 * i + 1] += x.y;
+                    v[4 * i + 2] += x.z;
+                    v[4 * i + 3] += x.w;
+                  }
+                }
+                store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
+              }
+            }
+          }
+          named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit
+        }
+      }
+    } else {
+      // ------------------------------------------- 3xTF32 splitter (warps 6..9)
+      if constexpr (kSplit3) {
+        const int stid = threadIdx.x - 192;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
+              if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_SPLITTER, it, s);
+              ok = false;
+              break;
+            }
+            float4* hi = reinterpret_cast<float4*>(smem + s * STAGE_BYTES);
+            float4* lo = reinterpret_cast<float4*>(smem + s * STAGE_BYTES + STAGE_HI);
+#pragma unroll 4
+            for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
+              const float4 x = hi[i];
+              float4 h, l;
+              split_tf32(x.x, h.x, l.x);
+              split_tf32(x.y, h.y, l.y);
+              split_tf32(x.z, h.z, l.z);
+              split_tf32(x.w, h.w, l.w);
+              hi[i] = h;
+              lo[i] = l;
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(&bars->split_full[s]);
+          }
+        }
+      }
+    }
+
+    // ------------------------------------------------------------ common exit
+    if (bars->abort_flag != 0u) {
+      // Give copies / MMAs still in flight time to land before shared memory
+      // and TMEM are released.
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      __syncwarp();
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+  }
+
+  // x = hi + lo with hi, lo both exactly representable in TF32 (round to
+  // nearest); hi*hi + hi*lo + lo*hi then carries ~21 mantissa bits.
+  __device__ static __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    const float r = x - hi;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
+    lo = __uint_as_float(l);
+  }
+};
+
+}  // namespace kcg

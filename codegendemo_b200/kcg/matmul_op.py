@@ -1,0 +1,61 @@
+"""Convenience wrappers over the reference-style flow
+``KernelArgMatmul -> KCGCompiler.compileKernel -> UserInputs -> CompiledKernelFactory.getKernel``
+(the sequence of SerialCompileTask._task_compile_kernel, Runtime/python/kcg/KCGTask.py:275-297)."""
+from codegendemo_b200.kcg.CompiledKernelFactory import CompiledKernelFactory, EnumOperator, UserInputs
+from codegendemo_b200.kcg.KCGCompiler import KCGCompiler
+from codegendemo_b200.kcg.Operators.matmul import KernelArgMatmul
+from codegendemo_b200.kcg.Utils import EnumKernelDType, FromTorchType
+
+
+def default_config(M: int, N: int, K: int, dtype: EnumKernelDType, **keys) -> KernelArgMatmul:
+    """A tensor-core config for the NN case (A is M x K row-major) with sensible B200 defaults;
+    any tuning key can be overridden by keyword (attribute names of KernelArgMatmul)."""
+    kpm = KernelArgMatmul(M, N, K, dtype, dtype, dtype)
+    eb = int(dtype) % 30
+    kpm.BLOCK_SIZE_M = 128
+    kpm.BLOCK_SIZE_N = 256 if N % 256 == 0 else 128 if N % 128 == 0 else 64
+    kpm.BLOCK_SIZE_K = 128 // eb
+    kpm.THREAD_SIZE_M, kpm.THREAD_SIZE_N = 8, kpm.BLOCK_SIZE_N // 16
+    kpm.WARP_SIZE = 32
+    kpm.WARP_LAYOUT_M, kpm.WARP_LAYOUT_N = 4, 8
+    kpm.BLOCK_LAYOUT_M, kpm.BLOCK_LAYOUT_N = 4, 2
+    kpm.isATranspose = 0
+    kpm.LOCAL_SPLIT_U = 1
+    kpm.BLOCK_MAPPING = 8
+    kpm.SHARED_PREFETCH = 1
+    kpm.REG_PREFETCH = 1
+    kpm.GLOB_LOAD_WIDTH_A = kpm.GLOB_LOAD_WIDTH_B = kpm.GLOB_STORE_WIDTH = 4
+    kpm.WARP_SCATTER_WIDTH_A = kpm.THREAD_SCATTER_WIDTH_A = kpm.THREAD_SIZE_M
+    kpm.WARP_SCATTER_WIDTH_B = kpm.THREAD_SCATTER_WIDTH_B = kpm.THREAD_SIZE_N
+    kpm.UNROLL_NUM = 4
+    for k, v in keys.items():
+        if not hasattr(kpm, k):
+            raise KeyError(f"unknown tuning key {k}")
+        setattr(kpm, k, v)
+    return kpm
+
+
+def build_kernel(kpm: KernelArgMatmul, deviceId: int = 0):
+    """Compile (or fetch from the cubin cache) and wrap one config; returns (UserInputs, CompiledKernel)."""
+    kpm.check()
+    compiler = KCGCompiler()
+    path, name, gx, gy, gz, bx, by, bz = compiler.compileKernel(kpm)[0]
+    inConfig = UserInputs(path, name, kpm, compiler.lastInfo)
+    inConfig.m_gridDims = [gx, gy, gz]
+    inConfig.m_blockDims = [bx, by, bz]
+    inConfig.operatorKind = EnumOperator.Matmul
+    return inConfig, CompiledKernelFactory.getKernel(inConfig, deviceId)
+
+
+def matmul(a, b, c=None, **keys):
+    """``c = a @ b`` on the current CUDA device through a default (or keyword-tuned) config."""
+    import torch
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2 and a.is_contiguous() and b.is_contiguous()
+    if c is None:
+        c = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    kpm = default_config(M, N, K, FromTorchType(a.dtype), **keys)
+    _, kern = build_kernel(kpm, a.device.index or 0)
+    kern.run(a, b, c)
+    return c

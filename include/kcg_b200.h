@@ -1,0 +1,153 @@
+/* C ABI of libkcg_b200.so: compile, load and launch the B200 (sm_100a) GEMM
+ * kernels behind the operator API of Xiebaokang/CodeGenDemo ("KCG").
+ *
+ * Every function returns 0 on success. A positive value is a CUresult from the
+ * CUDA driver, a negative value one of the KCG_E_* codes below; in both cases
+ * kcg_last_error() returns a thread-local message that starts with
+ * "KCG Error[CUDA]: Code: <n>, Messsage: " — the prefix (typo included) of the
+ * reference's loader errors (Runtime/python/kcg/loaderCCode/hip.c:8-21).
+ *
+ * The library links nothing from the CUDA driver at load time: libcuda.so.1 is
+ * opened on the first call that needs a GPU, so the library loads (and the
+ * compile entry works) on a machine without one. There is no CPU fallback: a
+ * load/launch call without a usable driver fails with KCG_E_NO_DRIVER.
+ */
+#ifndef KCG_B200_H_
+#define KCG_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KCG_NUM_CFG_KEYS 31
+
+/* Positional order of the 31 tuning-config integers. It is the argument order of
+ * the reference's compile_kernel_matmul (src/main.cc:64-102, mirrored by
+ * Runtime/python/kcg/KCGCompiler.py:14-44). */
+enum kcg_cfg_index {
+  KCG_CFG_BLOCK_SIZE_M = 0, KCG_CFG_BLOCK_SIZE_N, KCG_CFG_BLOCK_SIZE_K,
+  KCG_CFG_THREAD_SIZE_M, KCG_CFG_THREAD_SIZE_N, KCG_CFG_WARP_SIZE,
+  KCG_CFG_BLOCK_LAYOUT_M, KCG_CFG_BLOCK_LAYOUT_N, KCG_CFG_WARP_LAYOUT_M, KCG_CFG_WARP_LAYOUT_N,
+  KCG_CFG_GLOB_LOAD_WIDTH_A, KCG_CFG_GLOB_LOAD_WIDTH_B,
+  KCG_CFG_WARP_SCATTER_WIDTH_A, KCG_CFG_WARP_SCATTER_WIDTH_B,
+  KCG_CFG_THREAD_SCATTER_WIDTH_A, KCG_CFG_THREAD_SCATTER_WIDTH_B,
+  KCG_CFG_LOCAL_SPLIT_U, KCG_CFG_BLOCK_MAPPING, KCG_CFG_GLOB_STORE_WIDTH,
+  KCG_CFG_UNROLL_NUM, KCG_CFG_REG_PREFETCH, KCG_CFG_SHARED_PREFETCH,
+  KCG_CFG_LOAD_CONTINUOUS, KCG_CFG_REDUCE_C_CONTINUOUS,
+  KCG_CFG_DATATYPE_A, KCG_CFG_DATATYPE_B, KCG_CFG_DATATYPE_C,
+  KCG_CFG_M_SIZE, KCG_CFG_N_SIZE, KCG_CFG_K_SIZE, KCG_CFG_IS_ATRANS
+};
+
+/* DATATYPE_* values: 2 / 4 are the reference's float16 / float32 codes
+ * (Runtime/python/kcg/Utils.py:198-203); 62 is bfloat16 (new; 62 % 30 == 2 bytes). */
+#define KCG_DTYPE_FLOAT16 2
+#define KCG_DTYPE_FLOAT32 4
+#define KCG_DTYPE_BFLOAT16 62
+
+/* Kernel families. AUTO picks TCGEN05 when the tile shape is one the tensor-core
+ * kernel can build and SIMT otherwise. */
+#define KCG_KERNEL_AUTO 0
+#define KCG_KERNEL_SIMT 1     /* FFMA register-tiled kernel */
+#define KCG_KERNEL_TCGEN05 2  /* TMA + tcgen05/TMEM; fp32 runs as 3xTF32 */
+#define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
+#define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
+
+/* Error codes (negative; positive values are CUresult). */
+#define KCG_E_BAD_CONFIG (-1)      /* config fails the reference's check() rules or the kernel's */
+#define KCG_E_COMPILE (-2)         /* nvcc failed; message carries the tail of its log */
+#define KCG_E_NO_DRIVER (-3)       /* libcuda.so.1 / a GPU is not available */
+#define KCG_E_IO (-4)              /* cubin / cache file could not be read or written */
+#define KCG_E_DEVICE_TIMEOUT (-5)  /* a bounded wait inside the kernel ran out (status word) */
+#define KCG_E_BAD_ARG (-6)
+#define KCG_E_TOO_LARGE (-7)
+
+typedef struct kcg_kernel_info {
+  char path[1024];    /* cubin on disk (reference: hsaco path, src/main.cc:343-353) */
+  char name[512];     /* kernel symbol, same naming scheme as src/main.cc:119-145 */
+  int32_t grid[3];    /* launch dims (reference: func.grid.dim / func.block.dim attrs) */
+  int32_t block[3];
+  int32_t cluster[3];
+  int32_t smem_bytes; /* dynamic shared memory the launch must request */
+  int32_t kernel;     /* resolved KCG_KERNEL_* */
+  int32_t dtype;      /* DATATYPE_A */
+  int32_t bm, bn, bk; /* CTA tile */
+  int32_t stages;     /* shared-memory pipeline depth (tcgen05) */
+  int32_t splitk;     /* LOCAL_SPLIT_U */
+  int32_t group;      /* BLOCK_MAPPING */
+  int32_t atrans;     /* IS_ATRANS */
+  int32_t m, n, k;
+  int32_t reserved[8];
+} kcg_kernel_info;
+
+typedef struct kcg_compile_opts {
+  int32_t kernel;      /* KCG_KERNEL_*; 0 = auto */
+  int32_t num_stages;  /* 0 = derive from SHARED_PREFETCH (0 -> 2 stages, 1 -> as many as fit, max 6) */
+  int32_t num_sms;     /* persistent grid size cap; 0 = 148 (B200) */
+  int32_t force;       /* 1 = recompile even when the cubin is cached */
+} kcg_compile_opts;
+
+typedef struct kcg_device_props {
+  int32_t max_shared_mem;        /* opt-in maximum per block, bytes */
+  int32_t multiprocessor_count;
+  int32_t sm_clock_rate;         /* kHz */
+  int32_t mem_clock_rate;        /* kHz */
+  int32_t mem_bus_width;         /* bits */
+  int32_t l2_cache_bytes;
+  int32_t cc_major, cc_minor;
+} kcg_device_props;
+
+/* ---- compile boundary ---------------------------------------------------------
+ * Replaces compile_kernel_matmul (src/main.cc:315-357): validates the 31-key config
+ * (same rules as KernelArgMatmul.check, Runtime/python/kcg/Operators/matmul.py:180-194),
+ * names the kernel, runs `nvcc -cubin -gencode arch=compute_100a,code=sm_100a` on the
+ * kernel template with the config as macros (or reuses the cached cubin of that
+ * name) and reports path, name and launch dims. Needs no GPU. Reentrant. */
+int kcg_compile_matmul(const int32_t cfg[KCG_NUM_CFG_KEYS], kcg_kernel_info* out);
+int kcg_compile_matmul_ex(const int32_t cfg[KCG_NUM_CFG_KEYS], const kcg_compile_opts* opts,
+                          kcg_kernel_info* out);
+/* Writes the kernel symbol the config compiles to (no compilation). */
+int kcg_kernel_name(const int32_t cfg[KCG_NUM_CFG_KEYS], const kcg_compile_opts* opts, char* buf,
+                    int buf_len);
+/* Directory cubins are cached in ($KCG_CACHE_DIR, else <library dir>/_cache). */
+const char* kcg_cache_dir(void);
+
+/* ---- load boundary --------------------------------------------------------------
+ * Replaces load_binary / get_device_properties of the reference's loader extension
+ * (Runtime/python/kcg/loaderCCode/hip.c:60-133 and :44-58). `shared` above 48 KiB
+ * opts the function in to that much dynamic shared memory. */
+int kcg_load_binary(const char* name, const char* path, int shared, int device, uint64_t* module,
+                    uint64_t* function, int* n_regs, int* n_spills);
+int kcg_unload(uint64_t module);
+int kcg_device_properties(int device, kcg_device_props* out);
+
+/* ---- launch boundary ------------------------------------------------------------
+ * Replaces the generated launcher's launch() (Runtime/python/kcg/HIPLauncher.py:189-238):
+ * asynchronous on `stream` (a CUstream as integer; 0 = default stream), pointers are
+ * device addresses borrowed for the call. Tensor maps for TMA are built (and cached per
+ * pointer/shape) inside. Split-K kernels use a per-device workspace the library
+ * allocates on first use. C is overwritten (alpha = 1, beta = 0). */
+int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                    uint64_t A, uint64_t B, uint64_t C);
+/* Reads (and clears) the device status word written by bounded waits; returns
+ * KCG_E_DEVICE_TIMEOUT if a kernel gave up since the last check. Synchronises `stream`. */
+int kcg_check_status(int device, uint64_t stream);
+
+/* Whole-operator call on HOST buffers: copies A and B to the device (async from the
+ * caller's memory, pinned for full speed), runs the kernel and copies C back, all on
+ * `stream`, then synchronises. Device buffers are owned and reused by the library. */
+int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                    const void* hostA, const void* hostB, void* hostC);
+
+/* Number of kernel launches issued through this library since load (all threads). */
+uint64_t kcg_launch_count(void);
+/* Frees workspaces, device buffers and cached tensor maps of every device. */
+int kcg_shutdown(void);
+const char* kcg_last_error(void);
+const char* kcg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KCG_B200_H_ */
