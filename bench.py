@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (all N): the M-sharded bf16 GEMM M=32768, N=K=8192 (fp32 accumulate, bf16 out, inputs
+normal(0,1)/sqrt(K), seed 0): rank r of N computes rows [r*M/N, (r+1)*M/N) against a replicated B;
+no data-path collective. Total work is fixed, so scaling is "strong"; at N=1 one GPU computes the whole
+product. A "step" is one pass of the rank's slab through the tcgen05 kernel. At N=1 the line also
+carries short measurements of the other single-GPU configs (fp32 4096^3 as 3xTF32 and as FFMA SIMT,
+bf16 8192^3) under "other_workloads".
+
+Prints ONE JSON line on rank 0 (metric: GEMM TFLOP/s, device-timed with CUDA events, max over ranks).
+``--impl reference`` times the reference's CPU path for the same metric: ``torch.matmul`` on host
+tensors (the reference's own correctness oracle, Runtime/python/kcg/KCGTask.py:94) with all host
+threads, on a bounded row slab of the same workload.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOTAL, N_SIZE, K_SIZE = 32768, 8192, 8192
+METRIC = "GEMM TFLOP/s (device-timed) bf16 32768x8192x8192 M-sharded, fp32 accumulate"
+UNIT = "TFLOP/s"
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def build_bf16_kernel(m_rows: int, device: int):
+    from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
+    from codegendemo_b200.kcg.Utils import EnumKernelDType as E
+    kpm = default_config(m_rows, N_SIZE, K_SIZE, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
+                         NUM_STAGES=3)
+    return kpm, build_kernel(kpm, device)
+
+
+def time_kernel(kern, a, b, c, steps, warmup):
+    """Per-launch device times (ms) from CUDA events on the launching stream."""
+    import torch
+    for _ in range(warmup):
+        kern.run(a, b, c)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s, e in evs:
+        s.record()
+        kern.run(a, b, c)
+        e.record()
+    torch.cuda.synchronize()
+    return [s.elapsed_time(e) for s, e in evs]
+
+
+def other_workloads(device: int):
+    """Short device-timed figures for the remaining single-GPU configs (inputs > L2 or noted)."""
+    import torch
+    from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
+    from codegendemo_b200.kcg.Utils import EnumKernelDType as E
+    out = []
+    simt = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
+                THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
+                WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
+    cases = [
+        ("fp32 4096^3 3xTF32 tcgen05", 4096, 4096, 4096, E.float32, torch.float32, dict(BLOCK_SIZE_N=128), "f32(3xtf32)"),
+        ("fp32 4096^3 FFMA SIMT", 4096, 4096, 4096, E.float32, torch.float32, simt, "f32"),
+        ("bf16 8192^3 tcgen05", 8192, 8192, 8192, E.bfloat16, torch.bfloat16,
+         dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3), "bf16"),
+    ]
+    for tag, m, n, k, edt, tdt, keys, dt in cases:
+        try:
+            kpm = default_config(m, n, k, edt, **keys)
+            _, kern = build_kernel(kpm, device)
+            g = torch.Generator(device=f"cuda:{device}").manual_seed(0)
+            a = (torch.randn(m, k, generator=g, device=f"cuda:{device}") / math.sqrt(k)).to(tdt)
+            b = (torch.randn(k, n, generator=g, device=f"cuda:{device}") / math.sqrt(k)).to(tdt)
+            c = torch.empty(m, n, dtype=tdt, device=f"cuda:{device}")
+            ts = time_kernel(kern, a, b, c, steps=10, warmup=3)
+            kern.checkStatus()
+            ts.sort()
+            med = ts[len(ts) // 2]
+            out.append({"workload": tag, "dtype": dt, "ms": round(med, 4),
+                        "tflops": round(2.0 * m * n * k / (med * 1e9), 1)})
+            del a, b, c
+        except Exception as e:  # a secondary figure must not lose the headline line
+            out.append({"workload": tag, "error": str(e)[:200]})
+    return out
+
+
+def cpu_sample(rows: int, threads: int, repeats: int = 1):
+    """torch.matmul on host tensors for a `rows`-row slab of the workload (bf16 inputs up-cast to
+    fp32, as the oracle computes); returns (seconds per pass, TFLOP/s)."""
+    import torch
+    from oracle import oracle
+    torch.set_num_threads(threads)
+    A, B = oracle.make_inputs(rows, N_SIZE, K_SIZE, torch.bfloat16, dist="normal", seed=0)
+    Af, Bf = A.float(), B.float()
+    torch.matmul(Af[:64], Bf)  # warm the BLAS threads
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        torch.matmul(Af, Bf)
+        best = min(best, time.perf_counter() - t0)
+    return best, 2.0 * rows * N_SIZE * K_SIZE / best / 1e12
+
+
+def pick_cpu_rows(threads: int, target_s: float):
+    """Row-slab size whose host GEMM takes about `target_s` seconds (probe with 128 rows first)."""
+    t, _ = cpu_sample(128, threads)
+    rows = int(128 * target_s / max(t, 1e-6))
+    rows = max(128, min(M_TOTAL, (rows // 128) * 128))
+    return rows
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    rows = pick_cpu_rows(threads, target_s=max(1.0, 20.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_sample(rows, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_sample(rows, threads)
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = 2.0 * rows * N_SIZE * K_SIZE / dt / 1e12
+    sample = f"{rows}-row slab of A ({rows}x{K_SIZE}) times full B per step, torch.matmul fp32 on host"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(val, 4), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": round(val, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(val, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(n_gpus):
+    return {"workload": f"bf16 NN GEMM M=32768 N=8192 K=8192 sharded by M over {n_gpus} GPU(s), B replicated, "
+                        "C sharded (BASELINE.json configs[4]; at 1 GPU the whole product)",
+            "m": M_TOTAL, "n": N_SIZE, "k": K_SIZE, "rows_per_gpu": M_TOTAL // n_gpus,
+            "tile": "256x256x64, 3 stages, tcgen05 cta_group::1, persistent 148 CTAs",
+            "l2": "inputs larger than L2 (A slab + B + C slab >= 256 MiB per GPU); no flush"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-extras", action="store_true", help="skip other_workloads and cpu_baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
+
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg import dist as kdist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the GEMM path has no CPU fallback")
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    n_gpus = world
+    row0, row1 = kdist.shard_rows(M_TOTAL, n_gpus, rank, 256)
+    rows = row1 - row0
+
+    # Seeded synthetic operands, generated on the device per slab (values: normal(0,1)/sqrt(K)).
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    a = (torch.randn(rows, K_SIZE, generator=g, device=dev) / math.sqrt(K_SIZE)).to(torch.bfloat16)
+    gb = torch.Generator(device=dev).manual_seed(99)
+    b = (torch.randn(K_SIZE, N_SIZE, generator=gb, device=dev) / math.sqrt(K_SIZE)).to(torch.bfloat16)
+    kdist.replicate_b(b, src=0)  # every rank holds the same B before timing
+    c = torch.empty(rows, N_SIZE, dtype=torch.bfloat16, device=dev)
+
+    kpm, (inc, kern) = build_bf16_kernel(rows, local_rank)
+    lib = _lib.get_lib()
+    for _ in range(args.warmup):
+        kern.run(a, b, c)
+    kern.checkStatus()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    launches0 = lib.kcg_launch_count()
+    barrier()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    evs[0].record()
+    for i in range(args.steps):
+        kern.run(a, b, c)
+        evs[i + 1].record()
+    barrier()
+    launches = lib.kcg_launch_count() - launches0
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_launch = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop() if rank == 0 else None
+    kern.checkStatus()
+    total_ms = kdist.max_over_ranks(total_ms, device=dev)
+    ms_per_step = total_ms / args.steps
+    flops_total = 2.0 * M_TOTAL * N_SIZE * K_SIZE
+    value = flops_total / (ms_per_step * 1e9)
+
+    # roofline of the one kernel in the step (this rank's launches)
+    peaks = measured_peaks()
+    avg_launch_ms = sum(per_launch) / len(per_launch)
+    achieved = 2.0 * rows * N_SIZE * K_SIZE / (avg_launch_ms * 1e9)
+    timed_s = total_ms / 1e3
+    peak_kind = "bf16_tflops_sustained" if timed_s > 1.0 else "bf16_tflops"
+    peak = peaks[peak_kind]
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        try:
+            with open(tpath) as f:
+                t = json.load(f)
+            # bytes per flop of the captured launch, scaled to this launch
+            traffic = t["dram_bytes_per_launch"] * (rows * N_SIZE * K_SIZE) / (t["m"] * t["n"] * t["k"])
+        except (OSError, ValueError, KeyError):
+            traffic = None
+    roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
+                "frac": round(achieved / peak, 4), "traffic": traffic,
+                "peak_source": f"{peaks['source']} {peak_kind} (cuBLAS bf16 8192^3)",
+                "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(avg_launch_ms, 4)}
+
+    # end to end through the C ABI with host buffers: H2D(A slab, B) + kernel + D2H(C slab) per step
+    hA = a.cpu().pin_memory()
+    hB = b.cpu().pin_memory()
+    hC = torch.empty(rows, N_SIZE, dtype=torch.bfloat16).pin_memory()
+    kern.runHost(hA, hB, hC)  # warm-up (allocates the library's device buffers)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.e2e_steps):
+        kern.runHost(hA, hB, hC)
+    e1.record()
+    barrier()
+    e2e_ms = kdist.max_over_ranks(e0.elapsed_time(e1) / args.e2e_steps, device=dev)
+    e2e = {"value": round(flops_total / (e2e_ms * 1e9), 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 3),
+           "h2d_bytes_per_step": int(hA.numel() * 2 + hB.numel() * 2) * n_gpus,
+           "d2h_bytes_per_step": int(hC.numel() * 2) * n_gpus, "steps": args.e2e_steps,
+           "api": "kcg_matmul_host (CompiledKernel.runHost), pinned host buffers"}
+    same = bool(torch.equal(hC, c.cpu()))
+
+    extras, cpu_base = None, None
+    if rank == 0 and n_gpus == 1 and not args.no_extras:
+        del hA, hB, hC
+        extras = other_workloads(local_rank)
+        threads = os.cpu_count() or 1
+        crow = pick_cpu_rows(threads, target_s=12.0)
+        sec, tf = cpu_sample(crow, threads)
+        cpu_base = {"value": round(tf, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                    "sample": f"{crow}-row slab ({crow}x{K_SIZE} times {K_SIZE}x{N_SIZE}), torch.matmul fp32 on host "
+                              f"(the reference's oracle call), {sec:.2f} s"}
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(n_gpus), "roofline": roofline, "cpu_baseline": cpu_base, "e2e": e2e,
+            "gpu_launches": int(launches), "clocks": clocks, "e2e_matches_device_result": same,
+            "other_workloads": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

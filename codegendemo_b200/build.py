@@ -1,0 +1,81 @@
+"""Builds ``libkcg_b200.so`` in-tree and (optionally) a family of cubins ahead of time.
+
+    python -m codegendemo_b200.build            # library + default cubins
+    python -m codegendemo_b200.build --lib-only
+
+The library's host code is plain C++ (g++) that binds the CUDA driver lazily; kernels are compiled by
+the library's own compile entry with ``nvcc -cubin -gencode arch=compute_100a,code=sm_100a``.
+"""
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _newer(target: str, sources) -> bool:
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_library(force: bool = False) -> str:
+    out = os.path.join(HERE, "libkcg_b200.so")
+    srcs = [os.path.join(HERE, "csrc", "kcg_shim.cpp")]
+    deps = srcs + [os.path.join(HERE, "csrc", "kernels", "gemm_params.h"),
+                   os.path.join(os.path.dirname(HERE), "include", "kcg_b200.h")]
+    extra = os.path.join(HERE, "csrc", "kcg_noalloc.cu")
+    if os.path.exists(extra):
+        deps.append(extra)
+    if not force and _newer(out, deps):
+        return out
+    if os.path.exists(extra):
+        nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+               "-Xcompiler", "-fPIC", "-cudart", "static", "-I" + os.path.join(HERE, "csrc", "kernels"),
+               "-o", out, *srcs, extra, "-ldl", "-lpthread"]
+    else:
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I" + os.path.join(CUDA_HOME, "include"),
+               "-o", out, *srcs, "-ldl", "-lpthread"]
+    subprocess.check_call(cmd)
+    return out
+
+
+def prebuilt_configs():
+    """Configs compiled ahead of time, so that a GPU box needs no nvcc for the smoke run and the bench."""
+    from codegendemo_b200.kcg.matmul_op import default_config
+    from codegendemo_b200.kcg.Utils import EnumKernelDType as E
+    big = dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3)
+    simt = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
+                THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
+                WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
+    cases = [
+        (1024, 1024, 1024, E.float32, dict(BLOCK_SIZE_N=128)),
+        (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128)),
+        (4096, 4096, 4096, E.float32, simt),
+        (8192, 8192, 8192, E.bfloat16, big),
+    ]
+    for g in (1, 2, 4, 8):
+        cases.append((32768 // g, 8192, 8192, E.bfloat16, big))
+    return [default_config(m, n, k, dt, **keys) for (m, n, k, dt, keys) in cases]
+
+
+def prebuild_kernels(verbose: bool = True) -> int:
+    from codegendemo_b200.kcg.KCGCompiler import KCGCompiler
+    n = 0
+    for kpm in prebuilt_configs():
+        kpm.check()
+        path = KCGCompiler().compileKernel(kpm)[0][0]
+        n += 1
+        if verbose:
+            print("cubin:", os.path.basename(path))
+    return n
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, os.path.dirname(HERE))
+    print(build_library(force="--force" in sys.argv))
+    if "--lib-only" not in sys.argv:
+        prebuild_kernels()

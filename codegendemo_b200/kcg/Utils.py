@@ -147,6 +147,7 @@ class PathManager:
     @staticmethod
     def set_project_dir(path: str) -> None:
         PathManager._root = str(path)
+        os.environ["KCG_WORK_DIR"] = str(path)  # spawned compile / perf processes resolve the same root
 
     @staticmethod
     def project_dir() -> str:

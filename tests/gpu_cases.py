@@ -1,0 +1,79 @@
+"""Config list shared by the GPU parity tests and the CPU-side 'everything cross-compiles' test."""
+from codegendemo_b200.kcg.matmul_op import default_config
+from codegendemo_b200.kcg.Utils import EnumKernelDType as E
+
+SIMT_64 = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=64, BLOCK_SIZE_N=64, BLOCK_SIZE_K=16, THREAD_SIZE_M=4, THREAD_SIZE_N=4,
+               BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8, WARP_SCATTER_WIDTH_A=2,
+               WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=1, THREAD_SCATTER_WIDTH_B=2, GLOB_LOAD_WIDTH_A=2,
+               GLOB_LOAD_WIDTH_B=2, GLOB_STORE_WIDTH=2)
+SIMT_128 = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
+                THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
+                WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
+# the reference's own test tile 64x48x32 / 4x6 / LSU2 (Runtime/python/kcg/test.py:20-57), on 32-wide warps
+SIMT_REF_TILE = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=64, BLOCK_SIZE_N=48, BLOCK_SIZE_K=32, THREAD_SIZE_M=4,
+                     THREAD_SIZE_N=6, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=1, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
+                     WARP_SCATTER_WIDTH_A=2, WARP_SCATTER_WIDTH_B=2, THREAD_SCATTER_WIDTH_A=2,
+                     THREAD_SCATTER_WIDTH_B=2, GLOB_LOAD_WIDTH_A=4, GLOB_LOAD_WIDTH_B=2, GLOB_STORE_WIDTH=2,
+                     LOCAL_SPLIT_U=2, BLOCK_MAPPING=8)
+
+# (id, M, N, K, dtype, input distribution, keys)
+SEEDED = [
+    ("c1_fp32_1024_tf32x3", 1024, 1024, 1024, E.float32, "uniform", dict(BLOCK_SIZE_N=128)),
+    ("c1_fp32_1024_tf32x3_atrans", 1024, 1024, 1024, E.float32, "uniform", dict(BLOCK_SIZE_N=128, isATranspose=1)),
+    ("c1_fp32_1024_simt", 1024, 1024, 1024, E.float32, "uniform", SIMT_128),
+    ("c1_fp32_1024_simt_atrans_lsu2", 1024, 1024, 1024, E.float32, "uniform",
+     dict(SIMT_64, LOCAL_SPLIT_U=2, isATranspose=1)),
+    ("c1_fp32_1024_simt_noprefetch", 1024, 1024, 1024, E.float32, "uniform",
+     dict(SIMT_64, SHARED_PREFETCH=0, REG_PREFETCH=0, BLOCK_MAPPING=0)),
+    ("ref_shape_1024x1056x1024_simt", 1024, 1056, 1024, E.float32, "uniform", dict(SIMT_REF_TILE, isATranspose=1)),
+    ("fp32_bn256_bk16", 512, 512, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=3)),
+    ("fp32_bk64_2stage", 256, 256, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=64, BLOCK_SIZE_K=64, NUM_STAGES=2)),
+    ("fp32_bm256", 512, 256, 256, E.float32, "uniform", dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=128, NUM_STAGES=2)),
+    ("fp32_splitk4", 128, 256, 4096, E.float32, "uniform", dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),
+    ("bf16_1024", 1024, 1024, 1024, E.bfloat16, "normal", dict()),
+    ("bf16_256x256x64_tile", 1024, 1024, 1024, E.bfloat16, "normal", dict(BLOCK_SIZE_M=256, NUM_STAGES=3)),
+    ("bf16_atrans", 512, 512, 512, E.bfloat16, "normal", dict(isATranspose=1)),
+    ("bf16_bk32_group0", 512, 768, 512, E.bfloat16, "normal", dict(BLOCK_SIZE_K=32, BLOCK_MAPPING=0)),
+    ("bf16_bk128_bn128", 512, 512, 1024, E.bfloat16, "normal", dict(BLOCK_SIZE_K=128, BLOCK_SIZE_N=128)),
+    ("bf16_bn64_uniform", 256, 320, 192, E.bfloat16, "uniform", dict(BLOCK_SIZE_N=64, NUM_STAGES=2)),
+    ("bf16_splitk_skinny", 128, 4096, 4096, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=4)),
+    ("bf16_splitk3_uneven", 256, 512, 1280, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=3)),
+    ("fp16_1024", 1024, 1024, 1024, E.float16, "normal", dict()),
+    ("fp16_atrans_bm256", 512, 512, 512, E.float16, "normal", dict(isATranspose=1, BLOCK_SIZE_M=256, NUM_STAGES=3)),
+    ("naive_fp32", 256, 192, 96, E.float32, "uniform", dict(KERNEL_VARIANT=100, BLOCK_SIZE_N=64)),
+    ("naive_bf16_atrans", 256, 192, 96, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=100, isATranspose=1, BLOCK_SIZE_N=64, BLOCK_SIZE_K=32)),
+]
+
+# golden fixture -> configs able to run that shape
+GOLDEN = [
+    ("tile_128x64x64", E.float32, dict(BLOCK_SIZE_N=64, NUM_STAGES=2)),
+    ("tile_128x64x64", E.bfloat16, dict(BLOCK_SIZE_N=64, NUM_STAGES=2)),
+    ("tile_128x64x64", E.float16, dict(BLOCK_SIZE_N=64, BLOCK_SIZE_K=32, NUM_STAGES=2)),
+    ("tile_128x64x64", E.float32, dict(SIMT_64, LOCAL_SPLIT_U=1)),
+    ("multi_256x128x96", E.float32, dict(BLOCK_SIZE_N=64, NUM_STAGES=2)),
+    ("multi_256x128x96", E.float32, dict(BLOCK_SIZE_N=128, isATranspose=1, LOCAL_SPLIT_U=3)),
+    ("multi_256x128x96", E.bfloat16, dict(BLOCK_SIZE_N=128, BLOCK_SIZE_K=32)),
+    ("multi_256x128x96", E.float32, dict(SIMT_64, LOCAL_SPLIT_U=2, isATranspose=1)),
+    ("ref_tile_64x48x32", E.float32, dict(SIMT_REF_TILE, isATranspose=1)),
+    ("ref_tile_64x48x32", E.float32, dict(SIMT_REF_TILE, isATranspose=0, LOCAL_SPLIT_U=1, SHARED_PREFETCH=0)),
+]
+GOLDEN_SHAPES = {"tile_128x64x64": (128, 64, 64), "multi_256x128x96": (256, 128, 96), "ref_tile_64x48x32": (64, 48, 32)}
+
+BIG_FP32 = ("c2_fp32_4096", 4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128))
+BIG_BF16 = ("c3_bf16_8192", 8192, 8192, 8192, E.bfloat16, dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3))
+RECT = [("c4_bf16_128x11008", 128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=4, BLOCK_SIZE_N=256)),
+        ("c4_fp32_512x4096", 512, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=2)),
+        ("c4_bf16_2048x4096", 2048, 4096, 4096, E.bfloat16, dict())]
+
+
+def all_configs():
+    out = []
+    for (_, m, n, k, dt, _, keys) in SEEDED:
+        out.append(default_config(m, n, k, dt, **keys))
+    for (name, dt, keys) in GOLDEN:
+        m, n, k = GOLDEN_SHAPES[name]
+        out.append(default_config(m, n, k, dt, **keys))
+    for (_, m, n, k, dt, keys) in [BIG_FP32, BIG_BF16] + RECT:
+        out.append(default_config(m, n, k, dt, **keys))
+    return out

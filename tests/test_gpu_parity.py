@@ -1,0 +1,197 @@
+"""GPU parity tests: every kernel family through the C ABI (compile -> load -> launch) against the CPU oracle.
+
+Tolerances (on oracle.rel_errors()['max_rel'] = max |c-ref| / max(|ref|, rms(ref))):
+  fp32 kernels (3xTF32 tcgen05, FFMA SIMT) vs the fp64 host GEMM ........ 1e-4
+  bf16 / fp16 kernels vs fp32 accumulation on the host ................... 2e-2
+plus the reference's own flag, allclose(atol=1e-1, rtol=1e-1) (KCGTask.py:177).
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from codegendemo_b200 import _lib
+from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
+from codegendemo_b200.kcg.Utils import EnumKernelDType as E, ToTorchType
+from oracle import oracle
+from tests import gpu_cases
+
+pytestmark = pytest.mark.gpu
+GOLDEN_DIR = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def run_config(kpm, A, B):
+    """A is M x K on the host; the kernel gets A^T (K x M, contiguous) when IS_ATRANS=1."""
+    inc, kern = build_kernel(kpm, 0)
+    tdt = kpm.dtypeTorch('A')
+    a = (A.t().contiguous() if kpm.isATranspose else A).to(tdt).cuda()
+    b = B.to(tdt).cuda()
+    c = torch.full((kpm.M, kpm.N), float("nan"), dtype=tdt, device="cuda:0")  # poisoned output
+    before = _lib.get_lib().kcg_launch_count()
+    kern.run(a, b, c)
+    kern.checkStatus()
+    assert _lib.get_lib().kcg_launch_count() == before + 1
+    return c, kern, (a, b)
+
+
+@pytest.mark.parametrize("case", gpu_cases.SEEDED, ids=[c[0] for c in gpu_cases.SEEDED])
+def test_seeded_case_matches_oracle(case):
+    _, M, N, K, dt, dist, keys = case
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, N, K, tdt, dist, seed=0)
+    c, _, _ = run_config(default_config(M, N, K, dt, **keys), A, B)
+    err = oracle.rel_errors(c, oracle.host_matmul(A, B))
+    assert not err["nan"], "kernel left part of C unwritten"
+    assert err["max_rel"] <= oracle.tolerance_for(tdt), err
+    assert err["allclose_ref"], err
+
+
+@pytest.mark.parametrize("case", gpu_cases.GOLDEN, ids=[f"{c[0]}-{c[1]}-{i}" for i, c in enumerate(gpu_cases.GOLDEN)])
+def test_golden_vectors(case):
+    """Inputs and outputs of the reference's own hostMatmul. Golden inputs are multiples of 2^-8 in
+    [-1, 1), exactly representable in bf16 and fp16, so every dtype sees the same operands."""
+    name, dt, keys = case
+    g = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    A, B = torch.from_numpy(g["A"]), torch.from_numpy(g["B"])
+    M, N, K = gpu_cases.GOLDEN_SHAPES[name]
+    tdt = ToTorchType(dt)
+    assert torch.equal(A.to(tdt).float(), A) and torch.equal(B.to(tdt).float(), B)
+    c, _, _ = run_config(default_config(M, N, K, dt, **keys), A, B)
+    err = oracle.rel_errors(c, torch.from_numpy(g["C64"]))
+    assert err["max_rel"] <= oracle.tolerance_for(tdt), err
+    if dt == E.float32:
+        # fp32 kernels also sit within fp32 rounding noise of the reference's fp32 result
+        assert oracle.rel_errors(c, torch.from_numpy(g["C32"]).double())["max_rel"] <= 1e-4
+        assert oracle.port_lib().kcg_oracle_verify_f32(
+            g["C32"].ctypes.data_as(ctypes.c_void_p), c.cpu().numpy().ctypes.data_as(ctypes.c_void_p), M, N,
+            ctypes.c_double(0.01)) == 0  # the reference's verify(): |host - device| < 0.01 everywhere
+
+
+def test_results_are_bitwise_reproducible_including_split_k():
+    for keys in (dict(), dict(LOCAL_SPLIT_U=4)):
+        A, B = oracle.make_inputs(256, 512, 2048, torch.bfloat16, "normal", seed=3)
+        kpm = default_config(256, 512, 2048, E.bfloat16, **keys)
+        c1, kern, (a, b) = run_config(kpm, A, B)
+        c2 = torch.empty_like(c1)
+        for _ in range(3):
+            kern.run(a, b, c2)
+        kern.checkStatus()
+        assert torch.equal(c1, c2)
+
+
+def test_host_buffer_entry_matches_device_entry():
+    A, B = oracle.make_inputs(512, 512, 512, torch.bfloat16, "normal", seed=1)
+    kpm = default_config(512, 512, 512, E.bfloat16)
+    c, kern, _ = run_config(kpm, A, B)
+    hA, hB = A.pin_memory(), B.pin_memory()
+    hC = torch.empty(512, 512, dtype=torch.bfloat16).pin_memory()
+    kern.runHost(hA, hB, hC)
+    assert torch.equal(hC, c.cpu())
+    hC2 = torch.zeros(512, 512, dtype=torch.bfloat16)  # pageable memory works too
+    kern.runHost(A, B, hC2)
+    assert torch.equal(hC2, c.cpu())
+
+
+def _column_checksum_ok(c, a, b, tol):
+    """1^T (A B) == (1^T A) B — a full-size property that needs no O(MNK) reference."""
+    lhs = c.double().sum(0)
+    rhs = a.double().sum(0) @ b.double()
+    scale = (a.double().abs().sum(0) @ b.double().abs()).clamp_min(1e-30)
+    return ((lhs - rhs).abs() / scale).max().item() <= tol
+
+
+def _check_row_blocks(c, A, B, rows, tol):
+    ref = oracle.host_matmul(A[rows], B)
+    err = oracle.rel_errors(c[rows.cuda()].cpu(), ref)
+    assert err["max_rel"] <= tol and err["allclose_ref"], err
+
+
+def test_c2_fp32_4096_full_size_properties():
+    _, M, N, K, dt, keys = gpu_cases.BIG_FP32
+    A, B = oracle.make_inputs(M, N, K, torch.float32, "uniform", seed=0)
+    c, kern, (a, b) = run_config(default_config(M, N, K, dt, **keys), A, B)
+    assert _column_checksum_ok(c, a, b, 1e-6)
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randperm(M, generator=g)[:256].sort().values
+    _check_row_blocks(c, A, B, rows, oracle.TOL_FP32)
+    # linearity in A: (2A) B == 2 (A B) exactly (power-of-two scaling commutes with every rounding)
+    c2 = torch.empty_like(c)
+    kern.run(a * 2, b, c2)
+    kern.checkStatus()
+    assert torch.equal(c2, c * 2)
+
+
+def test_c3_bf16_8192_full_size_properties():
+    _, M, N, K, dt, keys = gpu_cases.BIG_BF16
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=0)
+    c, kern, (a, b) = run_config(default_config(M, N, K, dt, **keys), A, B)
+    assert _column_checksum_ok(c, a, b, 5e-3)
+    g = torch.Generator().manual_seed(6)
+    rows = torch.randperm(M, generator=g)[:128].sort().values
+    _check_row_blocks(c, A, B, rows, oracle.TOL_16BIT)
+    # row-slab independence (what M-sharding relies on): a slab computed alone equals the slab of the full product
+    kslab = default_config(M // 8, N, K, dt, **keys)
+    _, kern2 = build_kernel(kslab, 0)
+    cs = torch.empty(M // 8, N, dtype=torch.bfloat16, device="cuda:0")
+    kern2.run(a[3 * (M // 8):4 * (M // 8)], b, cs)
+    kern2.checkStatus()
+    assert torch.equal(cs, c[3 * (M // 8):4 * (M // 8)])
+
+
+@pytest.mark.parametrize("case", gpu_cases.RECT, ids=[c[0] for c in gpu_cases.RECT])
+def test_rectangular_sweep_points(case):
+    _, M, N, K, dt, keys = case
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, N, K, tdt, "uniform", seed=0)
+    c, _, (a, b) = run_config(default_config(M, N, K, dt, **keys), A, B)
+    g = torch.Generator().manual_seed(7)
+    rows = torch.randperm(M, generator=g)[:min(M, 64)].sort().values
+    _check_row_blocks(c, A, B, rows, oracle.tolerance_for(tdt))
+    assert _column_checksum_ok(c, a, b, 1e-6 if dt == E.float32 else 5e-3)
+
+
+def test_device_naive_reference_agrees_with_tensor_core_kernel():
+    """The on-device one-thread-per-element kernel (role of the reference's gemm_kernel) vs the tcgen05 kernel."""
+    A, B = oracle.make_inputs(256, 256, 256, torch.float32, "uniform", seed=2)
+    c_tc, _, _ = run_config(default_config(256, 256, 256, E.float32, BLOCK_SIZE_N=128), A, B)
+    c_nv, _, _ = run_config(default_config(256, 256, 256, E.float32, KERNEL_VARIANT=100), A, B)
+    assert oracle.rel_errors(c_tc, c_nv.double())["max_rel"] <= 1e-4
+
+
+def test_single_pass_tf32_is_less_accurate_than_3x():
+    """Shows the gate discriminates: one TF32 pass misses 1e-4 by a wide margin, three passes meet it."""
+    A, B = oracle.make_inputs(512, 512, 1024, torch.float32, "uniform", seed=0)
+    ref = oracle.host_matmul(A, B)
+    c1, _, _ = run_config(default_config(512, 512, 1024, E.float32, KERNEL_VARIANT=3, BLOCK_SIZE_N=128), A, B)
+    c3, _, _ = run_config(default_config(512, 512, 1024, E.float32, KERNEL_VARIANT=2, BLOCK_SIZE_N=128), A, B)
+    e1, e3 = oracle.rel_errors(c1, ref), oracle.rel_errors(c3, ref)
+    assert e3["max_rel"] <= 1e-4 < e1["max_rel"]
+    assert e3["normwise"] * 50 < e1["normwise"]
+
+
+def test_perf_tester_flow_on_gpu(work_dir):
+    """The reference-style timing/correctness step (KCGTask.py:133-193) on a real kernel."""
+    from codegendemo_b200.kcg.KCGTask import PerfTester
+    PerfTester._a = PerfTester._b = None
+    PerfTester.BestPerf = []
+    for keys in (dict(BLOCK_SIZE_N=128), dict(BLOCK_SIZE_N=256)):
+        kpm = default_config(1024, 1024, 1024, E.bfloat16, **keys)
+        inc, kern = build_kernel(kpm, 0)
+        r = PerfTester._test_perf(kpm, inc, kern, benchmarkCount=5, warmupCount=1, nTorchEpsInitTest=5)
+        assert r.isCorrect and r.kcg_elapseTimeMs > 0 and r.tflops > 1 and r.maxRelErr < 2e-2
+        PerfTester._getBestPerf([r], 2)
+    assert len(PerfTester.BestPerf) == 2
+    PerfTester._a = PerfTester._b = None
+    PerfTester.BestPerf = []
+
+
+def test_device_properties_and_load_errors():
+    lib = _lib.get_lib()
+    p = _lib.DeviceProps()
+    _lib.check(lib.kcg_device_properties(0, ctypes.byref(p)))
+    assert p.cc_major == 10 and p.multiprocessor_count >= 100 and p.max_shared_mem >= 227 * 1024
+    mod, fn = ctypes.c_uint64(), ctypes.c_uint64()
+    rc = lib.kcg_load_binary(b"nope", b"/nonexistent/file.cubin", 0, 0, ctypes.byref(mod), ctypes.byref(fn), None, None)
+    assert rc == _lib.E_IO and b"KCG Error[CUDA]" in lib.kcg_last_error()
