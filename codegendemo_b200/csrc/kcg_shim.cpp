@@ -428,7 +428,7 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
     const int x3 = (r.kernel == KCG_KERNEL_TCGEN05) ? 1 : 0;
     const int units = tiles * lsu;
     out->grid[0] = units < r.num_sms ? units : r.num_sms;  // persistent CTAs
-    out->block[0] = 192 + ((c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 128 : 0);
+    out->block[0] = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 512 : 192;
     out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm, bn, bk, r.stages, x3);
   } else if (r.kernel == KCG_KERNEL_SIMT) {
     // grid/block as the reference derives them (Optimizer.cc:20,336; Rewriter.cc:726-761)

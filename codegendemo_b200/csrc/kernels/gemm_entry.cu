@@ -24,10 +24,19 @@
 #error "unsupported KCG_DTYPE"
 #endif
 
-#if KCG_VARIANT == KCG_VARIANT_TCGEN05 || KCG_VARIANT == KCG_VARIANT_TF32X1
+#if KCG_VARIANT == KCG_VARIANT_TCGEN05 && KCG_DTYPE == KCG_DT_F32
+#include "gemm_tcgen05_f32x3.cuh"
+#ifndef KCG_CHUNK  // K blocks multiplied into one TMEM accumulator before promotion to registers
+#define KCG_CHUNK ((128 / KCG_BK) > 0 ? (128 / KCG_BK) : 1)
+#endif
+using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK>;
+extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
+#elif KCG_VARIANT == KCG_VARIANT_TCGEN05 || KCG_VARIANT == KCG_VARIANT_TF32X1
 #include "gemm_tcgen05.cuh"
-using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK,
-                         KCG_GROUP, (KCG_VARIANT == KCG_VARIANT_TCGEN05) ? 1 : 0>;
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);

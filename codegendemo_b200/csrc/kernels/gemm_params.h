@@ -125,6 +125,8 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
   if (!(BM == 128 || BM == 256)) return 2;
   if (BN < 128 / eb || BN > 256 || (BN % (128 / eb)) != 0 || (BN % 16) != 0) return 3;
   if ((BM / 128) * BN > 512) return 4;
+  // 3xTF32: two TMEM accumulator buffers and MT*BN/2 register accumulators per epilogue thread
+  if (eb == 4 && x3 && ((BM / 128) * BN > 256 || (BN % 64) != 0)) return 9;
   const int rowb = BK * eb;
   if (!(rowb == 32 || rowb == 64 || (rowb % 128) == 0) || rowb > 512) return 5;
   if ((BK % (32 / eb)) != 0 || (BK % 8) != 0) return 6;

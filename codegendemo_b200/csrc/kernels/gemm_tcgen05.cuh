@@ -10,9 +10,9 @@
 //   warps 2..5    epilogue: tcgen05.ld the accumulator (one TMEM lane = one C
 //                 row per thread), convert, vectorised global stores. With two
 //                 accumulator buffers it overlaps the next tile's main loop.
-//   warps 6..9    (fp32 3xTF32 only) splitter: rewrites each landed stage as
-//                 hi = tf32(x) in place and lo = tf32(x - hi) in a twin buffer,
-//                 so the MMA warp can issue lo*hi + hi*lo + hi*hi.
+//
+// fp32 data runs here as ONE TF32 pass (comparison only); the accurate fp32 path
+// is gemm_tcgen05_f32x3.cuh.
 //
 // Config keys -> template parameters (reference meaning: Optimizer.cc:285-469):
 //   BLOCK_SIZE_M/N/K -> kBM (128 | 256 = two M=128 accumulators), kBN, kBK
@@ -34,26 +34,24 @@
 namespace kcg {
 
 template <int kDType, int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK,
-          int kGroup, int kX3>
+          int kGroup>
 struct TcGemm {
-  static_assert(tc_config_error(kDType, kBM, kBN, kBK, kStages, kX3) == 0,
+  static_assert(tc_config_error(kDType, kBM, kBN, kBK, kStages, 0) == 0,
                 "config not buildable by the tcgen05 kernel");
   static constexpr TcLayout L = make_tc_layout(kDType, kBM, kBN, kBK, kATrans);
   static constexpr int EB = L.eb;
   static constexpr bool kTf32 = (EB == 4);
-  static constexpr bool kSplit3 = kTf32 && (kX3 != 0);
   static constexpr int UMMA_K = L.umma_k;
   static constexpr int MT = kBM / 128;
   static constexpr int ACC_COLS = MT * kBN;
   static constexpr int NACC = (2 * ACC_COLS <= 512) ? 2 : 1;
   static constexpr int TMEM_COLS = kc_pow2_ceil(NACC * ACC_COLS);
   static constexpr int STAGE_HI = L.stage_hi_bytes;
-  static constexpr int STAGE_BYTES = kSplit3 ? 2 * STAGE_HI : STAGE_HI;
+  static constexpr int STAGE_BYTES = STAGE_HI;
   static constexpr int KSTEPS = kBK / UMMA_K;
   static constexpr int NUM_EPI_THREADS = 128;
-  static constexpr int NUM_SPLIT_THREADS = 128;
-  static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS + (kSplit3 ? NUM_SPLIT_THREADS : 0);
-  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, kBM, kBN, kBK, kStages, kX3);
+  static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
+  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, kBM, kBN, kBK, kStages, 0);
   static constexpr uint32_t FMT = (kDType == KCG_DT_F32)    ? FMT_TF32
                                   : (kDType == KCG_DT_BF16) ? FMT_BF16
                                                             : FMT_F16;
@@ -62,7 +60,6 @@ struct TcGemm {
   struct Barriers {
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    uint64_t split_full[kStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -162,7 +159,6 @@ struct TcGemm {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
-        mbar_init(&bars->split_full[s], NUM_SPLIT_THREADS);
       }
       for (int a = 0; a < 2; ++a) {
         mbar_init(&bars->tmem_full[a], 1);
@@ -237,8 +233,7 @@ struct TcGemm {
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
-            uint64_t* ready = kSplit3 ? &bars->split_full[s] : &bars->full[s];
-            if (!mbar_wait(ready, ph, &bars->abort_flag)) {
+            if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
               report(p, bars, KCG_ST_TIMEOUT_MMA, it, s);
               ok = false;
               break;
@@ -266,17 +261,7 @@ struct TcGemm {
                 const uint64_t adesc =
                     make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
                 const uint32_t d = tmem_acc + t * kBN;
-                if constexpr (kSplit3) {
-                  const uint64_t adesc_lo = make_smem_desc(sa + STAGE_HI + a_t + a_off, L.a_lbo,
-                                                           L.a_sbo, L.a_desc_swizzle);
-                  const uint64_t bdesc_lo = make_smem_desc(sb + STAGE_HI + b_off, L.b_lbo, L.b_sbo,
-                                                           L.b_desc_swizzle);
-                  umma_ss<true>(d, adesc_lo, bdesc, IDESC, acc_flag);
-                  umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
-                  umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
-                } else {
-                  umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
-                }
+                umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
               }
             }
             umma_commit(&bars->empty[s]);  // stage reusable once these MMAs retire
@@ -284,7 +269,7 @@ struct TcGemm {
           if (ok) umma_commit(&bars->tmem_full[ab]);
         }
       }
-    } else if (warp < 6) {
+    } else {
       // ------------------------------------------------------------ epilogue
       const int q = warp & 3;  // TMEM lane quarter this warp may read
       const int epi_tid = (warp - 2) * 32 + lane;
@@ -375,40 +360,6 @@ struct TcGemm {
           named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit
         }
       }
-    } else {
-      // ------------------------------------------- 3xTF32 splitter (warps 6..9)
-      if constexpr (kSplit3) {
-        const int stid = threadIdx.x - 192;
-        uint32_t it = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
-          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
-            const uint32_t s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
-              if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_SPLITTER, it, s);
-              ok = false;
-              break;
-            }
-            float4* hi = reinterpret_cast<float4*>(smem + s * STAGE_BYTES);
-            float4* lo = reinterpret_cast<float4*>(smem + s * STAGE_BYTES + STAGE_HI);
-#pragma unroll 4
-            for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
-              const float4 x = hi[i];
-              float4 h, l;
-              split_tf32(x.x, h.x, l.x);
-              split_tf32(x.y, h.y, l.y);
-              split_tf32(x.z, h.z, l.z);
-              split_tf32(x.w, h.w, l.w);
-              hi[i] = h;
-              lo[i] = l;
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(&bars->split_full[s]);
-          }
-        }
-      }
     }
 
     // ------------------------------------------------------------ common exit
@@ -425,17 +376,6 @@ struct TcGemm {
       tc_fence_after_sync();
       tmem_dealloc(tmem_base, TMEM_COLS);
     }
-  }
-
-  // x = hi + lo with hi, lo both exactly representable in TF32 (round to
-  // nearest); hi*hi + hi*lo + lo*hi then carries ~21 mantissa bits.
-  __device__ static __forceinline__ void split_tf32(float x, float& hi, float& lo) {
-    uint32_t h, l;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
-    hi = __uint_as_float(h);
-    const float r = x - hi;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(r));
-    lo = __uint_as_float(l);
   }
 };
 

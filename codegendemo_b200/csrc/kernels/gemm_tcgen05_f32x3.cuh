@@ -1,0 +1,418 @@
+// fp32 GEMM on the tensor cores with fp32-level accuracy: 3xTF32 split plus
+// chunked promotion of the TMEM accumulator into fp32 registers.
+//
+// Why two extra mechanisms on top of the plain tcgen05 pipeline:
+//  * kind::tf32 reads fp32 words and ignores the low 13 mantissa bits, so
+//    hi = x needs no work; lo = tf32_rn(x - trunc_tf32(x)) is written by splitter
+//    warps into a twin of every landed stage, and each K step issues
+//    lo*hi + hi*lo + hi*hi (lo*lo, ~2^-22 relative, is dropped).
+//  * The tensor core adds into its fp32 accumulator with truncation, a bias that
+//    grows linearly with the number of accumulated K steps (measured: 3e-5
+//    normwise at K = 4096). So the MMA warp restarts a fresh accumulator every
+//    kChunk K blocks, alternating between two TMEM buffers, and the epilogue
+//    warps add each finished chunk into register accumulators with ordinary
+//    round-to-nearest FADDs while the next chunk is being multiplied.
+//
+// Warp roles (512 threads, four warpgroups so that setmaxnreg can move registers
+// from the control warps to the accumulating warps):
+//   WG0  warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-3 idle
+//   WG1  warps 4-7   splitter (lo twin of each stage)
+//   WG2/3 warps 8-15 accumulate + epilogue; warp w reads TMEM lane quarter w%4,
+//         column half (w-8)/4; kAccPerThread = MT*BN/2 fp32 registers per thread
+//
+// Same work decomposition, raster, split-K reduction and bounded waits as
+// gemm_tcgen05.cuh.
+#pragma once
+#include "gemm_params.h"
+#include "ptx_sm100.cuh"
+
+namespace kcg {
+
+template <int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK, int kGroup, int kChunk>
+struct TcGemmF32x3 {
+  static constexpr int kDType = KCG_DT_F32;
+  static_assert(tc_config_error(kDType, kBM, kBN, kBK, kStages, 1) == 0,
+                "config not buildable by the 3xTF32 kernel");
+  static constexpr TcLayout L = make_tc_layout(kDType, kBM, kBN, kBK, kATrans);
+  static constexpr int UMMA_K = 8;
+  static constexpr int MT = kBM / 128;
+  static constexpr int ACC_COLS = MT * kBN;
+  static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
+  static_assert(kBN % 64 == 0, "each epilogue warp drains whole 32-column pieces of its column half");
+  static constexpr int TMEM_COLS = kc_pow2_ceil(2 * ACC_COLS);
+  static constexpr int STAGE_HI = L.stage_hi_bytes;
+  static constexpr int STAGE_BYTES = 2 * STAGE_HI;
+  static constexpr int KSTEPS = kBK / UMMA_K;
+  static constexpr int NUM_THREADS = 512;
+  static constexpr int NUM_SPLIT_THREADS = 128;
+  static constexpr int NUM_EPI_THREADS = 256;
+  static constexpr int HALF_COLS = kBN / 2;
+  static constexpr int PIECES = HALF_COLS / 32;
+  static constexpr int ACC_PER_THREAD = MT * HALF_COLS;
+  static_assert(ACC_PER_THREAD <= 128, "register accumulators per thread");
+  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, kBM, kBN, kBK, kStages, 1);
+  static constexpr uint32_t IDESC = make_instr_desc(FMT_TF32, kATrans ? 1u : 0u, 1u, 128u, kBN);
+
+  struct Barriers {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t split_full[kStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+    uint32_t last_flag;
+  };
+  static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
+
+  struct Unit {
+    int m0, n0, tile, split, kb0, kbn;
+  };
+
+  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb) {
+    Unit w;
+    w.tile = u / kSplitK;
+    w.split = u - w.tile * kSplitK;
+    int mb, nb;
+    if constexpr (kGroup > 1) {
+      const int per_group = kGroup * tiles_n;
+      const int g = w.tile / per_group;
+      const int first_m = g * kGroup;
+      const int gsz = (tiles_m - first_m < kGroup) ? (tiles_m - first_m) : kGroup;
+      const int r = w.tile - g * per_group;
+      mb = first_m + (r % gsz);
+      nb = r / gsz;
+    } else {
+      mb = w.tile / tiles_n;
+      nb = w.tile - mb * tiles_n;
+    }
+    w.m0 = mb * kBM;
+    w.n0 = nb * kBN;
+    const int per = (num_kb + kSplitK - 1) / kSplitK;
+    w.kb0 = w.split * per;
+    int kb1 = w.kb0 + per;
+    if (kb1 > num_kb) kb1 = num_kb;
+    w.kbn = (kb1 > w.kb0) ? (kb1 - w.kb0) : 0;
+    return w;
+  }
+
+  __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
+                                                uint32_t code, uint32_t d0, uint32_t d1) {
+    bars->abort_flag = 1u;
+    if (atomicCAS(p.status, 0u, code) == 0u) {
+      p.status[1] = blockIdx.x;
+      p.status[2] = d0;
+      p.status[3] = d1;
+    }
+  }
+
+  template <int REGS>
+  __device__ static __forceinline__ void reg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
+  }
+  template <int REGS>
+  __device__ static __forceinline__ void reg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
+  }
+
+  __device__ static void run(const KcgGemmParams& p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tiles_m = (p.M + kBM - 1) / kBM;
+    const int tiles_n = (p.N + kBN - 1) / kBN;
+    const int num_kb = (p.K + kBK - 1) / kBK;
+    const int num_units = tiles_m * tiles_n * kSplitK;
+
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(&bars->full[s], 1);
+        mbar_init(&bars->empty[s], 1);
+        mbar_init(&bars->split_full[s], NUM_SPLIT_THREADS);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&bars->tmem_full[a], 1);
+        mbar_init(&bars->tmem_empty[a], NUM_EPI_THREADS);
+      }
+      bars->abort_flag = 0u;
+      bars->last_flag = 0u;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp < 4) {
+      reg_dec<56>();
+      if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- producer
+        tma_prefetch_desc(&p.tmA);
+        tma_prefetch_desc(&p.tmB);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1u;
+            if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_PRODUCER, it, s);
+              ok = false;
+              break;
+            }
+            uint8_t* sa = smem + s * STAGE_BYTES;
+            uint8_t* sb = sa + L.a_bytes;
+            mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
+            const int k0 = (w.kb0 + kb) * kBK;
+#pragma unroll
+            for (int j = 0; j < L.a_boxes; ++j) {
+              if constexpr (kATrans) {
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.m0 + j * L.atom, k0);
+              } else {
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s],
+                            k0 + j * L.a_box_inner, w.m0);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < L.b_boxes; ++j) {
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, k0);
+            }
+          }
+        }
+      } else if (warp == 1 && lane == 0) {
+        // -------------------------------------------------------- MMA issuer
+        uint32_t it = 0, chunk_it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          for (int kb0 = 0; kb0 < w.kbn && ok; kb0 += kChunk, ++chunk_it) {
+            const uint32_t ab = chunk_it & 1u;
+            const uint32_t aph = (chunk_it >> 1) & 1u;
+            if (!mbar_wait(&bars->tmem_empty[ab], aph ^ 1u, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_MMA, 0x100u + ab, chunk_it);
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
+            const int kb1 = (kb0 + kChunk < w.kbn) ? kb0 + kChunk : w.kbn;
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
+              const uint32_t s = it % kStages;
+              const uint32_t ph = (it / kStages) & 1u;
+              if (!mbar_wait(&bars->split_full[s], ph, &bars->abort_flag)) {
+                report(p, bars, KCG_ST_TIMEOUT_MMA, it, s);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+              const uint32_t sb = sa + L.a_bytes;
+#pragma unroll
+              for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t a_off;
+                if constexpr (kATrans) {
+                  a_off = ks * UMMA_K * 128;
+                } else {
+                  constexpr int swb = (kBK * 4 < 128) ? kBK * 4 : 128;
+                  a_off = ((ks * 32) / swb) * L.a_box_bytes + ((ks * 32) % swb);
+                }
+                const uint32_t b_off = ks * UMMA_K * 128;
+                const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
+                const uint64_t bdesc = make_smem_desc(sb + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
+                const uint64_t bdesc_lo =
+                    make_smem_desc(sb + STAGE_HI + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
+#pragma unroll
+                for (int t = 0; t < MT; ++t) {
+                  const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
+                                               : t * 128 * (L.a_box_bytes / kBM);
+                  const uint64_t adesc =
+                      make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
+                  const uint64_t adesc_lo = make_smem_desc(sa + STAGE_HI + a_t + a_off, L.a_lbo,
+                                                           L.a_sbo, L.a_desc_swizzle);
+                  const uint32_t d = tmem_acc + t * kBN;
+                  umma_ss<true>(d, adesc_lo, bdesc, IDESC, first);
+                  umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
+                  umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
+                }
+              }
+              umma_commit(&bars->empty[s]);
+            }
+            if (ok) umma_commit(&bars->tmem_full[ab]);
+          }
+        }
+      }
+    } else if (warp < 8) {
+      // --------------------------------------------------------------- splitter
+      reg_dec<56>();
+      const int stid = threadIdx.x - 128;
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1u;
+          if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
+            if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_SPLITTER, it, s);
+            ok = false;
+            break;
+          }
+          const uint4* hi = reinterpret_cast<const uint4*>(smem + s * STAGE_BYTES);
+          uint4* lo = reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + STAGE_HI);
+#pragma unroll 4
+          for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
+            const uint4 x = hi[i];
+            uint4 l;
+            l.x = lo_part(x.x);
+            l.y = lo_part(x.y);
+            l.z = lo_part(x.z);
+            l.w = lo_part(x.w);
+            lo[i] = l;
+          }
+          fence_proxy_async_smem();
+          mbar_arrive(&bars->split_full[s]);
+        }
+      }
+    } else {
+      // --------------------------------------------------- accumulate + epilogue
+      reg_inc<200>();
+      const int q = warp & 3;
+      const int half = (warp - 8) >> 2;
+      const int epi_tid = threadIdx.x - 256;
+      const int row_in_acc = q * 32 + lane;
+      const int col_half0 = half * HALF_COLS;
+      float* Cout = reinterpret_cast<float*>(p.C);
+      uint32_t chunk_it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        float acc[ACC_PER_THREAD];
+#pragma unroll
+        for (int i = 0; i < ACC_PER_THREAD; ++i) acc[i] = 0.f;
+        for (int kb0 = 0; kb0 < w.kbn; kb0 += kChunk, ++chunk_it) {
+          const uint32_t ab = chunk_it & 1u;
+          const uint32_t aph = (chunk_it >> 1) & 1u;
+          const bool got = mbar_wait(&bars->tmem_full[ab], aph, &bars->abort_flag);
+          if (!__all_sync(0xffffffffu, got)) {
+            if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, chunk_it, ab);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t tmem_acc =
+              tmem_base + ab * ACC_COLS + col_half0 + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+          for (int t = 0; t < MT; ++t) {
+#pragma unroll
+            for (int c = 0; c < PIECES; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tmem_acc + t * kBN + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                acc[(t * PIECES + c) * 32 + i] += __uint_as_float(r[i]);
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(&bars->tmem_empty[ab]);
+        }
+        if (!ok) break;
+        // ---- tile (or split partial) complete in registers: store
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          const int row = w.m0 + t * 128 + row_in_acc;
+#pragma unroll
+          for (int c = 0; c < PIECES; ++c) {
+            const int col = w.n0 + col_half0 + c * 32;
+            if (row < p.M && col < p.N) {
+              float* dst = (kSplitK > 1)
+                               ? p.splitk_ws + (static_cast<size_t>(w.split) * p.M + row) * p.N + col
+                               : Cout + static_cast<size_t>(row) * p.ldc + col;
+              float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int b = (t * PIECES + c) * 32 + 4 * i;
+                d4[i] = make_float4(acc[b], acc[b + 1], acc[b + 2], acc[b + 3]);
+              }
+            }
+          }
+        }
+        if constexpr (kSplitK > 1) {
+          __threadfence();
+          named_bar_sync(1, NUM_EPI_THREADS);
+          if (epi_tid == 0) {
+            const unsigned int old = atomicAdd(&p.tile_counters[w.tile], 1u);
+            bars->last_flag = (old == static_cast<unsigned int>(kSplitK - 1)) ? 1u : 0u;
+            if (old == static_cast<unsigned int>(kSplitK - 1)) p.tile_counters[w.tile] = 0u;
+          }
+          named_bar_sync(1, NUM_EPI_THREADS);
+          if (bars->last_flag != 0u) {
+            __threadfence();
+            for (int t = 0; t < MT; ++t) {
+              const int row = w.m0 + t * 128 + row_in_acc;
+              if (row >= p.M) continue;
+              for (int c = 0; c < PIECES; ++c) {
+                const int col = w.n0 + col_half0 + c * 32;
+                if (col >= p.N) continue;
+                float v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0.f;
+                for (int s = 0; s < kSplitK; ++s) {
+                  const float4* src = reinterpret_cast<const float4*>(
+                      p.splitk_ws + (static_cast<size_t>(s) * p.M + row) * p.N + col);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const float4 x = __ldcg(src + i);
+                    v[4 * i] += x.x;
+                    v[4 * i + 1] += x.y;
+                    v[4 * i + 2] += x.z;
+                    v[4 * i + 3] += x.w;
+                  }
+                }
+                float4* d4 = reinterpret_cast<float4*>(Cout + static_cast<size_t>(row) * p.ldc + col);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                  d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              }
+            }
+          }
+          named_bar_sync(1, NUM_EPI_THREADS);
+        }
+      }
+    }
+
+    // ------------------------------------------------------------ common exit
+    if (bars->abort_flag != 0u) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      __syncwarp();
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+  }
+
+  // tf32_rn(x - trunc_tf32(x)) on raw bits; the subtraction is exact in fp32.
+  __device__ static __forceinline__ uint32_t lo_part(uint32_t xbits) {
+    const float x = __uint_as_float(xbits);
+    const float hi = __uint_as_float(xbits & 0xffffe000u);
+    uint32_t l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+    return l;
+  }
+};
+
+}  // namespace kcg

@@ -216,6 +216,8 @@ class TuningSpaceChecker_Matmul:
             return False
         if (bm // 128) * bn > 512:
             return False
+        if eb == 4 and ((bm // 128) * bn > 256 or bn % 64):  # 3xTF32: two TMEM buffers + register accumulators
+            return False
         rowb = bk * eb
         if not (rowb in (32, 64) or rowb % 128 == 0) or rowb > 512:
             return False

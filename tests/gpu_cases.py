@@ -27,6 +27,7 @@ SEEDED = [
      dict(SIMT_64, SHARED_PREFETCH=0, REG_PREFETCH=0, BLOCK_MAPPING=0)),
     ("ref_shape_1024x1056x1024_simt", 1024, 1056, 1024, E.float32, "uniform", dict(SIMT_REF_TILE, isATranspose=1)),
     ("fp32_bn256_bk16", 512, 512, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=3)),
+    ("fp32_bn256_bk32_k11008", 128, 256, 11008, E.float32, "uniform", dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=2)),
     ("fp32_bk64_2stage", 256, 256, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=64, BLOCK_SIZE_K=64, NUM_STAGES=2)),
     ("fp32_bm256", 512, 256, 256, E.float32, "uniform", dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=128, NUM_STAGES=2)),
     ("fp32_splitk4", 128, 256, 4096, E.float32, "uniform", dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),

@@ -54,7 +54,7 @@ def test_kernel_name_scheme_covers_every_key():
     for part in ("MNK1024x1024x1024", "DTabcfloat32xfloat32xfloat32", "AT0", "BTmnk128x128x32", "LSU2", "BM4",
                  "UNROLL4", "REGP1", "SHMP1", "LC0", "RC0", "ST", "_V2"):
         assert part in name, part
-    assert info.kernel == _lib.KERNEL_TCGEN05 and info.block[0] == 320  # 3xTF32 adds 4 splitter warps
+    assert info.kernel == _lib.KERNEL_TCGEN05 and info.block[0] == 512  # 3xTF32: 4 warpgroups
     assert info.splitk == 2 and info.grid[0] == min(148, 8 * 8 * 2)
 
 
