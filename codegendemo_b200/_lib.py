@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
     "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
-    "kcg_last_error", "kcg_version",
+    "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
 )
 
 
@@ -119,6 +119,9 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_check_status.argtypes = [ctypes.c_int, u64]
     lib.kcg_matmul_host.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64,
                                     ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.kcg_gemm_bf16_splitk_noalloc.argtypes = [ctypes.c_int, u64, u64, u64, u64, ctypes.c_int, ctypes.c_int,
+                                                 ctypes.c_int, ctypes.c_int]
+    lib.kcg_gemm_bf16_splitk_noalloc.restype = ctypes.c_int
     lib.kcg_launch_count.restype = u64
     lib.kcg_last_error.restype = ctypes.c_char_p
     lib.kcg_version.restype = ctypes.c_char_p

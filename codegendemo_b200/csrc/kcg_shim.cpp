@@ -496,6 +496,11 @@ int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64
 // ============================================================================ C ABI
 extern "C" {
 
+// Internal (not part of the ABI): lets the library's other translation units report through
+// kcg_last_error() and count their launches.
+int kcg_internal_fail(int code, const char* msg) { return fail(code, "%s", msg); }
+void kcg_internal_count_launch(void) { g_launches.fetch_add(1); }
+
 const char* kcg_last_error(void) { return g_last_error.c_str(); }
 const char* kcg_version(void) { return "kcg-b200 0.1 (sm_100a)"; }
 uint64_t kcg_launch_count(void) { return g_launches.load(); }

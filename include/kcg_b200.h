@@ -140,6 +140,30 @@ int kcg_check_status(int device, uint64_t stream);
 int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
                     const void* hostA, const void* hostB, void* hostC);
 
+/* ---- allocation-free split-K GEMM -------------------------------------------------
+ * No counterpart in the reference (its launcher never allocates because its kernels need no
+ * workspace). For callers that must not allocate device memory at the point of the GEMM - code
+ * running inside a fixed memory pool, a serving loop with a frozen memory budget, a process whose
+ * free HBM belongs to another allocator - where the workspace kcg_launch_gemm allocates on first
+ * use would fail, stall or synchronise the device. bf16 C = A*B (A is M x K, B is K x N, row-major),
+ * K split KCG_NOALLOC_SPLITK ways, tile 128x256x64; same kernel code as the compiled path.
+ *
+ * The split-K workspace is a fixed array inside the library's device image (about 32 MiB per GPU
+ * that loads the library, held until the process exits). Limits: M, N, K multiples of 128, 256, 64;
+ * K >= 64*KCG_NOALLOC_SPLITK; KCG_NOALLOC_SPLITK*M*N <= KCG_NOALLOC_MAX_PARTIAL_FLOATS and
+ * (M/128)*(N/256) <= KCG_NOALLOC_MAX_TILES, else KCG_E_TOO_LARGE. The call itself calls no
+ * cudaMalloc/cudaFree or allocating library routine. The first call on a device resolves the
+ * array's device address and raises the kernel's shared-memory limit; make that first call before
+ * any stream capture begins. All calls on a device share the one array: two calls that overlap on the
+ * GPU (different streams, no ordering) race on it and give wrong results; calls ordered on one
+ * stream are safe. `synchronize` != 0 waits for the stream and reports a kernel that gave up in a
+ * bounded wait as KCG_E_DEVICE_TIMEOUT; with 0 the call is asynchronous. */
+#define KCG_NOALLOC_SPLITK 4
+#define KCG_NOALLOC_MAX_PARTIAL_FLOATS (8 * 1024 * 1024)
+#define KCG_NOALLOC_MAX_TILES 4096
+int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64_t B, uint64_t C, int M, int N,
+                                 int K, int synchronize);
+
 /* Number of kernel launches issued through this library since load (all threads). */
 uint64_t kcg_launch_count(void);
 /* Frees workspaces, device buffers and cached tensor maps of every device. */
