@@ -1,0 +1,78 @@
+"""Compile, run and check ONE tuning config from the command line.
+
+The single-case counterpart of the autotune driver (role of the reference's ad-hoc
+Runtime/python/kcg/test.py): handy for a quick check of a config and as a small, self-ending
+workload for profilers.
+
+    python -m codegendemo_b200.kcg.run_single --m 2048 --n 8192 --k 8192 --dtype bf16 \
+        --set BLOCK_SIZE_M=256 --set BLOCK_SIZE_N=256 --set NUM_STAGES=3 --launches 3 --warmup 2
+"""
+import argparse
+import math
+import sys
+
+from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
+from codegendemo_b200.kcg.Utils import EnumKernelDType
+
+
+def main(argv=None) -> int:
+    import torch
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--m", type=int, required=True)
+    ap.add_argument("--n", type=int, required=True)
+    ap.add_argument("--k", type=int, required=True)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp16", "fp32"])
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE",
+                    help="override a tuning key (attribute of KernelArgMatmul), e.g. BLOCK_SIZE_N=128")
+    ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--no-check", action="store_true")
+    a = ap.parse_args(argv)
+    edt = {"bf16": EnumKernelDType.bfloat16, "fp16": EnumKernelDType.float16, "fp32": EnumKernelDType.float32}[a.dtype]
+    tdt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
+    keys = {}
+    for kv in a.set:
+        k, v = kv.split("=", 1)
+        keys[k] = int(v)
+    kpm = default_config(a.m, a.n, a.k, edt, **keys)
+    torch.cuda.set_device(a.device)
+    dev = f"cuda:{a.device}"
+    inConfig, kern = build_kernel(kpm, a.device)
+    g = torch.Generator(device=dev).manual_seed(0)
+    A = (torch.randn(a.m, a.k, generator=g, device=dev) / math.sqrt(a.k)).to(tdt)
+    B = (torch.randn(a.k, a.n, generator=g, device=dev) / math.sqrt(a.k)).to(tdt)
+    C = torch.empty(a.m, a.n, dtype=tdt, device=dev)
+    a_in = A.t().contiguous() if kpm.isATranspose else A
+    for _ in range(a.warmup):
+        kern.run(a_in, B, C)
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(a.launches):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        kern.run(a_in, B, C)
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    kern.checkStatus()
+    times.sort()
+    med = times[len(times) // 2]
+    print(f"kernel {inConfig.kernelFuncName}")
+    print(f"grid {inConfig.gridDims()} block {inConfig.blockDims()} smem {inConfig.sharedMem()} B")
+    print(f"median {med:.4f} ms  {2.0 * a.m * a.n * a.k / (med * 1e9):.1f} TFLOP/s over {a.launches} launches")
+    if not a.no_check:
+        rows = min(a.m, 512)
+        ref = (A[:rows].double() @ B.double()) if tdt == torch.float32 else (A[:rows].float() @ B.float())
+        diff = (C[:rows].to(ref.dtype) - ref).abs()
+        rms = ref.pow(2).mean().sqrt()
+        max_rel = (diff / torch.maximum(ref.abs(), rms)).max().item()
+        tol = 1e-4 if tdt == torch.float32 else 2e-2
+        print(f"max_rel (first {rows} rows, device reference) {max_rel:.3e}  tolerance {tol}  "
+              f"{'OK' if max_rel <= tol else 'FAIL'}")
+        return 0 if max_rel <= tol else 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
