@@ -146,6 +146,8 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
   p.lda = K;
   p.ldb = N;
   p.ldc = N;
+  p.split_first_tile = 0;  // every tile is split
+  p.split_factor = kSplitK;
   p.splitk_ws = reinterpret_cast<float*>(d->scratch);
   p.tile_counters = reinterpret_cast<unsigned int*>(d->scratch + kPartialBytes);
   p.status = reinterpret_cast<unsigned int*>(d->scratch + kPartialBytes + kCounterBytes);

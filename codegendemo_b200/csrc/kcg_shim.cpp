@@ -454,7 +454,7 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
   out->m = M;
   out->n = N;
   out->k = K;
-  (void)K;
+  out->reserved[0] = r.num_sms;
   return 0;
 }
 
@@ -639,6 +639,9 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
   p.ldb = N;
   p.ldc = N;
   p.status = reinterpret_cast<unsigned int*>(s->status);
+  p.split_first_tile = (M / (info->bm > 0 ? info->bm : 1)) * (N / (info->bn > 0 ? info->bn : 1));
+  p.split_factor = 1;
+  int grid0 = info->grid[0];
   if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1) {
     const kcg::TcLayout L = kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
     if (info->atrans) {
@@ -653,11 +656,46 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
     if (int e = encode_map(s, &p.tmB, info->dtype, B, N, K, static_cast<uint64_t>(N) * eb, L.b_box_inner,
                            L.b_box_outer, L.b_tma_swizzle))
       return e;
+    // K splitting: LOCAL_SPLIT_U > 1 splits every tile; otherwise only the tiles of the last,
+    // partially filled wave of the persistent grid are split so that it fills the GPU
+    // (KCG_TAIL_SPLIT=0 turns that off).
+    const int T = (M / info->bm) * (N / info->bn);
+    const int num_kb = K / info->bk;
+    const int G = info->reserved[0] > 0 ? info->reserved[0] : 148;
+    int first = T, factor = 1;
     if (info->splitk > 1) {
+      first = 0;
+      factor = info->splitk;
+    } else {
+      const char* e = getenv("KCG_TAIL_SPLIT");
+      const int rem = T % G;
+      if (!(e && e[0] == '0') && rem > 0) {
+        int f = G / rem;
+        if (f > 8) f = 8;
+        if (f > num_kb) f = num_kb;
+        // Worth it only when the time saved on the last wave exceeds the cost of the reduction
+        // (partials through L2, one extra round trip): estimate the tile's main-loop time from
+        // a per-SM rate of ~10 MFLOP/us (16-bit) or ~1.4 MFLOP/us useful (fp32 as 3xTF32).
+        const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel == KCG_KERNEL_TCGEN05) ? 1.4
+                                    : (info->dtype == KCG_DTYPE_FLOAT32)                                     ? 4.5
+                                                                                                             : 10.0;
+        const double tile_us = 2.0 * info->bm * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
+        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= 20.0) {
+          first = T - rem;
+          factor = f;
+        }
+      }
+    }
+    const int units = first + (T - first) * factor;
+    grid0 = units < G ? units : G;
+    p.split_first_tile = first;
+    p.split_factor = factor;
+    if (factor > 1) {
       std::lock_guard<std::mutex> g(g_dev_mutex);
-      const size_t need = static_cast<size_t>(info->splitk) * M * N * sizeof(float);
+      const size_t slots = static_cast<size_t>(T - first) * factor;
+      const size_t need = slots * info->bm * info->bn * sizeof(float);
       if (int e = grow(&s->ws, &s->ws_bytes, need)) return e;
-      const size_t tiles = static_cast<size_t>(M / info->bm) * (N / info->bn);
+      const size_t tiles = static_cast<size_t>(T - first);
       if (s->counters_n < tiles) {
         size_t have = s->counters_n * 4;
         if (int e = grow(&s->counters, &have, tiles * 4)) return e;
@@ -671,7 +709,7 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
   void* args[1] = {&p};
   CUlaunchConfig cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDimX = info->grid[0];
+  cfg.gridDimX = grid0;
   cfg.gridDimY = info->grid[1];
   cfg.gridDimZ = info->grid[2];
   cfg.blockDimX = info->block[0];

@@ -36,11 +36,16 @@ struct alignas(64) KcgGemmParams {
   const void* A;
   const void* B;
   void* C;
-  float* splitk_ws;             // [SPLITK][M][N] fp32 partials (split-K only)
-  unsigned int* tile_counters;  // one per output tile, zero between launches (split-K only)
+  float* splitk_ws;             // fp32 partial tiles, [slot][BM][BN]; slot = unit - split_first_tile
+  unsigned int* tile_counters;  // one per split tile (tile - split_first_tile), zero between launches
   unsigned int* status;         // 4 words: code, blockIdx.x, detail0, detail1
   int M, N, K;
   int lda, ldb, ldc;  // leading dimensions in elements (row-major storage)
+  // K splitting over CTAs: tiles [0, split_first_tile) are computed whole, every tile from
+  // split_first_tile on is cut into split_factor K ranges. LOCAL_SPLIT_U = S splits every tile
+  // (first = 0, factor = S); with LOCAL_SPLIT_U = 1 the launcher splits only the tiles of the last,
+  // partially filled wave of the persistent grid (or nothing: factor = 1).
+  int split_first_tile, split_factor;
 };
 
 namespace kcg {

@@ -69,16 +69,27 @@ struct TcGemm {
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
   struct Unit {
-    int m0, n0, tile, split, kb0, kbn;
+    int m0, n0, tile, split, nsplit, slot, kb0, kbn;
   };
 
   // Work unit u -> output tile (grouped raster, matmul.cpp:79-86 semantics:
   // groups of kGroup tile-rows walk N first so a wave shares A and B in L2)
   // and K range of this split.
-  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb) {
+  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb,
+                                                     int first_split, int factor) {
     Unit w;
-    w.tile = u / kSplitK;
-    w.split = u - w.tile * kSplitK;
+    if (u < first_split) {
+      w.tile = u;
+      w.split = 0;
+      w.nsplit = 1;
+      w.slot = 0;
+    } else {
+      const int v = u - first_split;
+      w.tile = first_split + v / factor;
+      w.split = v - (w.tile - first_split) * factor;
+      w.nsplit = factor;
+      w.slot = v;
+    }
     int mb, nb;
     if constexpr (kGroup > 1) {
       const int per_group = kGroup * tiles_n;
@@ -94,7 +105,7 @@ struct TcGemm {
     }
     w.m0 = mb * kBM;
     w.n0 = nb * kBN;
-    const int per = (num_kb + kSplitK - 1) / kSplitK;
+    const int per = (num_kb + w.nsplit - 1) / w.nsplit;
     w.kb0 = w.split * per;
     int kb1 = w.kb0 + per;
     if (kb1 > num_kb) kb1 = num_kb;
@@ -153,7 +164,9 @@ struct TcGemm {
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + kBN - 1) / kBN;
     const int num_kb = (p.K + kBK - 1) / kBK;
-    const int num_units = tiles_m * tiles_n * kSplitK;
+    const int first_split = p.split_first_tile;
+    const int split_factor = p.split_factor > 0 ? p.split_factor : 1;
+    const int num_units = first_split + (tiles_m * tiles_n - first_split) * split_factor;
 
     if (threadIdx.x == 0) {
       for (int s = 0; s < kStages; ++s) {
@@ -186,7 +199,7 @@ struct TcGemm {
         uint32_t it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
@@ -221,7 +234,7 @@ struct TcGemm {
         uint32_t it = 0, acc_it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++acc_it) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           const uint32_t ab = acc_it % NACC;
           const uint32_t aph = (acc_it / NACC) & 1u;
           if (!mbar_wait(&bars->tmem_empty[ab], aph ^ 1u, &bars->abort_flag)) {
@@ -277,7 +290,7 @@ struct TcGemm {
       uint32_t acc_it = 0;
       OutT* Cout = reinterpret_cast<OutT*>(p.C);
       for (int u = blockIdx.x; u < num_units; u += gridDim.x, ++acc_it) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         const uint32_t ab = acc_it % NACC;
         const uint32_t aph = (acc_it / NACC) & 1u;
         // The warp must leave the wait as one: tcgen05.ld below is warp-collective.
@@ -306,8 +319,9 @@ struct TcGemm {
             }
             const int col = w.n0 + c * 32;
             if (row < p.M && col < p.N) {
-              if constexpr (kSplitK > 1) {
-                float* dst = p.splitk_ws + (static_cast<size_t>(w.split) * p.M + row) * p.N + col;
+              if (w.nsplit > 1) {
+                float* dst = p.splitk_ws +
+                             (static_cast<size_t>(w.slot) * kBM + t * 128 + row_in_acc) * kBN + c * 32;
                 store_chunk<float>(dst, v);
               } else {
                 store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
@@ -318,15 +332,16 @@ struct TcGemm {
         tc_fence_before_sync();
         mbar_arrive(&bars->tmem_empty[ab]);
 
-        if constexpr (kSplitK > 1) {
+        if (w.nsplit > 1) {
           // Publish this split's partial tile; the last split to arrive sums all
           // partials in split order (bitwise reproducible) and writes C.
+          const int ctr = w.tile - first_split;
           __threadfence();
           named_bar_sync(1, NUM_EPI_THREADS);
           if (epi_tid == 0) {
-            const unsigned int old = atomicAdd(&p.tile_counters[w.tile], 1u);
-            bars->last_flag = (old == static_cast<unsigned int>(kSplitK - 1)) ? 1u : 0u;
-            if (old == static_cast<unsigned int>(kSplitK - 1)) p.tile_counters[w.tile] = 0u;
+            const unsigned int old = atomicAdd(&p.tile_counters[ctr], 1u);
+            bars->last_flag = (old == static_cast<unsigned int>(w.nsplit - 1)) ? 1u : 0u;
+            if (old == static_cast<unsigned int>(w.nsplit - 1)) p.tile_counters[ctr] = 0u;
           }
           named_bar_sync(1, NUM_EPI_THREADS);
           const bool last = bars->last_flag != 0u;
@@ -341,16 +356,33 @@ struct TcGemm {
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                for (int s = 0; s < kSplitK; ++s) {
-                  const float4* src = reinterpret_cast<const float4*>(
-                      p.splitk_ws + (static_cast<size_t>(s) * p.M + row) * p.N + col);
+                // Partials of up to four splits are fetched before any is added, so that
+                // the L2 round trips overlap; the adds still run in split order.
+                for (int s0 = 0; s0 < w.nsplit; s0 += 4) {
+                  float4 x[4][8];
 #pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const float4 x = __ldcg(src + i);
-                    v[4 * i] += x.x;
-                    v[4 * i + 1] += x.y;
-                    v[4 * i + 2] += x.z;
-                    v[4 * i + 3] += x.w;
+                  for (int j = 0; j < 4; ++j) {
+                    if (s0 + j < w.nsplit) {
+                      const float4* src = reinterpret_cast<const float4*>(
+                          p.splitk_ws +
+                          ((static_cast<size_t>(ctr) * w.nsplit + s0 + j) * kBM + t * 128 + row_in_acc) *
+                              kBN +
+                          c * 32);
+#pragma unroll
+                      for (int i = 0; i < 8; ++i) x[j][i] = __ldcg(src + i);
+                    }
+                  }
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (s0 + j < w.nsplit) {
+#pragma unroll
+                      for (int i = 0; i < 8; ++i) {
+                        v[4 * i] += x[j][i].x;
+                        v[4 * i + 1] += x[j][i].y;
+                        v[4 * i + 2] += x[j][i].z;
+                        v[4 * i + 3] += x[j][i].w;
+                      }
+                    }
                   }
                 }
                 store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);

@@ -66,13 +66,24 @@ struct TcGemmF32x3 {
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
   struct Unit {
-    int m0, n0, tile, split, kb0, kbn;
+    int m0, n0, tile, split, nsplit, slot, kb0, kbn;
   };
 
-  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb) {
+  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb,
+                                                     int first_split, int factor) {
     Unit w;
-    w.tile = u / kSplitK;
-    w.split = u - w.tile * kSplitK;
+    if (u < first_split) {
+      w.tile = u;
+      w.split = 0;
+      w.nsplit = 1;
+      w.slot = 0;
+    } else {
+      const int v = u - first_split;
+      w.tile = first_split + v / factor;
+      w.split = v - (w.tile - first_split) * factor;
+      w.nsplit = factor;
+      w.slot = v;
+    }
     int mb, nb;
     if constexpr (kGroup > 1) {
       const int per_group = kGroup * tiles_n;
@@ -88,7 +99,7 @@ struct TcGemmF32x3 {
     }
     w.m0 = mb * kBM;
     w.n0 = nb * kBN;
-    const int per = (num_kb + kSplitK - 1) / kSplitK;
+    const int per = (num_kb + w.nsplit - 1) / w.nsplit;
     w.kb0 = w.split * per;
     int kb1 = w.kb0 + per;
     if (kb1 > num_kb) kb1 = num_kb;
@@ -126,7 +137,9 @@ struct TcGemmF32x3 {
     const int tiles_m = (p.M + kBM - 1) / kBM;
     const int tiles_n = (p.N + kBN - 1) / kBN;
     const int num_kb = (p.K + kBK - 1) / kBK;
-    const int num_units = tiles_m * tiles_n * kSplitK;
+    const int first_split = p.split_first_tile;
+    const int split_factor = p.split_factor > 0 ? p.split_factor : 1;
+    const int num_units = first_split + (tiles_m * tiles_n - first_split) * split_factor;
 
     if (threadIdx.x == 0) {
       for (int s = 0; s < kStages; ++s) {
@@ -161,7 +174,7 @@ struct TcGemmF32x3 {
         uint32_t it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
@@ -194,7 +207,7 @@ struct TcGemmF32x3 {
         uint32_t it = 0, chunk_it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           for (int kb0 = 0; kb0 < w.kbn && ok; kb0 += kChunk, ++chunk_it) {
             const uint32_t ab = chunk_it & 1u;
             const uint32_t aph = (chunk_it >> 1) & 1u;
@@ -258,7 +271,7 @@ struct TcGemmF32x3 {
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         for (int kb = 0; kb < w.kbn; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -295,7 +308,7 @@ struct TcGemmF32x3 {
       uint32_t chunk_it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb);
+        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         float acc[ACC_PER_THREAD];
 #pragma unroll
         for (int i = 0; i < ACC_PER_THREAD; ++i) acc[i] = 0.f;
@@ -335,8 +348,9 @@ struct TcGemmF32x3 {
           for (int c = 0; c < PIECES; ++c) {
             const int col = w.n0 + col_half0 + c * 32;
             if (row < p.M && col < p.N) {
-              float* dst = (kSplitK > 1)
-                               ? p.splitk_ws + (static_cast<size_t>(w.split) * p.M + row) * p.N + col
+              float* dst = (w.nsplit > 1)
+                               ? p.splitk_ws + (static_cast<size_t>(w.slot) * kBM + t * 128 + row_in_acc) * kBN +
+                                     col_half0 + c * 32
                                : Cout + static_cast<size_t>(row) * p.ldc + col;
               float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
@@ -347,29 +361,37 @@ struct TcGemmF32x3 {
             }
           }
         }
-        if constexpr (kSplitK > 1) {
+        if (w.nsplit > 1) {
+          const int ctr = w.tile - first_split;
           __threadfence();
           named_bar_sync(1, NUM_EPI_THREADS);
           if (epi_tid == 0) {
-            const unsigned int old = atomicAdd(&p.tile_counters[w.tile], 1u);
-            bars->last_flag = (old == static_cast<unsigned int>(kSplitK - 1)) ? 1u : 0u;
-            if (old == static_cast<unsigned int>(kSplitK - 1)) p.tile_counters[w.tile] = 0u;
+            const unsigned int old = atomicAdd(&p.tile_counters[ctr], 1u);
+            bars->last_flag = (old == static_cast<unsigned int>(w.nsplit - 1)) ? 1u : 0u;
+            if (old == static_cast<unsigned int>(w.nsplit - 1)) p.tile_counters[ctr] = 0u;
           }
           named_bar_sync(1, NUM_EPI_THREADS);
           if (bars->last_flag != 0u) {
             __threadfence();
+            // One partial at a time: the accumulating warps have no registers to spare for
+            // deeper prefetch (more loads in flight made ptxas spill inside the main loop).
+#pragma unroll 1
             for (int t = 0; t < MT; ++t) {
               const int row = w.m0 + t * 128 + row_in_acc;
               if (row >= p.M) continue;
+#pragma unroll 1
               for (int c = 0; c < PIECES; ++c) {
                 const int col = w.n0 + col_half0 + c * 32;
                 if (col >= p.N) continue;
                 float v[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                for (int s = 0; s < kSplitK; ++s) {
+#pragma unroll 1
+                for (int s = 0; s < w.nsplit; ++s) {
                   const float4* src = reinterpret_cast<const float4*>(
-                      p.splitk_ws + (static_cast<size_t>(s) * p.M + row) * p.N + col);
+                      p.splitk_ws +
+                      ((static_cast<size_t>(ctr) * w.nsplit + s) * kBM + t * 128 + row_in_acc) * kBN +
+                      col_half0 + c * 32);
 #pragma unroll
                   for (int i = 0; i < 8; ++i) {
                     const float4 x = __ldcg(src + i);
