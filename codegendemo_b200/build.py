@@ -45,21 +45,16 @@ def build_library(force: bool = False) -> str:
 
 def prebuilt_configs():
     """Configs compiled ahead of time, so that a GPU box needs no nvcc for the smoke run and the bench."""
-    from codegendemo_b200.kcg.matmul_op import default_config
+    from codegendemo_b200.kcg.matmul_op import default_config, tuned_config
     from codegendemo_b200.kcg.Utils import EnumKernelDType as E
-    big = dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3)
     simt = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
                 THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
                 WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
-    cases = [
-        (1024, 1024, 1024, E.float32, dict(BLOCK_SIZE_N=128)),
-        (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128)),
-        (4096, 4096, 4096, E.float32, simt),
-        (8192, 8192, 8192, E.bfloat16, big),
-    ]
+    cfgs = [tuned_config(1024, 1024, 1024, E.float32), tuned_config(4096, 4096, 4096, E.float32),
+            default_config(4096, 4096, 4096, E.float32, **simt), tuned_config(8192, 8192, 8192, E.bfloat16)]
     for g in (1, 2, 4, 8):
-        cases.append((32768 // g, 8192, 8192, E.bfloat16, big))
-    return [default_config(m, n, k, dt, **keys) for (m, n, k, dt, keys) in cases]
+        cfgs.append(tuned_config(32768 // g, 8192, 8192, E.bfloat16))
+    return cfgs
 
 
 def prebuild_kernels(verbose: bool = True) -> int:

@@ -263,6 +263,23 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
     const int splitk = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
     if (splitk > K / bk) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U %d exceeds the %d K blocks", splitk, K / bk);
+  } else if (want == KCG_KERNEL_TCGEN05_PAIR) {
+    // CTA pairs: each CTA holds BM/2 rows of the tile and BN/2 columns of B
+    const int f32 = (dt == KCG_DTYPE_FLOAT32) ? 1 : 0;
+    if (f32 ? (bm != 256 && bm != 512) : (bm != 256 && bm != 512))
+      return fail(KCG_E_BAD_CONFIG, "the CTA-pair kernels need BLOCK_SIZE_M = 256 or 512 (128 or 256 rows per CTA)");
+    if ((bm / 256) * bn > (f32 ? 256 : 512))
+      return fail(KCG_E_BAD_CONFIG, "accumulators of the tile exceed the TMEM columns available");
+    const int splitk = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
+    if (!f32 && splitk > 1) return fail(KCG_E_BAD_CONFIG, "the 16-bit CTA-pair kernel does not split K");
+    if (splitk > K / bk) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U %d exceeds the %d K blocks", splitk, K / bk);
+    auto ok = [&](int st) { return bn % 2 == 0 && kcg::tc_config_error(dt, bm / 2, bn / 2, bk, st, f32) == 0; };
+    int st = (opts && opts->num_stages > 0) ? opts->num_stages : 2;
+    if (!(opts && opts->num_stages > 0) && c[KCG_CFG_SHARED_PREFETCH])
+      while (st < 7 && ok(st + 1)) ++st;
+    if (!ok(st)) return fail(KCG_E_BAD_CONFIG, "tile %dx%dx%d / %d stages not buildable by the CTA-pair kernel", bm, bn, bk, st);
+    if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
+    r->stages = st;
   } else if (want == KCG_KERNEL_SIMT) {
     if (int e = check_simt(c)) return e;
     r->stages = c[KCG_CFG_SHARED_PREFETCH] ? 2 : 1;
@@ -430,6 +447,14 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
     out->grid[0] = units < r.num_sms ? units : r.num_sms;  // persistent CTAs
     out->block[0] = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 512 : 192;
     out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm, bn, bk, r.stages, x3);
+  } else if (r.kernel == KCG_KERNEL_TCGEN05_PAIR) {
+    const int f32 = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32) ? 1 : 0;
+    const int units = tiles * lsu;
+    const int pairs = units < r.num_sms / 2 ? units : r.num_sms / 2;
+    out->grid[0] = 2 * pairs;  // persistent clusters of two CTAs
+    out->cluster[0] = 2;
+    out->block[0] = f32 ? 512 : 192;
+    out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm / 2, bn / 2, bk, r.stages, f32);
   } else if (r.kernel == KCG_KERNEL_SIMT) {
     // grid/block as the reference derives them (Optimizer.cc:20,336; Rewriter.cc:726-761)
     out->grid[0] = tiles;
@@ -642,8 +667,11 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
   p.split_first_tile = (M / (info->bm > 0 ? info->bm : 1)) * (N / (info->bn > 0 ? info->bn : 1));
   p.split_factor = 1;
   int grid0 = info->grid[0];
-  if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1) {
-    const kcg::TcLayout L = kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
+  const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
+  if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 || pair) {
+    // the pair kernel loads per-CTA slices: BM/2 rows of A, BN/2 columns of B
+    const kcg::TcLayout L = pair ? kcg::make_tc_layout(info->dtype, info->bm / 2, info->bn / 2, info->bk, info->atrans)
+                                 : kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
     if (info->atrans) {
       if (int e = encode_map(s, &p.tmA, info->dtype, A, M, K, static_cast<uint64_t>(M) * eb, L.a_box_inner,
                              L.a_box_outer, L.a_tma_swizzle))
@@ -661,9 +689,13 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
     // (KCG_TAIL_SPLIT=0 turns that off).
     const int T = (M / info->bm) * (N / info->bn);
     const int num_kb = K / info->bk;
-    const int G = info->reserved[0] > 0 ? info->reserved[0] : 148;
+    const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
+    const int G = pair ? nsm / 2 : nsm;  // work units that run at once (CTAs, or CTA pairs)
+    const bool can_split = !pair || info->dtype == KCG_DTYPE_FLOAT32;
     int first = T, factor = 1;
-    if (info->splitk > 1) {
+    if (!can_split) {
+      // the 16-bit pair kernel does not split K; grid as compiled
+    } else if (info->splitk > 1) {
       first = 0;
       factor = info->splitk;
     } else {
@@ -676,10 +708,11 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
         // Worth it only when the time saved on the last wave exceeds the cost of the reduction
         // (partials through L2, one extra round trip): estimate the tile's main-loop time from
         // a per-SM rate of ~10 MFLOP/us (16-bit) or ~1.4 MFLOP/us useful (fp32 as 3xTF32).
-        const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel == KCG_KERNEL_TCGEN05) ? 1.4
+        const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1) ? 1.4
                                     : (info->dtype == KCG_DTYPE_FLOAT32)                                     ? 4.5
                                                                                                              : 10.0;
-        const double tile_us = 2.0 * info->bm * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
+        const double tile_us =
+            2.0 * (info->bm / (pair ? 2 : 1)) * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
         if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= 20.0) {
           first = T - rem;
           factor = f;
@@ -687,7 +720,7 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
       }
     }
     const int units = first + (T - first) * factor;
-    grid0 = units < G ? units : G;
+    if (can_split) grid0 = (units < G ? units : G) * (pair ? 2 : 1);
     p.split_first_tile = first;
     p.split_factor = factor;
     if (factor > 1) {
@@ -695,7 +728,7 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
       const size_t slots = static_cast<size_t>(T - first) * factor;
       const size_t need = slots * info->bm * info->bn * sizeof(float);
       if (int e = grow(&s->ws, &s->ws_bytes, need)) return e;
-      const size_t tiles = static_cast<size_t>(T - first);
+      const size_t tiles = static_cast<size_t>(T - first) * (pair ? 2 : 1);  // one counter per CTA half
       if (s->counters_n < tiles) {
         size_t have = s->counters_n * 4;
         if (int e = grow(&s->counters, &have, tiles * 4)) return e;

@@ -41,6 +41,23 @@ extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);
 }
+#elif KCG_VARIANT == KCG_VARIANT_TCGEN05_PAIR && KCG_DTYPE == KCG_DT_F32
+#include "gemm_tcgen05_f32x3.cuh"
+#ifndef KCG_CHUNK
+#define KCG_CHUNK ((128 / KCG_BK) > 0 ? (128 / KCG_BK) : 1)
+#endif
+using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK, 1>;
+extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
+#elif KCG_VARIANT == KCG_VARIANT_TCGEN05_PAIR
+#include "gemm_tcgen05_pair.cuh"
+using Gemm = kcg::TcGemmPair<KCG_DTYPE, KCG_BM / 256, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_GROUP>;
+extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
 #elif KCG_VARIANT == KCG_VARIANT_SIMT
 #include "gemm_simt.cuh"
 using Gemm = kcg::SimtGemm<KCG_T, KCG_BM, KCG_BN, KCG_BK, KCG_TM, KCG_TN, KCG_BLM, KCG_BLN, KCG_WLM,

@@ -21,6 +21,8 @@
 #define KCG_VARIANT_TCGEN05 2  // TMA + tcgen05/TMEM kernel (bf16, fp16, fp32 as 3xTF32)
 #define KCG_VARIANT_TF32X1 3   // tcgen05 single-pass TF32 (fp32 in, reduced accuracy; comparison only)
 
+#define KCG_VARIANT_TCGEN05_PAIR 4  // tcgen05 cta_group::2 on clusters of two CTAs (fp16 / bf16)
+
 // Device status word values (status[0]); 0 = ok.
 #define KCG_ST_OK 0u
 #define KCG_ST_TIMEOUT_PRODUCER 1u

@@ -28,14 +28,24 @@
 
 namespace kcg {
 
-template <int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK, int kGroup, int kChunk>
+// kPair = 1 runs the same pipeline on clusters of two CTAs sharing each MMA
+// (tcgen05 cta_group::2, M = 256): a CTA then holds kBM/2 rows of the tile and loads and
+// splits only half of the B tile (kBN/2 columns); the leader CTA (even rank) issues the
+// MMAs once the splitters of BOTH CTAs have arrived, and frees stages / publishes
+// accumulators in both CTAs with one commit each. Halving the B operand traffic per SM
+// lifts the shared-memory bound of the single-CTA form.
+template <int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK, int kGroup, int kChunk,
+          int kPair = 0>
 struct TcGemmF32x3 {
   static constexpr int kDType = KCG_DT_F32;
-  static_assert(tc_config_error(kDType, kBM, kBN, kBK, kStages, 1) == 0,
+  static constexpr int NCTA = kPair ? 2 : 1;
+  static constexpr int R = kBM / NCTA;     // rows of the tile held by one CTA
+  static constexpr int BNL = kBN / NCTA;   // B columns loaded by one CTA
+  static_assert(tc_config_error(kDType, R, BNL, kBK, kStages, 1) == 0,
                 "config not buildable by the 3xTF32 kernel");
-  static constexpr TcLayout L = make_tc_layout(kDType, kBM, kBN, kBK, kATrans);
+  static constexpr TcLayout L = make_tc_layout(kDType, R, BNL, kBK, kATrans);
   static constexpr int UMMA_K = 8;
-  static constexpr int MT = kBM / 128;
+  static constexpr int MT = R / 128;
   static constexpr int ACC_COLS = MT * kBN;
   static_assert(2 * ACC_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
   static_assert(kBN % 64 == 0, "each epilogue warp drains whole 32-column pieces of its column half");
@@ -50,8 +60,8 @@ struct TcGemmF32x3 {
   static constexpr int PIECES = HALF_COLS / 32;
   static constexpr int ACC_PER_THREAD = MT * HALF_COLS;
   static_assert(ACC_PER_THREAD <= 128, "register accumulators per thread");
-  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, kBM, kBN, kBK, kStages, 1);
-  static constexpr uint32_t IDESC = make_instr_desc(FMT_TF32, kATrans ? 1u : 0u, 1u, 128u, kBN);
+  static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, R, BNL, kBK, kStages, 1);
+  static constexpr uint32_t IDESC = make_instr_desc(FMT_TF32, kATrans ? 1u : 0u, 1u, kPair ? 256u : 128u, kBN);
 
   struct Barriers {
     uint64_t full[kStages];
@@ -145,11 +155,11 @@ struct TcGemmF32x3 {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
-        mbar_init(&bars->split_full[s], NUM_SPLIT_THREADS);
+        mbar_init(&bars->split_full[s], 4 * NCTA);  // one arrival per splitter warp of each CTA
       }
       for (int a = 0; a < 2; ++a) {
         mbar_init(&bars->tmem_full[a], 1);
-        mbar_init(&bars->tmem_empty[a], NUM_EPI_THREADS);
+        mbar_init(&bars->tmem_empty[a], 8 * NCTA);  // one arrival per accumulating warp of each CTA
       }
       bars->abort_flag = 0u;
       bars->last_flag = 0u;
@@ -157,13 +167,24 @@ struct TcGemmF32x3 {
       fence_proxy_async_smem();
     }
     if (warp == 1) {
-      tmem_alloc(&bars->tmem_base, TMEM_COLS);
-      tmem_relinquish();
+      if constexpr (kPair) {
+        tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
+        tmem_relinquish_pair();
+      } else {
+        tmem_alloc(&bars->tmem_base, TMEM_COLS);
+        tmem_relinquish();
+      }
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
+    const uint32_t rank = kPair ? cluster_cta_rank() : 0u;  // 0 = leader
+    const int unit0 = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int unit_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int row_base = static_cast<int>(rank) * R;     // this CTA's first row inside the tile
+    const int bcol_base = static_cast<int>(rank) * BNL;  // this CTA's first B column inside the tile
 
     if (warp < 4) {
       reg_dec<56>();
@@ -173,7 +194,7 @@ struct TcGemmF32x3 {
         tma_prefetch_desc(&p.tmB);
         uint32_t it = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        for (int u = unit0; u < num_units && ok; u += unit_stride) {
           const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
@@ -190,23 +211,23 @@ struct TcGemmF32x3 {
 #pragma unroll
             for (int j = 0; j < L.a_boxes; ++j) {
               if constexpr (kATrans) {
-                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.m0 + j * L.atom, k0);
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.m0 + row_base + j * L.atom, k0);
               } else {
                 tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s],
-                            k0 + j * L.a_box_inner, w.m0);
+                            k0 + j * L.a_box_inner, w.m0 + row_base);
               }
             }
 #pragma unroll
             for (int j = 0; j < L.b_boxes; ++j) {
-              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, k0);
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + bcol_base + j * L.atom, k0);
             }
           }
         }
-      } else if (warp == 1 && lane == 0) {
-        // -------------------------------------------------------- MMA issuer
+      } else if (warp == 1 && lane == 0 && rank == 0u) {
+        // ---------------------------- MMA issuer (in a pair: the leader CTA only)
         uint32_t it = 0, chunk_it = 0;
         bool ok = true;
-        for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        for (int u = unit0; u < num_units && ok; u += unit_stride) {
           const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
           for (int kb0 = 0; kb0 < w.kbn && ok; kb0 += kChunk, ++chunk_it) {
             const uint32_t ab = chunk_it & 1u;
@@ -247,20 +268,38 @@ struct TcGemmF32x3 {
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                   const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
-                                               : t * 128 * (L.a_box_bytes / kBM);
+                                               : t * 128 * (L.a_box_bytes / R);
                   const uint64_t adesc =
                       make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
                   const uint64_t adesc_lo = make_smem_desc(sa + STAGE_HI + a_t + a_off, L.a_lbo,
                                                            L.a_sbo, L.a_desc_swizzle);
                   const uint32_t d = tmem_acc + t * kBN;
-                  umma_ss<true>(d, adesc_lo, bdesc, IDESC, first);
-                  umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
-                  umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
+                  if constexpr (kPair) {
+                    umma_ss_pair<true>(d, adesc_lo, bdesc, IDESC, first);
+                    umma_ss_pair<true>(d, adesc, bdesc_lo, IDESC, 1u);
+                    umma_ss_pair<true>(d, adesc, bdesc, IDESC, 1u);
+                  } else {
+                    umma_ss<true>(d, adesc_lo, bdesc, IDESC, first);
+                    umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
+                    umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
+                  }
                 }
               }
-              umma_commit(&bars->empty[s]);
+              if constexpr (kPair) {  // the stage is free in both CTAs once these MMAs retire
+                umma_commit_pair(smem_u32(&bars->empty[s]));
+                umma_commit_pair(map_to_cta(smem_u32(&bars->empty[s]), 1u));
+              } else {
+                umma_commit(&bars->empty[s]);
+              }
             }
-            if (ok) umma_commit(&bars->tmem_full[ab]);
+            if (ok) {
+              if constexpr (kPair) {
+                umma_commit_pair(smem_u32(&bars->tmem_full[ab]));
+                umma_commit_pair(map_to_cta(smem_u32(&bars->tmem_full[ab]), 1u));
+              } else {
+                umma_commit(&bars->tmem_full[ab]);
+              }
+            }
           }
         }
       }
@@ -270,7 +309,7 @@ struct TcGemmF32x3 {
       const int stid = threadIdx.x - 128;
       uint32_t it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+      for (int u = unit0; u < num_units && ok; u += unit_stride) {
         const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         for (int kb = 0; kb < w.kbn; ++kb, ++it) {
           const uint32_t s = it % kStages;
@@ -293,7 +332,14 @@ struct TcGemmF32x3 {
             lo[i] = l;
           }
           fence_proxy_async_smem();
-          mbar_arrive(&bars->split_full[s]);
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars->split_full[s]), 0u));
+            } else {
+              mbar_arrive(&bars->split_full[s]);
+            }
+          }
         }
       }
     } else {
@@ -307,7 +353,7 @@ struct TcGemmF32x3 {
       float* Cout = reinterpret_cast<float*>(p.C);
       uint32_t chunk_it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+      for (int u = unit0; u < num_units && ok; u += unit_stride) {
         const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         float acc[ACC_PER_THREAD];
 #pragma unroll
@@ -337,19 +383,27 @@ struct TcGemmF32x3 {
             }
           }
           tc_fence_before_sync();
-          mbar_arrive(&bars->tmem_empty[ab]);
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[ab]), 0u));
+            } else {
+              mbar_arrive(&bars->tmem_empty[ab]);
+            }
+          }
         }
         if (!ok) break;
         // ---- tile (or split partial) complete in registers: store
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
-          const int row = w.m0 + t * 128 + row_in_acc;
+          const int row = w.m0 + row_base + t * 128 + row_in_acc;
 #pragma unroll
           for (int c = 0; c < PIECES; ++c) {
             const int col = w.n0 + col_half0 + c * 32;
             if (row < p.M && col < p.N) {
               float* dst = (w.nsplit > 1)
-                               ? p.splitk_ws + (static_cast<size_t>(w.slot) * kBM + t * 128 + row_in_acc) * kBN +
+                               ? p.splitk_ws +
+                                     (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN +
                                      col_half0 + c * 32
                                : Cout + static_cast<size_t>(row) * p.ldc + col;
               float4* d4 = reinterpret_cast<float4*>(dst);
@@ -362,7 +416,7 @@ struct TcGemmF32x3 {
           }
         }
         if (w.nsplit > 1) {
-          const int ctr = w.tile - first_split;
+          const int ctr = (w.tile - first_split) * NCTA + static_cast<int>(rank);  // per CTA half
           __threadfence();
           named_bar_sync(1, NUM_EPI_THREADS);
           if (epi_tid == 0) {
@@ -377,7 +431,7 @@ struct TcGemmF32x3 {
             // deeper prefetch (more loads in flight made ptxas spill inside the main loop).
 #pragma unroll 1
             for (int t = 0; t < MT; ++t) {
-              const int row = w.m0 + t * 128 + row_in_acc;
+              const int row = w.m0 + row_base + t * 128 + row_in_acc;
               if (row >= p.M) continue;
 #pragma unroll 1
               for (int c = 0; c < PIECES; ++c) {
@@ -390,7 +444,9 @@ struct TcGemmF32x3 {
                 for (int s = 0; s < w.nsplit; ++s) {
                   const float4* src = reinterpret_cast<const float4*>(
                       p.splitk_ws +
-                      ((static_cast<size_t>(ctr) * w.nsplit + s) * kBM + t * 128 + row_in_acc) * kBN +
+                      ((static_cast<size_t>(w.tile - first_split) * w.nsplit + s) * kBM + row_base + t * 128 +
+                       row_in_acc) *
+                          kBN +
                       col_half0 + c * 32);
 #pragma unroll
                   for (int i = 0; i < 8; ++i) {
@@ -420,10 +476,18 @@ struct TcGemmF32x3 {
     }
     tc_fence_before_sync();
     __syncthreads();
+    if constexpr (kPair) {
+      __syncwarp();
+      cluster_sync_all();  // the peer's shared memory and TMEM stay valid until both CTAs are done
+    }
     if (warp == 1) {
       __syncwarp();
       tc_fence_after_sync();
-      tmem_dealloc(tmem_base, TMEM_COLS);
+      if constexpr (kPair) {
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+      } else {
+        tmem_dealloc(tmem_base, TMEM_COLS);
+      }
     }
   }
 

@@ -27,11 +27,22 @@ def getTempJsonFileName(startIndex: int, endIndex: int, outDir: str) -> str:
 
 def _tensor_core(cfg: Dict) -> bool:
     v = cfg.get(kw.KEY_KERNEL_VARIANT, 0)
-    if v in (2, 3):
+    if v in (2, 3, 4):
         return True
     if v == 1:
         return False
     return TuningSpaceChecker_Matmul.tcgen05_tile_ok(cfg)
+
+
+def _per_cta(cfg: Dict) -> Dict:
+    """The operand tile one CTA holds: for the CTA-pair kernels (variant 4) half the rows and half
+    the B columns of the config's tile; the config itself otherwise."""
+    if cfg.get(kw.KEY_KERNEL_VARIANT, 0) != 4:
+        return cfg
+    half = dict(cfg)
+    half[kw.KEY_BLOCK_SIZE_M] = cfg[kw.KEY_BLOCK_SIZE_M] // 2
+    half[kw.KEY_BLOCK_SIZE_N] = cfg[kw.KEY_BLOCK_SIZE_N] // 2
+    return half
 
 
 # (keys the rule reads, predicate). A rule runs once all its keys are bound.
@@ -62,6 +73,8 @@ def _rules() -> List[Tuple[Tuple[str, ...], Callable[[Dict], bool]]]:
         return t > 0 and w >= t and w % t == 0 and cfg[kw.KEY_THREAD_SIZE_N] % w == 0
 
     def shm(cfg):
+        if cfg.get(kw.KEY_KERNEL_VARIANT, 0) == 4:
+            return TuningSpaceChecker_Matmul.check_shm_size(_per_cta(cfg))
         return TuningSpaceChecker_Matmul.check_shm_size(cfg)
 
     def simt_loads(cfg):
@@ -76,11 +89,18 @@ def _rules() -> List[Tuple[Tuple[str, ...], Callable[[Dict], bool]]]:
         st = cfg.get(kw.KEY_NUM_STAGES, 0)
         if not _tensor_core(cfg) or st <= 0:
             return True
-        return TuningSpaceChecker_Matmul.tcgen05_tile_ok(cfg, st)
+        return TuningSpaceChecker_Matmul.tcgen05_tile_ok(_per_cta(cfg), st)
 
     def forced_tile(cfg):
         # KERNEL_VARIANT 2/3 demands a tile the tensor-core kernel can build
-        return cfg.get(kw.KEY_KERNEL_VARIANT, 0) not in (2, 3) or TuningSpaceChecker_Matmul.tcgen05_tile_ok(cfg)
+        v = cfg.get(kw.KEY_KERNEL_VARIANT, 0)
+        if v == 4:  # CTA pair: each CTA holds half of the tile's rows and half of its B columns
+            bm, bn = cfg[kw.KEY_BLOCK_SIZE_M], cfg[kw.KEY_BLOCK_SIZE_N]
+            fp32 = int(cfg.get(kw.KEY_DTYPE_A, cfg[kw.KEY_DTYPE_C])) == 4
+            if bm not in (256, 512) or bn % 2 or (bm // 256) * bn > (256 if fp32 else 512):
+                return False
+            return TuningSpaceChecker_Matmul.tcgen05_tile_ok(_per_cta(cfg))
+        return v not in (2, 3) or TuningSpaceChecker_Matmul.tcgen05_tile_ok(cfg)
 
     tile = (kw.KEY_BLOCK_SIZE_M, kw.KEY_BLOCK_SIZE_N, kw.KEY_BLOCK_SIZE_K, kw.KEY_DTYPE_C)
     return [

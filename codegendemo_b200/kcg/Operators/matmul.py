@@ -113,7 +113,7 @@ class KernelArgMatmul:
 
     def usesTensorCores(self) -> bool:
         """True when the config's tile is one the tcgen05 kernel can build (what AUTO resolves to)."""
-        if self.KERNEL_VARIANT in (2, 3):
+        if self.KERNEL_VARIANT in (2, 3, 4):
             return True
         if self.KERNEL_VARIANT == 1:
             return False
@@ -132,7 +132,8 @@ class KernelArgMatmul:
             assert (self.BLOCK_LAYOUT_N * self.WARP_LAYOUT_N) == (self.BLOCK_SIZE_N // self.THREAD_SIZE_N)
             assert self.WARP_LAYOUT_N * self.WARP_LAYOUT_M == self.WARP_SIZE
         # shm size check
-        assert 2 * (self.BLOCK_SIZE_M + self.BLOCK_SIZE_N) * self.BLOCK_SIZE_K * sizeof(self.__dataType_A) \
+        per_cta = 2 if self.KERNEL_VARIANT == 4 else 1  # a CTA pair splits the tile's operands
+        assert 2 * (self.BLOCK_SIZE_M + self.BLOCK_SIZE_N) * self.BLOCK_SIZE_K * sizeof(self.__dataType_A) // per_cta \
             <= MAX_SHARED_BYTES
         if verbose:
             print("===== config check ok!")

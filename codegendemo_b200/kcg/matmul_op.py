@@ -35,6 +35,33 @@ def default_config(M: int, N: int, K: int, dtype: EnumKernelDType, **keys) -> Ke
     return kpm
 
 
+def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: int = 0, db=None) -> KernelArgMatmul:
+    """Best known config of a shape: the kernel database's entry when the shape was tuned, else a
+    rule of thumb from the B200 measurements (CTA-pair kernels once their larger tiles still fill
+    the 74 pairs for several waves, single-CTA 256x256 / 128x256 tiles otherwise)."""
+    from codegendemo_b200.kcg.InfoDb import KernelDb
+    db = db if db is not None else KernelDb()
+    hit = db.lookup(M, N, K, int(dtype), isATranspose)
+    if hit is not None:
+        return KernelArgMatmul.fromJson(hit["config"])
+    pairs = 74
+    if int(dtype) == int(EnumKernelDType.float32):
+        if M % 256 == 0 and N % 256 == 0 and K % 32 == 0 and (M // 256) * (N // 256) >= pairs:
+            return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
+                                  BLOCK_SIZE_K=32, NUM_STAGES=3, isATranspose=isATranspose)
+        if N % 256 == 0 and K % 16 == 0:
+            return default_config(M, N, K, dtype, BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4,
+                                  isATranspose=isATranspose)
+        return default_config(M, N, K, dtype, BLOCK_SIZE_N=128 if N % 128 == 0 else 64, isATranspose=isATranspose)
+    if M % 512 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 512) * (N // 256) >= 6 * pairs:
+        return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
+                              NUM_STAGES=4, isATranspose=isATranspose)
+    if M % 256 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 256) * (N // 256) >= 148:
+        return default_config(M, N, K, dtype, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3,
+                              isATranspose=isATranspose)
+    return default_config(M, N, K, dtype, isATranspose=isATranspose)
+
+
 def build_kernel(kpm: KernelArgMatmul, deviceId: int = 0):
     """Compile (or fetch from the cubin cache) and wrap one config; returns (UserInputs, CompiledKernel)."""
     kpm.check()
@@ -55,7 +82,8 @@ def matmul(a, b, c=None, **keys):
     assert K == K2 and a.is_contiguous() and b.is_contiguous()
     if c is None:
         c = torch.empty((M, N), dtype=a.dtype, device=a.device)
-    kpm = default_config(M, N, K, FromTorchType(a.dtype), **keys)
+    dt = FromTorchType(a.dtype)
+    kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
     _, kern = build_kernel(kpm, a.device.index or 0)
     kern.run(a, b, c)
     return c

@@ -52,6 +52,7 @@ enum kcg_cfg_index {
 #define KCG_KERNEL_SIMT 1     /* FFMA register-tiled kernel */
 #define KCG_KERNEL_TCGEN05 2  /* TMA + tcgen05/TMEM; fp32 runs as 3xTF32 */
 #define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
+#define KCG_KERNEL_TCGEN05_PAIR 4 /* fp16/bf16 on CTA pairs (tcgen05 cta_group::2), BLOCK_SIZE_M = 256 */
 #define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
 
 /* Error codes (negative; positive values are CUresult). */

@@ -41,6 +41,21 @@ SEEDED = [
     ("bf16_splitk3_uneven", 256, 512, 1280, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=3)),
     ("fp16_1024", 1024, 1024, 1024, E.float16, "normal", dict()),
     ("fp16_atrans_bm256", 512, 512, 512, E.float16, "normal", dict(isATranspose=1, BLOCK_SIZE_M=256, NUM_STAGES=3)),
+    # CTA-pair kernels (tcgen05 cta_group::2): BLOCK_SIZE_M is the pair's tile height
+    ("pair_bf16_256", 1024, 1024, 1024, E.bfloat16, "normal", dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256)),
+    ("pair_bf16_512_two_acc", 1024, 1024, 1024, E.bfloat16, "normal", dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512)),
+    ("pair_bf16_512_atrans_bn128", 1024, 512, 512, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=128, isATranspose=1)),
+    ("pair_fp16_256_bk32", 512, 768, 512, E.float16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_K=32, BLOCK_MAPPING=0)),
+    ("pair_fp32_256", 1024, 1024, 1024, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=3)),
+    ("pair_fp32_atrans_bk16", 512, 512, 512, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, isATranspose=1)),
+    ("pair_fp32_splitk2", 256, 512, 2048, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, LOCAL_SPLIT_U=2)),
+    ("pair_fp32_512x128", 1024, 512, 512, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, NUM_STAGES=4)),
     ("naive_fp32", 256, 192, 96, E.float32, "uniform", dict(KERNEL_VARIANT=100, BLOCK_SIZE_N=64)),
     ("naive_bf16_atrans", 256, 192, 96, E.bfloat16, "normal",
      dict(KERNEL_VARIANT=100, isATranspose=1, BLOCK_SIZE_N=64, BLOCK_SIZE_K=32)),
@@ -61,8 +76,12 @@ GOLDEN = [
 ]
 GOLDEN_SHAPES = {"tile_128x64x64": (128, 64, 64), "multi_256x128x96": (256, 128, 96), "ref_tile_64x48x32": (64, 48, 32)}
 
-BIG_FP32 = ("c2_fp32_4096", 4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128))
-BIG_BF16 = ("c3_bf16_8192", 8192, 8192, 8192, E.bfloat16, dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3))
+# full-size cases run the configs the bench uses (CTA-pair kernels)
+BIG_FP32 = ("c2_fp32_4096", 4096, 4096, 4096, E.float32,
+            dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=3))
+BIG_BF16 = ("c3_bf16_8192", 8192, 8192, 8192, E.bfloat16,
+            dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=4))
+BIG_BF16_SLAB = dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3)  # 1024-row slab: single-CTA tiles
 RECT = [("c4_bf16_128x11008", 128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=4, BLOCK_SIZE_N=256)),
         ("c4_fp32_512x4096", 512, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=2)),
         ("c4_bf16_2048x4096", 2048, 4096, 4096, E.bfloat16, dict())]
@@ -77,4 +96,5 @@ def all_configs():
         out.append(default_config(m, n, k, dt, **keys))
     for (_, m, n, k, dt, keys) in [BIG_FP32, BIG_BF16] + RECT:
         out.append(default_config(m, n, k, dt, **keys))
+    out.append(default_config(BIG_BF16[1] // 8, BIG_BF16[2], BIG_BF16[3], BIG_BF16[4], **BIG_BF16_SLAB))
     return out

@@ -73,6 +73,8 @@ def test_auto_variant_falls_back_to_simt_for_reference_sized_tiles():
     (dict(M=1000), "not divisible"),
     (dict(BLOCK_SIZE_M=64, KERNEL_VARIANT=2), "not buildable"),
     (dict(LOCAL_SPLIT_U=64), "exceeds"),
+    (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=128), "CTA-pair"),
+    (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, LOCAL_SPLIT_U=2), "does not split K"),
 ])
 def test_bad_configs_are_rejected_with_kcg_error(mutate, fragment):
     kpm = default_config(1024, 1024, 1024, E.bfloat16)
@@ -123,3 +125,16 @@ def test_every_gpu_test_config_cross_compiles():
         assert os.path.getsize(path) > 1000
         seen.add(name)
     assert len(seen) >= 30
+
+
+def test_pair_variant_launch_geometry():
+    kpm = default_config(8192, 8192, 8192, E.bfloat16, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4)
+    info = compile_info(kpm.compileArgs(), num_stages=4, kernel=4)
+    assert info.kernel == _lib.KERNEL_TCGEN05_PAIR and list(info.cluster) == [2, 1, 1]
+    assert info.grid[0] == 148 and info.block[0] == 192
+    assert info.smem_bytes == 4 * (256 + 128) * 64 * 2 + 2048  # per CTA: 256 rows of A, 128 columns of B
+    f32 = default_config(4096, 4096, 4096, E.float32, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
+                         BLOCK_SIZE_K=32, NUM_STAGES=3)
+    i2 = compile_info(f32.compileArgs(), num_stages=3, kernel=4)
+    assert i2.block[0] == 512 and list(i2.cluster) == [2, 1, 1]
+    assert i2.smem_bytes == 3 * 2 * (128 + 128) * 32 * 4 + 2048  # hi + lo twins of the per-CTA slices

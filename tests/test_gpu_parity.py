@@ -132,11 +132,12 @@ def test_c3_bf16_8192_full_size_properties():
     rows = torch.randperm(M, generator=g)[:128].sort().values
     _check_row_blocks(c, A, B, rows, oracle.TOL_16BIT)
     # row-slab independence (what M-sharding relies on): a slab computed alone equals the slab of the full product
-    kslab = default_config(M // 8, N, K, dt, **keys)
+    kslab = default_config(M // 8, N, K, dt, **gpu_cases.BIG_BF16_SLAB)
     _, kern2 = build_kernel(kslab, 0)
     cs = torch.empty(M // 8, N, dtype=torch.bfloat16, device="cuda:0")
     kern2.run(a[3 * (M // 8):4 * (M // 8)], b, cs)
     kern2.checkStatus()
+    # another kernel family and tile shape, same products summed in the same K order per element
     assert torch.equal(cs, c[3 * (M // 8):4 * (M // 8)])
 
 

@@ -69,9 +69,13 @@ def test_b200_spaces_enumerate_to_buildable_configs():
     d = PathManager.tuning_configs_dir()
     cfgs = ConfigGenerator.get_cfgs(os.path.join(d, "GEMM_configs_4096_b200.json"))
     assert 20 < len(cfgs) < 400
+    assert {c[kw.KEY_KERNEL_VARIANT] for c in cfgs} == {2, 4}
     for c in cfgs:
-        assert c[kw.KEY_BLOCK_SIZE_M] in (128, 256)  # BM=64 is in the space but not buildable -> pruned
-        assert TuningSpaceChecker_Matmul.tcgen05_tile_ok(c, c[kw.KEY_NUM_STAGES])
+        assert c[kw.KEY_BLOCK_SIZE_M] in (128, 256, 512)  # BM=64 is in the space but not buildable -> pruned
+        per_cta = ConfigGenerator._per_cta(c)  # CTA-pair configs are judged on the slice one CTA holds
+        assert TuningSpaceChecker_Matmul.tcgen05_tile_ok(per_cta, c[kw.KEY_NUM_STAGES])
+        if c[kw.KEY_KERNEL_VARIANT] == 4:
+            assert c[kw.KEY_BLOCK_SIZE_M] in (256, 512)
         KernelArgMatmul.fromJson(c).check()
     simt = ConfigGenerator.get_cfgs(os.path.join(d, "GEMM_configs_4096_simt_b200.json"))
     assert len(simt) > 50
@@ -179,3 +183,26 @@ def test_m_sharded_gemm_over_two_gloo_ranks(tmp_path):
                          text=True, timeout=300, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-3000:]
     assert "SHARD_OK rank0" in out.stdout and "SHARD_OK rank1" in out.stdout
+
+
+def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
+    from codegendemo_b200.kcg.InfoDb import KernelDb
+    from codegendemo_b200.kcg.matmul_op import tuned_config
+    db = KernelDb(str(tmp_path / "db.json"))
+    assert db.lookup(4096, 4096, 4096, 4) is None
+    slow = default_config(4096, 4096, 4096, E.float32, BLOCK_SIZE_N=128).jsonfy()
+    fast = default_config(4096, 4096, 4096, E.float32, BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4).jsonfy()
+    wrong = default_config(4096, 4096, 4096, E.float32, BLOCK_SIZE_N=64).jsonfy()
+    n = db.update([{"correct": True, "kcgMs": 0.9, "tflops": 150.0, "config": slow},
+                   {"correct": True, "kcgMs": 0.64, "tflops": 214.0, "config": fast},
+                   {"correct": False, "kcgMs": 0.1, "tflops": 999.0, "config": wrong}])
+    assert n == 2 and db.lookup(4096, 4096, 4096, 4)["config"]["BLOCK_SIZE_N"] == 256
+    db.save()
+    db2 = KernelDb(str(tmp_path / "db.json"))
+    kpm = tuned_config(4096, 4096, 4096, E.float32, db=db2)
+    assert (kpm.BLOCK_SIZE_N, kpm.BLOCK_SIZE_K, kpm.NUM_STAGES) == (256, 16, 4)
+    # untuned shapes fall back to the rule of thumb
+    other = tuned_config(8192, 8192, 8192, E.bfloat16, db=db2)
+    assert other.KERNEL_VARIANT == 4 and other.BLOCK_SIZE_M == 512
+    small = tuned_config(4096, 8192, 8192, E.bfloat16, db=db2)
+    assert small.KERNEL_VARIANT == 0 and small.BLOCK_SIZE_M == 256
