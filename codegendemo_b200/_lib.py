@@ -12,7 +12,7 @@ import os
 NUM_CFG_KEYS = 31
 LIB_NAME = "libkcg_b200.so"
 
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TF32X1, KERNEL_TCGEN05_PAIR, KERNEL_NAIVE = 0, 1, 2, 3, 4, 100
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TF32X1, KERNEL_TCGEN05_PAIR, KERNEL_NAIVE, KERNEL_WAIT_PROBE = 0, 1, 2, 3, 4, 100, 101
 
 E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_LARGE = (
     -1, -2, -3, -4, -5, -6, -7)

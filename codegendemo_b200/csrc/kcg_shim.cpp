@@ -284,7 +284,7 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if (int e = check_simt(c)) return e;
     r->stages = c[KCG_CFG_SHARED_PREFETCH] ? 2 : 1;
     if (simt_smem_bytes(c) > 227 * 1024) return fail(KCG_E_BAD_CONFIG, "shared memory %d B exceeds 227 KiB", simt_smem_bytes(c));
-  } else if (want == KCG_KERNEL_NAIVE) {
+  } else if (want == KCG_KERNEL_NAIVE || want == KCG_KERNEL_WAIT_PROBE) {
     r->stages = 1;
   } else {
     return fail(KCG_E_BAD_CONFIG, "unknown kernel family %d", want);
@@ -473,7 +473,12 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
   out->bn = bn;
   out->bk = bk;
   out->stages = r.stages;
-  out->splitk = (r.kernel == KCG_KERNEL_NAIVE) ? 1 : lsu;
+  out->splitk = (r.kernel == KCG_KERNEL_NAIVE || r.kernel == KCG_KERNEL_WAIT_PROBE) ? 1 : lsu;
+  if (r.kernel == KCG_KERNEL_WAIT_PROBE) {
+    out->grid[0] = out->grid[1] = 1;
+    out->block[0] = 32;
+    out->block[1] = 1;
+  }
   out->group = c[KCG_CFG_BLOCK_MAPPING];
   out->atrans = c[KCG_CFG_IS_ATRANS] ? 1 : 0;
   out->m = M;

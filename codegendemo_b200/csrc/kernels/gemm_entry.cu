@@ -72,6 +72,32 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 extern "C" __global__ void KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   kcg::naive_gemm<KCG_T, KCG_ATRANS>(p);
 }
+#elif KCG_VARIANT == 101  // wait probe: exercises the bounded-wait / status-word path
+// One CTA waits on an mbarrier that nothing ever signals, with a 20 ms limit instead of the
+// kernels' 1 s, records the same status a GEMM role would record and returns. It never spins
+// unbounded, traps or touches memory it does not own; C is left untouched.
+#undef KCG_WAIT_LIMIT_NS
+#define KCG_WAIT_LIMIT_NS 20000000ull
+#include "ptx_sm100.cuh"
+extern "C" __global__ void KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    kcg::mbar_init(&bar, 1);
+    abort_flag = 0u;
+    kcg::fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!kcg::mbar_wait(&bar, 0u, &abort_flag)) {
+      if (atomicCAS(p.status, 0u, KCG_ST_TIMEOUT_MMA) == 0u) {
+        p.status[1] = blockIdx.x;
+        p.status[2] = 0xdeadu;
+        p.status[3] = 0u;
+      }
+    }
+  }
+}
 #else
 #error "unknown KCG_VARIANT"
 #endif

@@ -54,6 +54,7 @@ enum kcg_cfg_index {
 #define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
 #define KCG_KERNEL_TCGEN05_PAIR 4 /* fp16/bf16 on CTA pairs (tcgen05 cta_group::2), BLOCK_SIZE_M = 256 */
 #define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
+#define KCG_KERNEL_WAIT_PROBE 101 /* no GEMM: one bounded wait (20 ms) that expires -> KCG_E_DEVICE_TIMEOUT */
 
 /* Error codes (negative; positive values are CUresult). */
 #define KCG_E_BAD_CONFIG (-1)      /* config fails the reference's check() rules or the kernel's */

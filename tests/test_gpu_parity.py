@@ -196,3 +196,21 @@ def test_device_properties_and_load_errors():
     mod, fn = ctypes.c_uint64(), ctypes.c_uint64()
     rc = lib.kcg_load_binary(b"nope", b"/nonexistent/file.cubin", 0, 0, ctypes.byref(mod), ctypes.byref(fn), None, None)
     assert rc == _lib.E_IO and b"KCG Error[CUDA]" in lib.kcg_last_error()
+
+
+def test_expired_device_wait_reports_status_and_leaves_the_context_usable():
+    """Failure detection on the device, without a fault: a probe kernel waits 20 ms on a barrier nothing
+    signals, records its status word and returns; the host reads KCG_E_DEVICE_TIMEOUT and the next launch works."""
+    A, B = oracle.make_inputs(256, 256, 256, torch.bfloat16, "normal", seed=4)
+    probe = default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64)
+    _, kern = build_kernel(probe, 0)
+    a, b = A.cuda(), B.cuda()
+    c = torch.zeros(256, 256, dtype=torch.bfloat16, device="cuda:0")
+    kern.run(a, b, c)
+    with pytest.raises(_lib.KCGError) as ei:
+        kern.checkStatus()
+    assert ei.value.code == _lib.E_DEVICE_TIMEOUT and "bounded wait" in str(ei.value)
+    assert torch.count_nonzero(c).item() == 0      # the probe wrote nothing
+    kern.checkStatus()                              # status was cleared by the failing check
+    good, _, _ = run_config(default_config(256, 256, 256, E.bfloat16), A, B)   # context still fine
+    assert oracle.rel_errors(good, oracle.host_matmul(A, B))["max_rel"] <= oracle.TOL_16BIT
