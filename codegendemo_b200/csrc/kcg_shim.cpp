@@ -58,7 +58,8 @@ int fail(int code, const char* fmt, ...) {
   X(cuModuleGetFunction) X(cuModuleUnload) X(cuFuncSetAttribute) X(cuFuncGetAttribute)         \
   X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) X(cuMemAlloc) X(cuMemFree) X(cuMemsetD32)      \
   X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoH) X(cuMemcpyHtoD)                    \
-  X(cuStreamSynchronize)
+  X(cuStreamSynchronize) X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamWaitEvent) X(cuEventCreate)        \
+  X(cuEventRecord) X(cuEventDestroy)
 
 struct Driver {
   void* handle = nullptr;
@@ -128,6 +129,8 @@ struct DeviceState {
   size_t counters_n = 0;
   CUdeviceptr hbuf[3] = {0, 0, 0};  // device copies for kcg_matmul_host
   size_t hbuf_bytes[3] = {0, 0, 0};
+  CUstream hstream[3] = {nullptr, nullptr, nullptr};  // kcg_matmul_host: copy-in, compute, copy-out
+  std::vector<CUevent> hevents;                       // slab hand-off events of kcg_matmul_host
   std::unordered_map<std::string, CUtensorMap> tmaps;
 };
 constexpr int kMaxDevices = 16;
@@ -271,7 +274,6 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if ((bm / 256) * bn > (f32 ? 256 : 512))
       return fail(KCG_E_BAD_CONFIG, "accumulators of the tile exceed the TMEM columns available");
     const int splitk = c[KCG_CFG_LOCAL_SPLIT_U] > 0 ? c[KCG_CFG_LOCAL_SPLIT_U] : 1;
-    if (!f32 && splitk > 1) return fail(KCG_E_BAD_CONFIG, "the 16-bit CTA-pair kernel does not split K");
     if (splitk > K / bk) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U %d exceeds the %d K blocks", splitk, K / bk);
     auto ok = [&](int st) { return bn % 2 == 0 && kcg::tc_config_error(dt, bm / 2, bn / 2, bk, st, f32) == 0; };
     int st = (opts && opts->num_stages > 0) ? opts->num_stages : 2;
@@ -696,11 +698,8 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
     const int num_kb = K / info->bk;
     const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
     const int G = pair ? nsm / 2 : nsm;  // work units that run at once (CTAs, or CTA pairs)
-    const bool can_split = !pair || info->dtype == KCG_DTYPE_FLOAT32;
     int first = T, factor = 1;
-    if (!can_split) {
-      // the 16-bit pair kernel does not split K; grid as compiled
-    } else if (info->splitk > 1) {
+    if (info->splitk > 1) {
       first = 0;
       factor = info->splitk;
     } else {
@@ -725,7 +724,7 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
       }
     }
     const int units = first + (T - first) * factor;
-    if (can_split) grid0 = (units < G ? units : G) * (pair ? 2 : 1);
+    grid0 = (units < G ? units : G) * (pair ? 2 : 1);
     p.split_first_tile = first;
     p.split_factor = factor;
     if (factor > 1) {
@@ -801,10 +800,62 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
       if (int e = grow(&s->hbuf[i], &s->hbuf_bytes[i], bytes[i])) return e;
   }
   CUstream st = reinterpret_cast<CUstream>(stream);
-  DRV(cuMemcpyHtoDAsync(s->hbuf[0], hostA, bytes[0], st));
-  DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], st));
-  if (int e = kcg_launch_gemm(function, info, device, stream, s->hbuf[0], s->hbuf[1], s->hbuf[2])) return e;
-  DRV(cuMemcpyDtoHAsync(hostC, s->hbuf[2], bytes[2], st));
+  // Row slabs of A / C move through three streams (copy-in, compute, copy-out) so that the
+  // transfers in both directions and the kernels overlap; B goes in first. Tiles do not straddle
+  // slabs: a slab is a multiple of BLOCK_SIZE_M rows.
+  const int bm = info->bm > 0 ? info->bm : 1;
+  const int tiles_m = info->m / bm;
+  const bool tensor_core = info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 ||
+                           info->kernel == KCG_KERNEL_TCGEN05_PAIR;
+  int nslabs = 1;
+  if (tensor_core && !info->atrans && bytes[0] + bytes[2] >= (64u << 20) && tiles_m >= 4)
+    nslabs = tiles_m < 8 ? tiles_m : 8;
+  if (nslabs == 1) {
+    DRV(cuMemcpyHtoDAsync(s->hbuf[0], hostA, bytes[0], st));
+    DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], st));
+    if (int e = kcg_launch_gemm(function, info, device, stream, s->hbuf[0], s->hbuf[1], s->hbuf[2])) return e;
+    DRV(cuMemcpyDtoHAsync(hostC, s->hbuf[2], bytes[2], st));
+    DRV(cuStreamSynchronize(st));
+    return 0;
+  }
+  {
+    std::lock_guard<std::mutex> g(g_dev_mutex);
+    for (int i = 0; i < 3; ++i)
+      if (!s->hstream[i]) DRV(cuStreamCreate(&s->hstream[i], CU_STREAM_NON_BLOCKING));
+    while (s->hevents.size() < static_cast<size_t>(2 * nslabs + 2)) {
+      CUevent ev;
+      DRV(cuEventCreate(&ev, CU_EVENT_DISABLE_TIMING));
+      s->hevents.push_back(ev);
+    }
+  }
+  CUstream s_in = s->hstream[0], s_exec = s->hstream[1], s_out = s->hstream[2];
+  CUevent ev_begin = s->hevents[2 * nslabs], ev_end = s->hevents[2 * nslabs + 1];
+  DRV(cuEventRecord(ev_begin, st));  // work already queued on the caller's stream comes first
+  DRV(cuStreamWaitEvent(s_in, ev_begin, 0));
+  DRV(cuStreamWaitEvent(s_exec, ev_begin, 0));
+  DRV(cuStreamWaitEvent(s_out, ev_begin, 0));
+  DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], s_in));
+  const int base_tiles = tiles_m / nslabs, extra = tiles_m % nslabs;
+  size_t row0 = 0;
+  for (int i = 0; i < nslabs; ++i) {
+    const size_t rows = static_cast<size_t>(base_tiles + (i < extra ? 1 : 0)) * bm;
+    const size_t a_off = row0 * info->k * eb, c_off = row0 * info->n * eb;
+    DRV(cuMemcpyHtoDAsync(s->hbuf[0] + a_off, static_cast<const char*>(hostA) + a_off, rows * info->k * eb, s_in));
+    DRV(cuEventRecord(s->hevents[2 * i], s_in));
+    DRV(cuStreamWaitEvent(s_exec, s->hevents[2 * i], 0));
+    kcg_kernel_info slab = *info;  // same cubin: the kernels take M from the launch parameters
+    slab.m = static_cast<int32_t>(rows);
+    if (int e = kcg_launch_gemm(function, &slab, device, reinterpret_cast<uint64_t>(s_exec), s->hbuf[0] + a_off,
+                                s->hbuf[1], s->hbuf[2] + c_off))
+      return e;
+    DRV(cuEventRecord(s->hevents[2 * i + 1], s_exec));
+    DRV(cuStreamWaitEvent(s_out, s->hevents[2 * i + 1], 0));
+    DRV(cuMemcpyDtoHAsync(static_cast<char*>(hostC) + c_off, s->hbuf[2] + c_off, rows * info->n * eb, s_out));
+    row0 += rows;
+  }
+  DRV(cuEventRecord(ev_end, s_out));
+  DRV(cuStreamWaitEvent(st, ev_end, 0));
+  DRV(cuStreamSynchronize(s_out));
   DRV(cuStreamSynchronize(st));
   return 0;
 }
@@ -820,8 +871,11 @@ int kcg_shutdown(void) {
     if (s.status) d.p_cuMemFree(s.status);
     if (s.ws) d.p_cuMemFree(s.ws);
     if (s.counters) d.p_cuMemFree(s.counters);
-    for (int j = 0; j < 3; ++j)
+    for (int j = 0; j < 3; ++j) {
       if (s.hbuf[j]) d.p_cuMemFree(s.hbuf[j]);
+      if (s.hstream[j]) d.p_cuStreamDestroy(s.hstream[j]);
+    }
+    for (CUevent ev : s.hevents) d.p_cuEventDestroy(ev);
     s = DeviceState();
   }
   return 0;

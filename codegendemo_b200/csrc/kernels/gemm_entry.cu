@@ -52,8 +52,8 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);
 }
 #elif KCG_VARIANT == KCG_VARIANT_TCGEN05_PAIR
-#include "gemm_tcgen05_pair.cuh"
-using Gemm = kcg::TcGemmPair<KCG_DTYPE, KCG_BM / 256, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_GROUP>;
+#include "gemm_tcgen05.cuh"
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 1>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);

@@ -88,7 +88,8 @@ RECT = [("c4_bf16_128x11008", 128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=
 
 
 def all_configs():
-    out = [default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64),
+    out = [default_config(4096, 4096, 4096, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3),
+           default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64),
            default_config(256, 256, 256, E.bfloat16)]
     for (_, m, n, k, dt, _, keys) in SEEDED:
         out.append(default_config(m, n, k, dt, **keys))

@@ -74,7 +74,6 @@ def test_auto_variant_falls_back_to_simt_for_reference_sized_tiles():
     (dict(BLOCK_SIZE_M=64, KERNEL_VARIANT=2), "not buildable"),
     (dict(LOCAL_SPLIT_U=64), "exceeds"),
     (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=128), "CTA-pair"),
-    (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, LOCAL_SPLIT_U=2), "does not split K"),
 ])
 def test_bad_configs_are_rejected_with_kcg_error(mutate, fragment):
     kpm = default_config(1024, 1024, 1024, E.bfloat16)

@@ -94,6 +94,30 @@ def test_host_buffer_entry_matches_device_entry():
     assert torch.equal(hC2, c.cpu())
 
 
+def test_host_buffer_entry_pipelined_slabs_match_device_entry():
+    """Above 64 MiB of A + C the host entry moves row slabs through three streams. A slab launch may
+    K-split its last wave differently from the whole-matrix launch, so the two results agree to fp32
+    summation-order noise (a rare last-bit difference after rounding to bf16), not bit for bit."""
+    M, N, K = 4096, 4096, 4096
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=8)
+    kpm = default_config(M, N, K, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3)
+    c, kern, _ = run_config(kpm, A, B)
+    hA, hB = A.pin_memory(), B.pin_memory()
+    hC = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    before = _lib.get_lib().kcg_launch_count()
+    kern.runHost(hA, hB, hC)
+    assert _lib.get_lib().kcg_launch_count() - before == 8  # eight slabs of two tile rows
+    ref = oracle.host_matmul(A, B)
+    first = hC.clone()
+    assert oracle.rel_errors(first, ref)["max_rel"] <= oracle.TOL_16BIT
+    dev = c.cpu()
+    differing = (first != dev).float().mean().item()
+    assert differing < 1e-2 and oracle.rel_errors(first, dev.float())["max_rel"] <= 1e-2
+    hC.fill_(float("nan"))
+    kern.runHost(hA, hB, hC)  # buffers, streams and events are reused; same slabs -> same bits
+    assert torch.equal(hC, first)
+
+
 def _column_checksum_ok(c, a, b, tol):
     """1^T (A B) == (1^T A) B — a full-size property that needs no O(MNK) reference."""
     lhs = c.double().sum(0)
