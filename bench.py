@@ -372,7 +372,11 @@ def main():
            "h2d_bytes_per_step": int(hA.numel() * 2 + hB.numel() * 2) * n_gpus,
            "d2h_bytes_per_step": int(hC.numel() * 2) * n_gpus, "steps": args.e2e_steps,
            "api": "kcg_matmul_host (CompiledKernel.runHost), pinned host buffers"}
-    same = bool(torch.equal(hC, c.cpu()))
+    # The host entry runs row slabs, whose last-wave K split can differ from the whole-slab launch:
+    # equal up to fp32 summation order, i.e. a rare last-bit difference after rounding to bf16.
+    dev_c = c.cpu().float()
+    e2e_diff = float(((hC.float() - dev_c).abs().max() / dev_c.abs().max().clamp_min(1e-30)).item())
+    same = bool(e2e_diff <= 1e-2)
 
     # Optional collective, timed apart from the GEMM: all-gather of the C slabs (NCCL over NVLink).
     allgather = None
@@ -403,9 +407,12 @@ def main():
         threads = os.cpu_count() or 1
         crow = pick_cpu_rows(threads, target_s=12.0)
         sec, tf = cpu_sample(crow, threads)
+        reps = max(1, min(8, int(10.0 / max(sec, 1e-3))))  # about 10 s of host work in total
+        if reps > 1:
+            sec, tf = cpu_sample(crow, threads, repeats=reps)
         cpu_base = {"value": round(tf, 4), "unit": UNIT, "cores": threads, "kind": "port",
                     "sample": f"{crow}-row slab ({crow}x{K_SIZE} times {K_SIZE}x{N_SIZE}), torch.matmul fp32 on host "
-                              f"(the reference's oracle call), {sec:.2f} s"}
+                              f"(the reference's oracle call), best of {reps} passes of {sec:.2f} s"}
     if rank == 0:
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
@@ -413,6 +420,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload_config(n_gpus), kernel=kernel_desc), "roofline": roofline, "cpu_baseline": cpu_base, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "e2e_matches_device_result": same,
+            "e2e_max_diff_vs_device_rel": e2e_diff,
             "other_workloads": extras, "allgather_c": allgather,
         }
         print(json.dumps(line), flush=True)

@@ -41,6 +41,13 @@ SEEDED = [
     ("bf16_splitk3_uneven", 256, 512, 1280, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=3)),
     ("fp16_1024", 1024, 1024, 1024, E.float16, "normal", dict()),
     ("fp16_atrans_bm256", 512, 512, 512, E.float16, "normal", dict(isATranspose=1, BLOCK_SIZE_M=256, NUM_STAGES=3)),
+    # smallest problems: one tile, one K block (pipeline prologue == epilogue)
+    ("bf16_one_tile_one_kblock", 128, 64, 64, E.bfloat16, "uniform", dict(BLOCK_SIZE_N=64, NUM_STAGES=2)),
+    ("fp32_one_tile_one_kblock", 128, 64, 16, E.float32, "uniform", dict(BLOCK_SIZE_N=64, BLOCK_SIZE_K=16, NUM_STAGES=2)),
+    ("pair_bf16_one_tile_one_kblock", 256, 128, 64, E.bfloat16, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=128, NUM_STAGES=2)),
+    ("bf16_more_stages_than_kblocks", 128, 256, 128, E.bfloat16, "normal", dict(NUM_STAGES=4)),
+    ("pair_bf16_tail_split", 2048, 4096, 4096, E.bfloat16, "normal", dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512)),
     # CTA-pair kernels (tcgen05 cta_group::2): BLOCK_SIZE_M is the pair's tile height
     ("pair_bf16_256", 1024, 1024, 1024, E.bfloat16, "normal", dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256)),
     ("pair_bf16_512_two_acc", 1024, 1024, 1024, E.bfloat16, "normal", dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512)),
