@@ -24,8 +24,9 @@ def _newer(target: str, sources) -> bool:
 def build_library(force: bool = False) -> str:
     out = os.path.join(HERE, "libkcg_b200.so")
     srcs = [os.path.join(HERE, "csrc", "kcg_shim.cpp")]
-    deps = srcs + [os.path.join(HERE, "csrc", "kernels", "gemm_params.h"),
-                   os.path.join(os.path.dirname(HERE), "include", "kcg_b200.h")]
+    kdir = os.path.join(HERE, "csrc", "kernels")  # the allocation-free entry instantiates a kernel from these
+    deps = srcs + [os.path.join(kdir, f) for f in sorted(os.listdir(kdir))] + [
+        os.path.join(os.path.dirname(HERE), "include", "kcg_b200.h")]
     extra = os.path.join(HERE, "csrc", "kcg_noalloc.cu")
     if os.path.exists(extra):
         deps.append(extra)
@@ -57,8 +58,23 @@ def prebuilt_configs():
     return cfgs
 
 
+def prune_stale_cubins() -> None:
+    """Cubins are cached under _cache/src-<hash of the kernel sources>; drop the directories of older sources."""
+    import shutil
+    from codegendemo_b200 import _lib
+    cur = _lib.get_lib().kcg_cache_dir().decode()
+    base = os.path.dirname(cur)
+    if os.path.basename(base) != "_cache":
+        return
+    for d in os.listdir(base):
+        full = os.path.join(base, d)
+        if full != cur and (d.startswith("src-") or d.endswith(".cubin")):
+            shutil.rmtree(full) if os.path.isdir(full) else os.remove(full)
+
+
 def prebuild_kernels(verbose: bool = True) -> int:
     from codegendemo_b200.kcg.KCGCompiler import KCGCompiler
+    prune_stale_cubins()
     n = 0
     for kpm in prebuilt_configs():
         kpm.check()

@@ -10,6 +10,7 @@
 // machine without a GPU (the compile entry needs none). Nothing here computes a
 // GEMM on the host: without a driver, load/launch fail with KCG_E_NO_DRIVER.
 #include <cuda.h>
+#include <dirent.h>
 #include <dlfcn.h>
 #include <fcntl.h>
 #include <spawn.h>
@@ -17,6 +18,7 @@
 #include <sys/wait.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -331,16 +333,76 @@ std::string lib_dir() {
   return ".";
 }
 
-std::string cache_dir() {
-  const char* e = getenv("KCG_CACHE_DIR");
-  std::string d = (e && *e) ? std::string(e) : lib_dir() + "/_cache";
-  mkdir(d.c_str(), 0755);
-  return d;
-}
-
 std::string kernel_src_dir() {
   const char* e = getenv("KCG_KERNEL_SRC_DIR");
   return (e && *e) ? std::string(e) : lib_dir() + "/csrc/kernels";
+}
+
+// Tag of the kernel sources a cubin was built from: FNV-1a over the names and contents of the
+// files in the kernel source directory, in name order. Cubins live in a sub-directory named
+// after it, so an edit of any kernel header can never be served by a cubin of the old source.
+// Without sources (a deployment that ships cubins only) the newest tagged sub-directory is used.
+std::string source_tag(const std::string& cache_base) {
+  static std::mutex mu;
+  static std::string tag;
+  std::lock_guard<std::mutex> g(mu);
+  if (!tag.empty()) return tag;
+  std::vector<std::string> names;
+  const std::string dir = kernel_src_dir();
+  if (DIR* d = opendir(dir.c_str())) {
+    while (struct dirent* ent = readdir(d)) {
+      const std::string n = ent->d_name;
+      if (n.size() > 2 && n[0] != '.' &&
+          (n.rfind(".cu") == n.size() - 3 || n.rfind(".cuh") == n.size() - 4 || n.rfind(".h") == n.size() - 2))
+        names.push_back(n);
+    }
+    closedir(d);
+  }
+  if (names.empty()) {
+    std::string best;
+    time_t best_t = 0;
+    if (DIR* d = opendir(cache_base.c_str())) {
+      while (struct dirent* ent = readdir(d)) {
+        const std::string n = ent->d_name;
+        struct stat st;
+        if (n.rfind("src-", 0) == 0 && stat((cache_base + "/" + n).c_str(), &st) == 0 && S_ISDIR(st.st_mode) &&
+            (best.empty() || st.st_mtime > best_t)) {
+          best = n;
+          best_t = st.st_mtime;
+        }
+      }
+      closedir(d);
+    }
+    tag = best.empty() ? "src-none" : best;
+    return tag;
+  }
+  std::sort(names.begin(), names.end());
+  uint64_t h = 1469598103934665603ull;
+  auto mix = [&](const char* p, size_t n) {
+    for (size_t i = 0; i < n; ++i) {
+      h ^= static_cast<unsigned char>(p[i]);
+      h *= 1099511628211ull;
+    }
+  };
+  for (const std::string& n : names) {
+    mix(n.data(), n.size() + 1);
+    std::ifstream f(dir + "/" + n, std::ios::binary);
+    std::string body((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
+    mix(body.data(), body.size());
+  }
+  char buf[32];
+  snprintf(buf, sizeof(buf), "src-%012llx", static_cast<unsigned long long>(h & 0xffffffffffffull));
+  tag = buf;
+  return tag;
+}
+
+std::string cache_dir() {
+  const char* e = getenv("KCG_CACHE_DIR");
+  const std::string base = (e && *e) ? std::string(e) : lib_dir() + "/_cache";
+  mkdir(base.c_str(), 0755);
+  const std::string d = base + "/" + source_tag(base);
+  mkdir(d.c_str(), 0755);
+  return d;
 }
 
 std::string find_nvcc() {
@@ -691,6 +753,14 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
     if (int e = encode_map(s, &p.tmB, info->dtype, B, N, K, static_cast<uint64_t>(N) * eb, L.b_box_inner,
                            L.b_box_outer, L.b_tma_swizzle))
       return e;
+    // The single-pass kernel writes C with TMA stores of 32-row x 128-byte boxes taken from
+    // 128B-swizzled staging buffers; the 3xTF32 kernel stores from registers.
+    const bool x3 = eb == 4 && info->kernel != KCG_KERNEL_TF32X1;
+    if (!x3) {
+      if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(N) * eb, 128 / eb, 32,
+                             3 /*CU_TENSOR_MAP_SWIZZLE_128B*/))
+        return e;
+    }
     // K splitting: LOCAL_SPLIT_U > 1 splits every tile; otherwise only the tiles of the last,
     // partially filled wave of the persistent grid are split so that it fills the GPU
     // (KCG_TAIL_SPLIT=0 turns that off).

@@ -125,6 +125,14 @@ constexpr TcLayout make_tc_layout(int dtype, int BM, int BN, int BK, int atrans)
   return L;
 }
 
+// Epilogue staging of the single-pass kernel: each of its four epilogue warps owns two
+// 32-row x 128-byte buffers from which C leaves through TMA stores. The 3xTF32 kernel
+// stores from registers and has none. `x3` only has a meaning for fp32 data: 16-bit data always
+// runs on the single-pass kernel.
+constexpr int tc_staging_bytes(int dtype, int x3) {
+  return (dtype == KCG_DT_F32 && x3) ? 0 : 4 * 2 * 32 * 128;
+}
+
 // Shape rules of the tcgen05 kernels; returns 0 when the config is buildable.
 constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int x3) {
   const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
@@ -140,15 +148,15 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
   if (eb == 2 && (BK % 16) != 0) return 6;
   if (stages < 2 || stages > 12) return 7;
   const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
-  if (stage * stages + 2048 > 227 * 1024) return 8;
+  if (stage * stages + 2048 + tc_staging_bytes(dtype, x3) > 227 * 1024) return 8;
   return 0;
 }
 
 constexpr int tc_smem_bytes(int dtype, int BM, int BN, int BK, int stages, int x3) {
   const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
   const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
-  // +1024 alignment slack, +1024 barriers / TMEM holder / flags
-  return stage * stages + 2048;
+  // +1024 alignment slack, +1024 barriers / TMEM holder / flags, + epilogue staging
+  return stage * stages + 2048 + tc_staging_bytes(dtype, x3);
 }
 
 }  // namespace kcg

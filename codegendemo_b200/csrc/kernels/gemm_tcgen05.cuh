@@ -8,8 +8,11 @@
 //                 releases stages / publishes accumulators with tcgen05.commit.
 //                 The warp also owns the TMEM allocation.
 //   warps 2..5    epilogue: tcgen05.ld the accumulator (one TMEM lane = one C
-//                 row per thread), convert, vectorised global stores. With two
-//                 accumulator buffers it overlaps the next tile's main loop.
+//                 row per thread), convert, stage 32 x 128-byte blocks in swizzled
+//                 shared memory and write C with TMA stores (full 128-byte lines,
+//                 asynchronous). K-split partials go to the workspace with vector
+//                 stores. With two accumulator buffers the epilogue overlaps the
+//                 next tile's main loop.
 //
 // fp32 data runs here as ONE TF32 pass (comparison only); the accurate fp32 path
 // is gemm_tcgen05_f32x3.cuh.
@@ -64,6 +67,10 @@ struct TcGemm {
   static constexpr int NUM_EPI_THREADS = 128;
   static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
   static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, R, BNL, kBK, kStages, 0);
+  static constexpr int STG_BYTES = 32 * 128;       // one staging buffer: 32 rows x 128 bytes
+  static constexpr int SCOLS = 128 / (kDType == KCG_DT_F32 ? 4 : 2);  // C columns per staging buffer
+  static_assert(8 * STG_BYTES == tc_staging_bytes(kDType, 0), "staging size out of step with the host");
+  static_assert(kBN % SCOLS == 0, "tile width must be a multiple of the staging width");
   static constexpr uint32_t FMT = (kDType == KCG_DT_F32)    ? FMT_TF32
                                   : (kDType == KCG_DT_BF16) ? FMT_BF16
                                                             : FMT_F16;
@@ -347,6 +354,9 @@ struct TcGemm {
       const int row_in_acc = q * 32 + lane;
       uint32_t acc_it = 0;
       OutT* Cout = reinterpret_cast<OutT*>(p.C);
+      uint8_t* stg = smem + kStages * STAGE_BYTES + 1024 + (warp - 2) * (2 * STG_BYTES);
+      uint32_t stg_it = 0;  // staging buffers this warp has filled
+      if (warp == 2 && lane == 0) tma_prefetch_desc(&p.tmC);
       for (int u = unit0; u < num_units; u += unit_stride, ++acc_it) {
         const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
         const uint32_t ab = acc_it % NACC;
@@ -359,6 +369,58 @@ struct TcGemm {
         }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
+        if (w.nsplit == 1) {
+          // Whole-K tile: each warp converts 32 rows x 128 bytes at a time into its own
+          // staging buffer (16-byte units XOR-swizzled by row, so neither the writes nor the
+          // TMA engine's reads conflict on banks) and one lane hands it to a TMA store. Two
+          // buffers per warp keep a store in flight while the next block is converted.
+#pragma unroll 1
+          for (int t = 0; t < MT; ++t) {
+            const int row0 = w.m0 + row_base + t * 128 + q * 32;
+#pragma unroll 1
+            for (int g = 0; g < kBN / SCOLS; ++g, ++stg_it) {
+              uint8_t* buf = stg + (stg_it & 1u) * STG_BYTES;
+              if (lane == 0) tma_store_wait_read<1>();  // the store that last read `buf` is done
+              __syncwarp();
+              uint32_t ra[32], rb[32];  // rb: columns 32..63 of a 16-bit block
+              tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS, ra);
+              if constexpr (SCOLS == 64) tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS + 32, rb);
+              tmem_ld_wait();
+              uint8_t* rowp = buf + lane * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                uint4 o;
+                if constexpr (sizeof(OutT) == 4) {
+                  o = make_uint4(ra[4 * j], ra[4 * j + 1], ra[4 * j + 2], ra[4 * j + 3]);
+                } else {
+                  uint32_t h[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const uint32_t* r = (j < 4) ? ra : rb;
+                    const float lo = __uint_as_float(r[8 * (j & 3) + 2 * i]);
+                    const float hi = __uint_as_float(r[8 * (j & 3) + 2 * i + 1]);
+                    if constexpr (kDType == KCG_DT_BF16) {
+                      __nv_bfloat162 x = __floats2bfloat162_rn(lo, hi);
+                      h[i] = *reinterpret_cast<uint32_t*>(&x);
+                    } else {
+                      __half2 x = __floats2half2_rn(lo, hi);
+                      h[i] = *reinterpret_cast<uint32_t*>(&x);
+                    }
+                  }
+                  o = make_uint4(h[0], h[1], h[2], h[3]);
+                }
+                *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = o;
+              }
+              fence_proxy_async_smem();  // generic-proxy writes visible to the TMA engine
+              __syncwarp();
+              const int col0 = w.n0 + g * SCOLS;
+              if (lane == 0 && row0 < p.M && col0 < p.N) {
+                tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
+                tma_store_commit();
+              }
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int t = 0; t < MT; ++t) {
           const int row = w.m0 + row_base + t * 128 + row_in_acc;
@@ -377,15 +439,12 @@ struct TcGemm {
             }
             const int col = w.n0 + c * 32;
             if (row < p.M && col < p.N) {
-              if (w.nsplit > 1) {
-                float* dst = p.splitk_ws +
-                             (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN + c * 32;
-                store_chunk<float>(dst, v);
-              } else {
-                store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
-              }
+              float* dst = p.splitk_ws +
+                           (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN + c * 32;
+              store_chunk<float>(dst, v);
             }
           }
+        }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -458,6 +517,7 @@ struct TcGemm {
           named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit
         }
       }
+      if (lane == 0) tma_store_wait_all<0>();  // staging is read and C written before the CTA exits
     }
 
     // ------------------------------------------------------------ common exit

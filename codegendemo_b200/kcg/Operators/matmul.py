@@ -225,7 +225,8 @@ class TuningSpaceChecker_Matmul:
         if bk % (32 // eb) or bk % 8 or (eb == 2 and bk % 16):
             return False
         stage = (bm + bn) * bk * eb * (2 if eb == 4 else 1)
-        return stage * stages + 2048 <= MAX_SHARED_BYTES
+        staging = 0 if eb == 4 else 32768  # TMA-store staging of the 16-bit kernel's epilogue
+        return stage * stages + 2048 + staging <= MAX_SHARED_BYTES
 
     @staticmethod
     def check_simt_loads(config: Dict) -> bool:

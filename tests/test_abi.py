@@ -41,6 +41,9 @@ def test_compile_entry_returns_reference_shaped_tuple():
     assert os.path.exists(path) and path.endswith(name + ".cubin")
     assert name.startswith("GEMM_MNK256x256x256_DTabcbfloat16xbfloat16xbfloat16_AT0_")
     assert (gx, gy, gz) == (4, 1, 1) and (bx, by, bz) == (192, 1, 1)
+    # launch shared memory = what the kernel lays out: stages, barriers + slack, epilogue staging
+    info = compile_info(kpm.compileArgs())
+    assert info.smem_bytes == info.stages * (128 + 128) * 64 * 2 + 2048 + 32768 <= 227 * 1024
     # cached: second call does not recompile
     mtime = os.path.getmtime(path)
     compile_kernel_matmul(*kpm.compileArgs())
@@ -131,9 +134,34 @@ def test_pair_variant_launch_geometry():
     info = compile_info(kpm.compileArgs(), num_stages=4, kernel=4)
     assert info.kernel == _lib.KERNEL_TCGEN05_PAIR and list(info.cluster) == [2, 1, 1]
     assert info.grid[0] == 148 and info.block[0] == 192
-    assert info.smem_bytes == 4 * (256 + 128) * 64 * 2 + 2048  # per CTA: 256 rows of A, 128 columns of B
+    # per CTA: 256 rows of A, 128 columns of B, + 32 KiB of TMA-store staging for the epilogue
+    assert info.smem_bytes == 4 * (256 + 128) * 64 * 2 + 2048 + 32768
     f32 = default_config(4096, 4096, 4096, E.float32, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
                          BLOCK_SIZE_K=32, NUM_STAGES=3)
     i2 = compile_info(f32.compileArgs(), num_stages=3, kernel=4)
     assert i2.block[0] == 512 and list(i2.cluster) == [2, 1, 1]
     assert i2.smem_bytes == 3 * 2 * (128 + 128) * 32 * 4 + 2048  # hi + lo twins of the per-CTA slices
+
+
+def test_cubin_cache_is_keyed_by_the_kernel_sources(tmp_path):
+    """Cubins live under <cache>/src-<hash of the kernel sources>: editing any kernel header must
+    never be served by a cubin built from the old text."""
+    import shutil
+    import subprocess
+    import sys
+    here = _lib.get_lib().kcg_cache_dir().decode()
+    assert re.fullmatch(r"src-[0-9a-f]{12}", os.path.basename(here)), here
+    src = os.path.join(os.path.dirname(_lib.__file__), "csrc", "kernels")
+    copy = tmp_path / "kernels"
+    shutil.copytree(src, copy)
+    with open(copy / "ptx_sm100.cuh", "a") as f:
+        f.write("// edited\n")
+    code = ("from codegendemo_b200 import _lib; import os;"
+            "print(os.path.basename(_lib.get_lib().kcg_cache_dir().decode()))")
+    root = os.path.dirname(os.path.dirname(_lib.__file__))
+    tags = []
+    for srcdir in (src, str(copy)):
+        env = dict(os.environ, KCG_KERNEL_SRC_DIR=srcdir, KCG_CACHE_DIR=str(tmp_path / "cache"))
+        tags.append(subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True,
+                                   check=True).stdout.strip())
+    assert tags[0] == os.path.basename(here) and tags[1] != tags[0] and tags[1].startswith("src-")
