@@ -21,7 +21,7 @@ E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_L
 EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
-    "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
+    "kcg_launch_gemm_ex", "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
     "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
 )
 
@@ -79,6 +79,12 @@ class CompileOpts(ctypes.Structure):
                 ("num_sms", ctypes.c_int32), ("force", ctypes.c_int32)]
 
 
+class Epilogue(ctypes.Structure):
+    """``kcg_epilogue``: C = act(alpha * A.B + beta * C + bias[col])."""
+    _fields_ = [("alpha", ctypes.c_float), ("beta", ctypes.c_float), ("bias", ctypes.c_uint64),
+                ("relu", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3)]
+
+
 class DeviceProps(ctypes.Structure):
     """``kcg_device_props``."""
     _fields_ = [("max_shared_mem", ctypes.c_int32), ("multiprocessor_count", ctypes.c_int32),
@@ -116,6 +122,8 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_unload.argtypes = [u64]
     lib.kcg_device_properties.argtypes = [ctypes.c_int, ctypes.POINTER(DeviceProps)]
     lib.kcg_launch_gemm.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64]
+    lib.kcg_launch_gemm_ex.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64,
+                                       ctypes.POINTER(Epilogue)]
     lib.kcg_check_status.argtypes = [ctypes.c_int, u64]
     lib.kcg_matmul_host.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64,
                                     ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
@@ -126,8 +134,8 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_last_error.restype = ctypes.c_char_p
     lib.kcg_version.restype = ctypes.c_char_p
     for name in ("kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_load_binary",
-                 "kcg_unload", "kcg_device_properties", "kcg_launch_gemm", "kcg_check_status",
-                 "kcg_matmul_host", "kcg_shutdown"):
+                 "kcg_unload", "kcg_device_properties", "kcg_launch_gemm", "kcg_launch_gemm_ex",
+                 "kcg_check_status", "kcg_matmul_host", "kcg_shutdown"):
         getattr(lib, name).restype = ctypes.c_int
     _lib = lib
     return lib

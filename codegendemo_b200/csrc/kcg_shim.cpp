@@ -716,7 +716,14 @@ int kcg_unload(uint64_t module) {
 
 int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
                     uint64_t B, uint64_t C) {
+  return kcg_launch_gemm_ex(function, info, device, stream, A, B, C, nullptr);
+}
+
+int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                       uint64_t B, uint64_t C, const kcg_epilogue* epi) {
   if (!function || !info || !A || !B || !C) return fail(KCG_E_BAD_ARG, "null argument");
+  if (epi && (epi->bias % 16) != 0) return fail(KCG_E_BAD_ARG, "bias must be 16-byte aligned");
+  if (epi && info->kernel == KCG_KERNEL_WAIT_PROBE) return fail(KCG_E_BAD_ARG, "the wait probe has no epilogue");
   DeviceState* s = nullptr;
   if (int e = ensure_device(device, &s)) return e;
   KcgGemmParams p;
@@ -735,6 +742,14 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
   p.status = reinterpret_cast<unsigned int*>(s->status);
   p.split_first_tile = (M / (info->bm > 0 ? info->bm : 1)) * (N / (info->bn > 0 ? info->bn : 1));
   p.split_factor = 1;
+  p.alpha = 1.f;
+  if (epi) {
+    p.alpha = epi->alpha;
+    p.beta = epi->beta;
+    p.bias = reinterpret_cast<const void*>(epi->bias);
+    p.epi_flags = ((epi->alpha != 1.f || epi->beta != 0.f) ? KCG_EPI_SCALE : 0u) | (epi->bias ? KCG_EPI_BIAS : 0u) |
+                  (epi->relu ? KCG_EPI_RELU : 0u);
+  }
   int grid0 = info->grid[0];
   const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
   if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 || pair) {

@@ -23,6 +23,11 @@
 
 #define KCG_VARIANT_TCGEN05_PAIR 4  // tcgen05 cta_group::2 on clusters of two CTAs (fp16 / bf16)
 
+// epi_flags bits
+#define KCG_EPI_SCALE 1u  // alpha / beta differ from 1 / 0
+#define KCG_EPI_BIAS 2u   // add bias[col]
+#define KCG_EPI_RELU 4u   // max(x, 0) last
+
 // Device status word values (status[0]); 0 = ok.
 #define KCG_ST_OK 0u
 #define KCG_ST_TIMEOUT_PRODUCER 1u
@@ -48,6 +53,12 @@ struct alignas(64) KcgGemmParams {
   // (first = 0, factor = S); with LOCAL_SPLIT_U = 1 the launcher splits only the tiles of the last,
   // partially filled wave of the persistent grid (or nothing: factor = 1).
   int split_first_tile, split_factor;
+  // Fused epilogue, in force when epi_flags != 0: D = act(alpha * (A.B) + beta * C + bias[col]),
+  // computed in fp32 before the rounding to C's type. beta * C reads C in place (skipped when
+  // beta == 0, so C may then hold anything); bias has N values of C's type.
+  float alpha, beta;
+  const void* bias;
+  unsigned int epi_flags;  // KCG_EPI_*
 };
 
 namespace kcg {

@@ -19,6 +19,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "epilogue.cuh"
 #include "gemm_params.h"
 
 namespace kcg {
@@ -259,13 +260,17 @@ struct SimtGemm {
       for (int e = tid * GSW; e < BM * BN; e += THREADS * GSW) {
         const int m = e / BN, n = e % BN;
         Vec<T, GSW> out;
+        float sv[GSW];
 #pragma unroll
         for (int j = 0; j < GSW; ++j) {
           float s = 0.f;
 #pragma unroll
           for (int z = 0; z < LSU; ++z) s += smC[(z * BM + m) * BN + n + j];
-          out.v[j] = from_f32<T>(s);
+          sv[j] = s;
         }
+        if (p.epi_flags != 0u) epi_span<T, GSW>(p, sv, m0 + m, n0 + n);
+#pragma unroll
+        for (int j = 0; j < GSW; ++j) out.v[j] = from_f32<T>(sv[j]);
         *reinterpret_cast<Vec<T, GSW>*>(C + static_cast<size_t>(m0 + m) * p.ldc + n0 + n) = out;
       }
     } else {
@@ -277,8 +282,12 @@ struct SimtGemm {
         for (int j = 0; j < TN; j += SW) {
           const int n = owned_index<TN, WSWB, TSWB, BLN, WLN>(j, warp_x, lane_x);
           Vec<T, SW> out;
+          float sv[SW];
 #pragma unroll
-          for (int o = 0; o < SW; ++o) out.v[o] = from_f32<T>(acc[i][j + o]);
+          for (int o = 0; o < SW; ++o) sv[o] = acc[i][j + o];
+          if (p.epi_flags != 0u) epi_span<T, SW>(p, sv, m0 + m, n0 + n);
+#pragma unroll
+          for (int o = 0; o < SW; ++o) out.v[o] = from_f32<T>(sv[o]);
           *reinterpret_cast<Vec<T, SW>*>(C + static_cast<size_t>(m0 + m) * p.ldc + n0 + n) = out;
         }
       }
@@ -301,7 +310,9 @@ __device__ void naive_gemm(const KcgGemmParams& p) {
                            : to_f32<T>(A[static_cast<size_t>(row) * p.lda + k]);
     s = fmaf(a, to_f32<T>(B[static_cast<size_t>(k) * p.ldb + col]), s);
   }
-  reinterpret_cast<T*>(p.C)[static_cast<size_t>(row) * p.ldc + col] = from_f32<T>(s);
+  float sv[1] = {s};
+  if (p.epi_flags != 0u) epi_span<T, 1>(p, sv, row, col);
+  reinterpret_cast<T*>(p.C)[static_cast<size_t>(row) * p.ldc + col] = from_f32<T>(sv[0]);
 }
 
 }  // namespace kcg

@@ -31,6 +31,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
 
@@ -386,19 +387,29 @@ struct TcGemm {
               tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS, ra);
               if constexpr (SCOLS == 64) tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS + 32, rb);
               tmem_ld_wait();
+              float va[32], vb[32];
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                va[i] = __uint_as_float(ra[i]);
+                if constexpr (SCOLS == 64) vb[i] = __uint_as_float(rb[i]);
+              }
+              if (p.epi_flags != 0u && row0 + lane < p.M) {
+                epi_span<OutT, 32>(p, va, row0 + lane, w.n0 + g * SCOLS);
+                if constexpr (SCOLS == 64) epi_span<OutT, 32>(p, vb, row0 + lane, w.n0 + g * SCOLS + 32);
+              }
               uint8_t* rowp = buf + lane * 128;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 uint4 o;
                 if constexpr (sizeof(OutT) == 4) {
-                  o = make_uint4(ra[4 * j], ra[4 * j + 1], ra[4 * j + 2], ra[4 * j + 3]);
+                  o = make_uint4(__float_as_uint(va[4 * j]), __float_as_uint(va[4 * j + 1]),
+                                 __float_as_uint(va[4 * j + 2]), __float_as_uint(va[4 * j + 3]));
                 } else {
                   uint32_t h[4];
 #pragma unroll
                   for (int i = 0; i < 4; ++i) {
-                    const uint32_t* r = (j < 4) ? ra : rb;
-                    const float lo = __uint_as_float(r[8 * (j & 3) + 2 * i]);
-                    const float hi = __uint_as_float(r[8 * (j & 3) + 2 * i + 1]);
+                    const float lo = (j < 4) ? va[8 * (j & 3) + 2 * i] : vb[8 * (j & 3) + 2 * i];
+                    const float hi = (j < 4) ? va[8 * (j & 3) + 2 * i + 1] : vb[8 * (j & 3) + 2 * i + 1];
                     if constexpr (kDType == KCG_DT_BF16) {
                       __nv_bfloat162 x = __floats2bfloat162_rn(lo, hi);
                       h[i] = *reinterpret_cast<uint32_t*>(&x);
@@ -510,6 +521,7 @@ struct TcGemm {
                     }
                   }
                 }
+                if (p.epi_flags != 0u) epi_span<OutT, 32>(p, v, row, col);
                 store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
               }
             }

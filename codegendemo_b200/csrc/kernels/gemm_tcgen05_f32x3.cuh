@@ -23,6 +23,7 @@
 // Same work decomposition, raster, split-K reduction and bounded waits as
 // gemm_tcgen05.cuh.
 #pragma once
+#include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
 
@@ -410,7 +411,9 @@ struct TcGemmF32x3 {
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int b = (t * PIECES + c) * 32 + 4 * i;
-                d4[i] = make_float4(acc[b], acc[b + 1], acc[b + 2], acc[b + 3]);
+                float o[4] = {acc[b], acc[b + 1], acc[b + 2], acc[b + 3]};
+                if (p.epi_flags != 0u && w.nsplit == 1) epi_span<float, 4>(p, o, row, col + 4 * i);
+                d4[i] = make_float4(o[0], o[1], o[2], o[3]);
               }
             }
           }
@@ -457,6 +460,7 @@ struct TcGemmF32x3 {
                     v[4 * i + 3] += x.w;
                   }
                 }
+                if (p.epi_flags != 0u) epi_span<float, 32>(p, v, row, col);
                 float4* d4 = reinterpret_cast<float4*>(Cout + static_cast<size_t>(row) * p.ldc + col);
 #pragma unroll
                 for (int i = 0; i < 8; ++i)

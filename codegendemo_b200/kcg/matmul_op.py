@@ -74,16 +74,29 @@ def build_kernel(kpm: KernelArgMatmul, deviceId: int = 0):
     return inConfig, CompiledKernelFactory.getKernel(inConfig, deviceId)
 
 
-def matmul(a, b, c=None, **keys):
-    """``c = a @ b`` on the current CUDA device through a default (or keyword-tuned) config."""
+_KERNELS = {}
+
+
+def matmul(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
+    """``c = a @ b`` on the current CUDA device through the kernel database's config for the shape
+    (or a default config tuned by keyword). ``alpha``, ``beta``, ``bias`` (N values of c's dtype) and
+    ``relu`` fuse ``c = act(alpha * a @ b + beta * c + bias)`` into the kernel's store. Compiled and
+    loaded kernels are kept per (shape, dtype, device, keys)."""
     import torch
     M, K = a.shape
     K2, N = b.shape
     assert K == K2 and a.is_contiguous() and b.is_contiguous()
     if c is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs the c to scale")
         c = torch.empty((M, N), dtype=a.dtype, device=a.device)
     dt = FromTorchType(a.dtype)
-    kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
-    _, kern = build_kernel(kpm, a.device.index or 0)
-    kern.run(a, b, c)
+    dev = a.device.index or 0
+    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())))
+    kern = _KERNELS.get(key)
+    if kern is None:
+        kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
+        _, kern = build_kernel(kpm, dev)
+        _KERNELS[key] = kern
+    kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu)
     return c

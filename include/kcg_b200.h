@@ -132,6 +132,22 @@ int kcg_device_properties(int device, kcg_device_props* out);
  * allocates on first use. C is overwritten (alpha = 1, beta = 0). */
 int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
                     uint64_t A, uint64_t B, uint64_t C);
+/* Fused epilogue: C = act(alpha * (A*B) + beta * C + bias[col]), fp32 arithmetic in that order,
+ * rounded once to C's type. No counterpart in the reference's launcher (its kernels store A*B
+ * only); it covers the bias / ReLU step the reference plans between chained matmuls
+ * (doc/重构方案.md). beta * C reads C in place and is skipped when beta == 0 (C may then be
+ * uninitialised); `bias` is a device address of N values of C's type, 16-byte aligned, or 0;
+ * relu != 0 applies max(x, 0) last. A null `epi` is kcg_launch_gemm. Every kernel family
+ * honours it, including the K-split kernels (the reducing CTA applies it once). */
+typedef struct kcg_epilogue {
+  float alpha;
+  float beta;
+  uint64_t bias;
+  int32_t relu;
+  int32_t reserved[3];
+} kcg_epilogue;
+int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                       uint64_t A, uint64_t B, uint64_t C, const kcg_epilogue* epi);
 /* Reads (and clears) the device status word written by bounded waits; returns
  * KCG_E_DEVICE_TIMEOUT if a kernel gave up since the last check. Synchronises `stream`. */
 int kcg_check_status(int device, uint64_t stream);

@@ -117,6 +117,22 @@ def host_matmul(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
     return torch.matmul(A.float(), B.float())
 
 
+def host_matmul_fused(A, B, alpha=1.0, beta=0.0, C=None, bias=None, relu=False) -> torch.Tensor:
+    """Checker for the fused epilogue, ``act(alpha * A @ B + beta * C + bias)``, on the host at
+    oracle precision. The reference has no fused epilogue (it only sketches matmul -> bias/ReLU
+    chains), so this composes its check, ``torch.matmul``, with the elementwise steps: parity of the
+    extension is pinned to that composition, not to reference output."""
+    out = host_matmul(A, B)
+    out = out * alpha
+    if beta != 0.0:
+        out = out + beta * C.detach().cpu().to(out.dtype)
+    if bias is not None:
+        out = out + bias.detach().cpu().to(out.dtype)[None, :]
+    if relu:
+        out = torch.clamp_min(out, 0.0)
+    return out
+
+
 # ------------------------------------------------------------------ seeded inputs
 def make_inputs(M: int, N: int, K: int, dtype: torch.dtype, dist: str = "uniform", seed: int = 0):
     """Seeded synthetic A (M x K) and B (K x N) on the host, identical bytes on every machine.

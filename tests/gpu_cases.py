@@ -94,11 +94,28 @@ RECT = [("c4_bf16_128x11008", 128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=
         ("c4_bf16_2048x4096", 2048, 4096, 4096, E.bfloat16, dict())]
 
 
+# fused-epilogue cases, one per kernel family and store path: (id, M, N, K, dtype, distribution, keys)
+FUSED = [
+    ("bf16_tma_store", 256, 512, 512, E.bfloat16, "normal", dict()),
+    ("fp16_tma_store", 256, 512, 512, E.float16, "normal", dict()),
+    ("bf16_pair", 1024, 512, 512, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4)),
+    ("bf16_splitk_reduce", 256, 512, 2048, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=4)),
+    ("fp32_3xtf32", 256, 256, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=128)),
+    ("fp32_3xtf32_splitk_reduce", 128, 256, 4096, E.float32, "uniform", dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),
+    ("fp32_3xtf32_pair", 512, 512, 512, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=3)),
+    ("fp32_simt", 256, 256, 256, E.float32, "uniform", SIMT_128),
+    ("fp32_simt_lsu2", 256, 256, 256, E.float32, "uniform", dict(SIMT_64, LOCAL_SPLIT_U=2)),
+    ("fp32_naive", 256, 192, 96, E.float32, "uniform", dict(KERNEL_VARIANT=100, BLOCK_SIZE_N=64)),
+]
+
+
 def all_configs():
     out = [default_config(4096, 4096, 4096, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3),
            default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64),
            default_config(256, 256, 256, E.bfloat16)]
-    for (_, m, n, k, dt, _, keys) in SEEDED:
+    for (_, m, n, k, dt, _, keys) in SEEDED + FUSED:
         out.append(default_config(m, n, k, dt, **keys))
     for (name, dt, keys) in GOLDEN:
         m, n, k = GOLDEN_SHAPES[name]

@@ -81,6 +81,60 @@ def test_results_are_bitwise_reproducible_including_split_k():
         assert torch.equal(c1, c2)
 
 
+EPILOGUES = [dict(alpha=0.5, beta=-0.75, bias=True, relu=True), dict(bias=True), dict(relu=True),
+             dict(alpha=-1.25, beta=0.5), dict(alpha=2.0)]
+
+
+@pytest.mark.parametrize("case", gpu_cases.FUSED, ids=[c[0] for c in gpu_cases.FUSED])
+def test_fused_epilogue_matches_oracle(case):
+    """c = act(alpha * a.b + beta * c + bias) through kcg_launch_gemm_ex, every kernel family and
+    both store paths (whole-K tiles and the K-split reduction), against the host composition."""
+    _, M, N, K, dt, dist, keys = case
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, N, K, tdt, dist, seed=4)
+    g = torch.Generator().manual_seed(11)
+    Cin = (torch.rand(M, N, generator=g) * 2 - 1).to(tdt)
+    bias = (torch.rand(N, generator=g) * 2 - 1).to(tdt)
+    kpm = default_config(M, N, K, dt, **keys)
+    _, kern = build_kernel(kpm, 0)
+    a = (A.t().contiguous() if kpm.isATranspose else A).cuda()
+    b, bias_d = B.cuda(), bias.cuda()
+    for epi in EPILOGUES:
+        kw = dict(epi)
+        use_bias = kw.pop("bias", False)
+        beta = kw.get("beta", 0.0)
+        # beta == 0 must not read C: poison it
+        c = Cin.cuda() if beta != 0.0 else torch.full((M, N), float("nan"), dtype=tdt, device="cuda:0")
+        kern.run(a, b, c, bias=bias_d if use_bias else None, **kw)
+        kern.checkStatus()
+        ref = oracle.host_matmul_fused(A, B, alpha=kw.get("alpha", 1.0), beta=beta, C=Cin,
+                                       bias=bias if use_bias else None, relu=kw.get("relu", False))
+        err = oracle.rel_errors(c, ref)
+        assert not err["nan"], (epi, "kernel left part of C unwritten or read a poisoned C")
+        assert err["max_rel"] <= oracle.tolerance_for(tdt), (epi, err)
+    # the plain call on the same kernel is unchanged
+    c = torch.full((M, N), float("nan"), dtype=tdt, device="cuda:0")
+    kern.run(a, b, c)
+    kern.checkStatus()
+    assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.tolerance_for(tdt)
+
+
+def test_matmul_op_fuses_bias_relu_chain():
+    """matmul -> bias + ReLU -> matmul, the chain the reference sketches, as two fused launches."""
+    from codegendemo_b200.kcg.matmul_op import matmul
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(512, 1024, generator=g) / 32).bfloat16()
+    w1 = (torch.randn(1024, 512, generator=g) / 32).bfloat16()
+    w2 = (torch.randn(512, 256, generator=g) / 22).bfloat16()
+    b1 = (torch.randn(512, generator=g) / 8).bfloat16()
+    h = matmul(x.cuda(), w1.cuda(), bias=b1.cuda(), relu=True)
+    y = matmul(h, w2.cuda())
+    torch.cuda.synchronize()
+    h_ref = torch.relu(x.float() @ w1.float() + b1.float()).bfloat16()
+    assert oracle.rel_errors(h, h_ref.float())["max_rel"] <= 2e-2
+    assert oracle.rel_errors(y, h_ref.float() @ w2.float())["max_rel"] <= 2e-2
+
+
 def test_host_buffer_entry_matches_device_entry():
     A, B = oracle.make_inputs(512, 512, 512, torch.bfloat16, "normal", seed=1)
     kpm = default_config(512, 512, 512, E.bfloat16)
