@@ -808,11 +808,19 @@ int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int devic
         }
       }
     }
+    // The 3xTF32 kernel applies a fused epilogue in its reduction loop only (its register file is
+    // full of accumulators at the direct store), so a fused launch sends every tile through the
+    // workspace as a one-way split; the tail split is not combined with it.
+    const bool ws_epilogue = x3 && p.epi_flags != 0u;
+    if (ws_epilogue && info->splitk <= 1) {
+      first = 0;
+      factor = 1;
+    }
     const int units = first + (T - first) * factor;
     grid0 = (units < G ? units : G) * (pair ? 2 : 1);
     p.split_first_tile = first;
     p.split_factor = factor;
-    if (factor > 1) {
+    if (factor > 1 || ws_epilogue) {
       std::lock_guard<std::mutex> g(g_dev_mutex);
       const size_t slots = static_cast<size_t>(T - first) * factor;
       const size_t need = slots * info->bm * info->bn * sizeof(float);

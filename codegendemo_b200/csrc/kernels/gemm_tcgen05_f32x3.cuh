@@ -394,7 +394,12 @@ struct TcGemmF32x3 {
           }
         }
         if (!ok) break;
-        // ---- tile (or split partial) complete in registers: store
+        // ---- tile (or split partial) complete in registers: store. A launch with a fused
+        // epilogue sends whole-K tiles through the workspace too (every tile is then its own
+        // one-way "split": the launcher sets split_first_tile = 0) and applies the epilogue in
+        // the reduction loop below, where the accumulators are dead: with all of them live
+        // there are no registers left for the bias / C operands.
+        const bool via_ws = w.nsplit > 1 || p.epi_flags != 0u;
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
           const int row = w.m0 + row_base + t * 128 + row_in_acc;
@@ -402,33 +407,34 @@ struct TcGemmF32x3 {
           for (int c = 0; c < PIECES; ++c) {
             const int col = w.n0 + col_half0 + c * 32;
             if (row < p.M && col < p.N) {
-              float* dst = (w.nsplit > 1)
-                               ? p.splitk_ws +
-                                     (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN +
-                                     col_half0 + c * 32
-                               : Cout + static_cast<size_t>(row) * p.ldc + col;
+              float* dst = via_ws ? p.splitk_ws +
+                                        (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN +
+                                        col_half0 + c * 32
+                                  : Cout + static_cast<size_t>(row) * p.ldc + col;
               float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int b = (t * PIECES + c) * 32 + 4 * i;
-                float o[4] = {acc[b], acc[b + 1], acc[b + 2], acc[b + 3]};
-                if (p.epi_flags != 0u && w.nsplit == 1) epi_span<float, 4>(p, o, row, col + 4 * i);
-                d4[i] = make_float4(o[0], o[1], o[2], o[3]);
+                d4[i] = make_float4(acc[b], acc[b + 1], acc[b + 2], acc[b + 3]);
               }
             }
           }
         }
-        if (w.nsplit > 1) {
-          const int ctr = (w.tile - first_split) * NCTA + static_cast<int>(rank);  // per CTA half
-          __threadfence();
-          named_bar_sync(1, NUM_EPI_THREADS);
-          if (epi_tid == 0) {
-            const unsigned int old = atomicAdd(&p.tile_counters[ctr], 1u);
-            bars->last_flag = (old == static_cast<unsigned int>(w.nsplit - 1)) ? 1u : 0u;
-            if (old == static_cast<unsigned int>(w.nsplit - 1)) p.tile_counters[ctr] = 0u;
+        if (via_ws) {
+          bool reduce_here = true;  // a one-way split reads back what this same thread just wrote
+          if (w.nsplit > 1) {
+            const int ctr = (w.tile - first_split) * NCTA + static_cast<int>(rank);  // per CTA half
+            __threadfence();
+            named_bar_sync(1, NUM_EPI_THREADS);
+            if (epi_tid == 0) {
+              const unsigned int old = atomicAdd(&p.tile_counters[ctr], 1u);
+              bars->last_flag = (old == static_cast<unsigned int>(w.nsplit - 1)) ? 1u : 0u;
+              if (old == static_cast<unsigned int>(w.nsplit - 1)) p.tile_counters[ctr] = 0u;
+            }
+            named_bar_sync(1, NUM_EPI_THREADS);
+            reduce_here = bars->last_flag != 0u;
           }
-          named_bar_sync(1, NUM_EPI_THREADS);
-          if (bars->last_flag != 0u) {
+          if (reduce_here) {
             __threadfence();
             // One partial at a time: the accumulating warps have no registers to spare for
             // deeper prefetch (more loads in flight made ptxas spill inside the main loop).
