@@ -61,7 +61,7 @@ int fail(int code, const char* fmt, ...) {
   X(cuLaunchKernelEx) X(cuTensorMapEncodeTiled) X(cuMemAlloc) X(cuMemFree) X(cuMemsetD32)      \
   X(cuMemcpyHtoDAsync) X(cuMemcpyDtoHAsync) X(cuMemcpyDtoH) X(cuMemcpyHtoD)                    \
   X(cuStreamSynchronize) X(cuStreamCreate) X(cuStreamDestroy) X(cuStreamWaitEvent) X(cuEventCreate)        \
-  X(cuEventRecord) X(cuEventDestroy)
+  X(cuEventRecord) X(cuEventDestroy) X(cuIpcGetMemHandle) X(cuIpcOpenMemHandle) X(cuIpcCloseMemHandle)
 
 struct Driver {
   void* handle = nullptr;
@@ -721,7 +721,68 @@ int kcg_launch_gemm(uint64_t function, const kcg_kernel_info* info, int device, 
 
 int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
                        uint64_t B, uint64_t C, const kcg_epilogue* epi) {
+  return kcg_launch_gemm_allgather(function, info, device, stream, A, B, C, epi, nullptr, 0);
+}
+
+// ---- peer buffers: device memory another process of the same node can map (CUDA IPC)
+int kcg_peer_alloc(int device, uint64_t bytes, uint64_t* dptr, uint8_t handle[64]) {
+  if (!dptr || !handle || bytes == 0) return fail(KCG_E_BAD_ARG, "null argument");
+  static_assert(sizeof(CUipcMemHandle) == 64, "IPC handle size");
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  CUdeviceptr d = 0;
+  DRV(cuMemAlloc(&d, bytes));
+  CUipcMemHandle h;
+  CUresult r = driver().p_cuIpcGetMemHandle(&h, d);
+  if (r != CUDA_SUCCESS) {
+    driver().p_cuMemFree(d);
+    return drv_fail(r, "cuIpcGetMemHandle");
+  }
+  memcpy(handle, &h, 64);
+  *dptr = static_cast<uint64_t>(d);
+  return 0;
+}
+
+int kcg_peer_open(int device, const uint8_t handle[64], uint64_t* dptr) {
+  if (!dptr || !handle) return fail(KCG_E_BAD_ARG, "null argument");
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  CUipcMemHandle h;
+  memcpy(&h, handle, 64);
+  CUdeviceptr d = 0;
+  DRV(cuIpcOpenMemHandle(&d, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS));
+  *dptr = static_cast<uint64_t>(d);
+  return 0;
+}
+
+int kcg_peer_close(int device, uint64_t dptr) {
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  DRV(cuIpcCloseMemHandle(static_cast<CUdeviceptr>(dptr)));
+  return 0;
+}
+
+int kcg_peer_free(int device, uint64_t dptr) {
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  DRV(cuMemFree(static_cast<CUdeviceptr>(dptr)));
+  return 0;
+}
+
+int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                              uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers) {
   if (!function || !info || !A || !B || !C) return fail(KCG_E_BAD_ARG, "null argument");
+  if (n_peers < 0 || n_peers > KCG_MAX_PEERS || (n_peers > 0 && !peer_c))
+    return fail(KCG_E_BAD_ARG, "n_peers must be 0..%d with their addresses", KCG_MAX_PEERS);
+  if (n_peers > 0) {
+    const bool staged = (info->kernel == KCG_KERNEL_TCGEN05 && info->dtype != KCG_DTYPE_FLOAT32) ||
+                        (info->kernel == KCG_KERNEL_TCGEN05_PAIR && info->dtype != KCG_DTYPE_FLOAT32) ||
+                        info->kernel == KCG_KERNEL_TF32X1;
+    if (!staged)
+      return fail(KCG_E_BAD_CONFIG, "the fused all-gather needs a single-pass tcgen05 kernel (bf16 / fp16)");
+    for (int i = 0; i < n_peers; ++i)
+      if (!peer_c[i] || peer_c[i] % 16) return fail(KCG_E_BAD_ARG, "peer address %d is null or not 16-byte aligned", i);
+  }
   if (epi && (epi->bias % 16) != 0) return fail(KCG_E_BAD_ARG, "bias must be 16-byte aligned");
   if (epi && info->kernel == KCG_KERNEL_WAIT_PROBE) return fail(KCG_E_BAD_ARG, "the wait probe has no epilogue");
   DeviceState* s = nullptr;
@@ -750,6 +811,8 @@ int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int devic
     p.epi_flags = ((epi->alpha != 1.f || epi->beta != 0.f) ? KCG_EPI_SCALE : 0u) | (epi->bias ? KCG_EPI_BIAS : 0u) |
                   (epi->relu ? KCG_EPI_RELU : 0u);
   }
+  p.n_peers = n_peers;
+  for (int i = 0; i < n_peers; ++i) p.peerC[i] = reinterpret_cast<void*>(peer_c[i]);
   int grid0 = info->grid[0];
   const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
   if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 || pair) {

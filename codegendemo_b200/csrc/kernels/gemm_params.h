@@ -23,6 +23,8 @@
 
 #define KCG_VARIANT_TCGEN05_PAIR 4  // tcgen05 cta_group::2 on clusters of two CTAs (fp16 / bf16)
 
+#define KCG_MAX_PEERS 7  // other GPUs of one NVSwitch domain of eight
+
 // epi_flags bits
 #define KCG_EPI_SCALE 1u  // alpha / beta differ from 1 / 0
 #define KCG_EPI_BIAS 2u   // add bias[col]
@@ -59,6 +61,12 @@ struct alignas(64) KcgGemmParams {
   float alpha, beta;
   const void* bias;
   unsigned int epi_flags;  // KCG_EPI_*
+  // Fused all-gather of an M-sharded product: besides C, every finished tile is also written
+  // to the same rows / columns of n_peers more matrices with C's pitch — this rank's slab inside
+  // the full C of every other GPU, mapped into this process (plain vector stores over NVLink;
+  // no remote loads, no flags: the data is in place when every rank's kernel has completed).
+  int n_peers;
+  void* peerC[KCG_MAX_PEERS];
 };
 
 namespace kcg {

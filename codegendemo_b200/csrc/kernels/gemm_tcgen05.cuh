@@ -429,6 +429,28 @@ struct TcGemm {
                 tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
                 tma_store_commit();
               }
+              if (p.n_peers > 0) {
+                // Fused all-gather: the same block goes to this rank's rows of every peer's C.
+                // Lane l re-reads 16-byte unit (l & 7) of rows 4i + l / 8, so that eight lanes
+                // write one full 128-byte line and a warp store covers four rows.
+                uint4 unit[8];
+                const int uj = lane & 7;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int ur = 4 * i + (lane >> 3);
+                  unit[i] = *reinterpret_cast<const uint4*>(buf + ur * 128 + ((uj ^ (ur & 7)) << 4));
+                }
+                const int ucol = col0 + uj * (16 / static_cast<int>(sizeof(OutT)));
+                for (int pe = 0; pe < p.n_peers; ++pe) {
+                  OutT* pc = reinterpret_cast<OutT*>(p.peerC[pe]);
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    const int urow = row0 + 4 * i + (lane >> 3);
+                    if (urow < p.M && ucol < p.N)
+                      *reinterpret_cast<uint4*>(pc + static_cast<size_t>(urow) * p.ldc + ucol) = unit[i];
+                  }
+                }
+              }
             }
           }
         } else {
@@ -523,6 +545,8 @@ struct TcGemm {
                 }
                 if (p.epi_flags != 0u) epi_span<OutT, 32>(p, v, row, col);
                 store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
+                for (int pe = 0; pe < p.n_peers; ++pe)
+                  store_chunk<OutT>(reinterpret_cast<OutT*>(p.peerC[pe]) + static_cast<size_t>(row) * p.ldc + col, v);
               }
             }
           }
@@ -530,6 +554,7 @@ struct TcGemm {
         }
       }
       if (lane == 0) tma_store_wait_all<0>();  // staging is read and C written before the CTA exits
+      if (p.n_peers > 0) __threadfence_system();  // peer stores ordered before the kernel's completion
     }
 
     // ------------------------------------------------------------ common exit

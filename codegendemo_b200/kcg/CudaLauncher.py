@@ -53,10 +53,12 @@ class CudaLauncher:
             self.m_runtime = CudaLoaderST().loadBinary(self.m_libFile)
         return self.m_runtime
 
-    def launchKernel(self, device, *args, stream=None, alpha=1.0, beta=0.0, bias=None, relu=False):
+    def launchKernel(self, device, *args, stream=None, alpha=1.0, beta=0.0, bias=None, relu=False, peers=None):
         """(a, b, c) -> c = a.b on `stream` (torch's current stream by default). The keyword
-        arguments fuse c = act(alpha * a.b + beta * c + bias) into the kernel's store; the reference's
-        launcher has no such arguments and the plain call behaves as the reference's."""
+        arguments fuse c = act(alpha * a.b + beta * c + bias) into the kernel's store; `peers` (up to 7
+        device addresses or tensors shaped like c) also receive every finished tile: the fused
+        all-gather of an M-sharded product. The reference's launcher has no such arguments and the plain
+        call behaves as the reference's."""
         rt = self._getWrapper()
         if len(args) != 3:
             raise TypeError("matmul kernel takes (a, b, c)")
@@ -64,12 +66,19 @@ class CudaLauncher:
             stream = DeviceInfo.get_cuda_stream(device)
         a, b, c = (_pointer_of(x) for x in args)
         lib = _lib.get_lib()
-        if alpha == 1.0 and beta == 0.0 and bias is None and not relu:
+        if alpha == 1.0 and beta == 0.0 and bias is None and not relu and not peers:
             _lib.check(lib.kcg_launch_gemm(ctypes.c_uint64(rt.m_function), ctypes.byref(self.m_cInfo),
                                            int(device), ctypes.c_uint64(int(stream)),
                                            ctypes.c_uint64(a), ctypes.c_uint64(b), ctypes.c_uint64(c)))
             return
         epi = _lib.Epilogue(float(alpha), float(beta), _pointer_of(bias) if bias is not None else 0, int(bool(relu)))
+        if peers:
+            arr = (ctypes.c_uint64 * len(peers))(*[_pointer_of(x) for x in peers])
+            _lib.check(lib.kcg_launch_gemm_allgather(ctypes.c_uint64(rt.m_function), ctypes.byref(self.m_cInfo),
+                                                     int(device), ctypes.c_uint64(int(stream)), ctypes.c_uint64(a),
+                                                     ctypes.c_uint64(b), ctypes.c_uint64(c), ctypes.byref(epi),
+                                                     arr, len(peers)))
+            return
         _lib.check(lib.kcg_launch_gemm_ex(ctypes.c_uint64(rt.m_function), ctypes.byref(self.m_cInfo),
                                           int(device), ctypes.c_uint64(int(stream)), ctypes.c_uint64(a),
                                           ctypes.c_uint64(b), ctypes.c_uint64(c), ctypes.byref(epi)))

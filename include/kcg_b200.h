@@ -148,6 +148,26 @@ typedef struct kcg_epilogue {
 } kcg_epilogue;
 int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
                        uint64_t A, uint64_t B, uint64_t C, const kcg_epilogue* epi);
+/* ---- M-sharded product with the all-gather of C fused into the kernel ---------------
+ * No counterpart in the reference (it has no multi-GPU code). Rank r of G computes rows
+ * [r*M/G, (r+1)*M/G) of C with the same cubin as kcg_launch_gemm; `C` is the address of that slab
+ * inside this GPU's full C, and peer_c[i] the address of the same slab inside the full C of
+ * another GPU, mapped into this process (kcg_peer_open). Every finished tile is written to
+ * all of them from the kernel's epilogue with plain 16-byte stores (over NVLink for the peers):
+ * no remote loads, no flags or waits; the full C is complete on a GPU once the kernels of all
+ * ranks have completed (synchronise the streams, then barrier). 16-bit single-pass tcgen05
+ * kernels only (KCG_KERNEL_TCGEN05 / _PAIR with fp16 / bf16 data); n_peers = 0 is
+ * kcg_launch_gemm_ex. KCG_MAX_PEERS = 7. */
+int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                              uint64_t A, uint64_t B, uint64_t C, const kcg_epilogue* epi,
+                              const uint64_t* peer_c, int n_peers);
+/* Device memory that other processes of the node can map: alloc + 64-byte CUDA IPC handle on
+ * the owner, open / close on the others, free on the owner after every peer closed it. */
+int kcg_peer_alloc(int device, uint64_t bytes, uint64_t* dptr, uint8_t handle[64]);
+int kcg_peer_open(int device, const uint8_t handle[64], uint64_t* dptr);
+int kcg_peer_close(int device, uint64_t dptr);
+int kcg_peer_free(int device, uint64_t dptr);
+
 /* Reads (and clears) the device status word written by bounded waits; returns
  * KCG_E_DEVICE_TIMEOUT if a kernel gave up since the last check. Synchronises `stream`. */
 int kcg_check_status(int device, uint64_t stream);

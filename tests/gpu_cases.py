@@ -123,4 +123,7 @@ def all_configs():
     for (_, m, n, k, dt, keys) in [BIG_FP32, BIG_BF16] + RECT:
         out.append(default_config(m, n, k, dt, **keys))
     out.append(default_config(BIG_BF16[1] // 8, BIG_BF16[2], BIG_BF16[3], BIG_BF16[4], **BIG_BF16_SLAB))
+    # per-rank slabs of the two-GPU fused all-gather test (tests/helpers_allgather_ranks.py)
+    for keys in (dict(), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), dict(LOCAL_SPLIT_U=2)):
+        out.append(default_config(1024, 1024, 1024, E.bfloat16, **keys))
     return out

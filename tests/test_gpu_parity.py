@@ -135,6 +135,53 @@ def test_matmul_op_fuses_bias_relu_chain():
     assert oracle.rel_errors(y, h_ref.float() @ w2.float())["max_rel"] <= 2e-2
 
 
+@pytest.mark.parametrize("case", [c for c in gpu_cases.FUSED if c[0] in (
+    "bf16_tma_store", "fp16_tma_store", "bf16_pair", "bf16_splitk_reduce")], ids=lambda c: c[0])
+def test_fused_allgather_stores_reach_every_target(case):
+    """The all-gather epilogue on one GPU: the 'peers' are three more buffers of this GPU, so the
+    kernel's extra stores (staged path and K-split reduction) are checked without a second device."""
+    _, M, N, K, dt, dist, keys = case
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, N, K, tdt, dist, seed=6)
+    _, kern = build_kernel(default_config(M, N, K, dt, **keys), 0)
+    a, b = A.cuda(), B.cuda()
+    c = torch.full((M, N), float("nan"), dtype=tdt, device="cuda:0")
+    peers = [torch.full((M, N), float("nan"), dtype=tdt, device="cuda:0") for _ in range(3)]
+    kern.run(a, b, c, peers=peers)
+    kern.checkStatus()
+    assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.tolerance_for(tdt)
+    for pc in peers:
+        assert torch.equal(pc, c)
+    # with a fused epilogue the peers receive the finished values too
+    bias = torch.linspace(-1, 1, N).to(tdt).cuda()
+    kern.run(a, b, c, peers=peers[:1], bias=bias, relu=True)
+    kern.checkStatus()
+    assert torch.equal(peers[0], c) and not torch.equal(peers[1], c)
+
+
+def test_fused_allgather_rejects_kernels_without_a_staged_epilogue():
+    _, kern = build_kernel(default_config(256, 256, 256, E.float32, BLOCK_SIZE_N=128), 0)
+    x = torch.zeros(256, 256, device="cuda:0")
+    with pytest.raises(_lib.KCGError) as ei:
+        kern.run(x, x, x.clone(), peers=[x.clone()])
+    assert ei.value.code == _lib.E_BAD_CONFIG
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fused_allgather_two_gpus():
+    """Two ranks, one GPU each: every rank's full C holds both slabs after one fused launch per rank."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29631",
+                        os.path.join(root, "tests", "helpers_allgather_ranks.py")],
+                       cwd=root, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("ALLGATHER_OK") == 2, r.stdout[-3000:]
+
+
 def test_host_buffer_entry_matches_device_entry():
     A, B = oracle.make_inputs(512, 512, 512, torch.bfloat16, "normal", seed=1)
     kpm = default_config(512, 512, 512, E.bfloat16)

@@ -185,6 +185,32 @@ def test_m_sharded_gemm_over_two_gloo_ranks(tmp_path):
     assert "SHARD_OK rank0" in out.stdout and "SHARD_OK rank1" in out.stdout
 
 
+def test_fused_allgather_targets_and_argument_checks():
+    """Where a rank's slab goes in every GPU's full C, and what the launch entry refuses (checked before any
+    driver call, so it runs without a GPU)."""
+    import ctypes
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    bases = [0x1000000, 0x2000000, 0x3000000, 0x4000000]
+    mine, peers = kdist.slab_targets(2, bases, 4096)
+    assert mine == 0x3000000 + 2 * 4096 and peers == [b + 2 * 4096 for b in (0x1000000, 0x2000000, 0x4000000)]
+    with pytest.raises(ValueError):
+        kdist.slab_targets(4, bases, 4096)
+    with pytest.raises(ValueError):
+        kdist.slab_targets(0, list(range(9)), 16)
+    lib = _lib.get_lib()
+    bf16 = compile_info(default_config(256, 512, 512, E.bfloat16).compileArgs())
+    f32 = compile_info(default_config(256, 256, 256, E.float32, BLOCK_SIZE_N=128).compileArgs())
+    arr = (ctypes.c_uint64 * 8)(*([0x100] * 8))
+    rc = lib.kcg_launch_gemm_allgather(1, ctypes.byref(bf16), 0, 0, 256, 256, 256, None, arr, 8)
+    assert rc == _lib.E_BAD_ARG and b"n_peers" in lib.kcg_last_error()
+    rc = lib.kcg_launch_gemm_allgather(1, ctypes.byref(f32), 0, 0, 256, 256, 256, None, arr, 1)
+    assert rc == _lib.E_BAD_CONFIG and b"single-pass" in lib.kcg_last_error()
+    arr[0] = 0x108  # not 16-byte aligned
+    rc = lib.kcg_launch_gemm_allgather(1, ctypes.byref(bf16), 0, 0, 256, 256, 256, None, arr, 1)
+    assert rc == _lib.E_BAD_ARG and b"aligned" in lib.kcg_last_error()
+
+
 def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     from codegendemo_b200.kcg.InfoDb import KernelDb
     from codegendemo_b200.kcg.matmul_op import tuned_config
