@@ -55,6 +55,8 @@ def prebuilt_configs():
             default_config(4096, 4096, 4096, E.float32, **simt), tuned_config(8192, 8192, 8192, E.bfloat16)]
     for g in (1, 2, 4, 8):
         cfgs.append(tuned_config(32768 // g, 8192, 8192, E.bfloat16))
+        if g > 1:  # tile of the bench's fused GEMM + all-gather leg (two TMEM accumulator buffers)
+            cfgs.append(default_config(32768 // g, 8192, 8192, E.bfloat16))
     return cfgs
 
 

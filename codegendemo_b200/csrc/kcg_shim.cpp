@@ -838,6 +838,10 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
       if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(N) * eb, 128 / eb, 32,
                              3 /*CU_TENSOR_MAP_SWIZZLE_128B*/))
         return e;
+      for (int i = 0; i < n_peers; ++i)  // the same boxes over every peer's copy of this slab
+        if (int e = encode_map(s, &p.tmPeer[i], info->dtype, peer_c[i], N, M, static_cast<uint64_t>(N) * eb,
+                               128 / eb, 32, 3))
+          return e;
     }
     // K splitting: LOCAL_SPLIT_U > 1 splits every tile; otherwise only the tiles of the last,
     // partially filled wave of the persistent grid are split so that it fills the GPU

@@ -427,29 +427,11 @@ struct TcGemm {
               const int col0 = w.n0 + g * SCOLS;
               if (lane == 0 && row0 < p.M && col0 < p.N) {
                 tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
+                // Fused all-gather: the same staged block also goes to this rank's rows of every
+                // peer's C, one bulk store per peer (over NVLink). They read the same buffer and
+                // share the bulk group, so the buffer is reused only after all of them have read it.
+                for (int pe = 0; pe < p.n_peers; ++pe) tma_store_2d(&p.tmPeer[pe], buf, col0, row0);
                 tma_store_commit();
-              }
-              if (p.n_peers > 0) {
-                // Fused all-gather: the same block goes to this rank's rows of every peer's C.
-                // Lane l re-reads 16-byte unit (l & 7) of rows 4i + l / 8, so that eight lanes
-                // write one full 128-byte line and a warp store covers four rows.
-                uint4 unit[8];
-                const int uj = lane & 7;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const int ur = 4 * i + (lane >> 3);
-                  unit[i] = *reinterpret_cast<const uint4*>(buf + ur * 128 + ((uj ^ (ur & 7)) << 4));
-                }
-                const int ucol = col0 + uj * (16 / static_cast<int>(sizeof(OutT)));
-                for (int pe = 0; pe < p.n_peers; ++pe) {
-                  OutT* pc = reinterpret_cast<OutT*>(p.peerC[pe]);
-#pragma unroll
-                  for (int i = 0; i < 8; ++i) {
-                    const int urow = row0 + 4 * i + (lane >> 3);
-                    if (urow < p.M && ucol < p.N)
-                      *reinterpret_cast<uint4*>(pc + static_cast<size_t>(urow) * p.ldc + ucol) = unit[i];
-                  }
-                }
               }
             }
           }
