@@ -154,6 +154,21 @@ constexpr int tc_staging_bytes(int dtype, int x3) {
   return (dtype == KCG_DT_F32 && x3) ? 0 : 4 * 2 * 32 * 128;
 }
 
+// 3xTF32 kernel: depth of the ring of lo twins beside `stages` TMA-fed hi stages. The kernel
+// supports a shorter lo ring, but measured on 4096^3 every shorter ring lost: the splitter must
+// run about 2 us (hand-offs + 2 x 32 KB of shared-memory traffic) ahead of the MMAs, i.e. three
+// 32-wide or four 16-wide K blocks, which is what equal rings give (pair 256x256x32: 3 hi + 3 lo
+// 215-229 TFLOP/s, 3 + 2 158, 4 + 3 162, 5 + 2 163; single 128x256x16: 4 + 4 214, 4 + 3 144,
+// 6 + 3 150). So the lo ring is as deep as the hi ring.
+constexpr int tc_lo_stages(int stages) { return stages; }
+
+// Bytes of the operand rings: single-pass kernel stages * (A + B tile); 3xTF32 adds the lo ring.
+constexpr int tc_ring_bytes(int dtype, int BM, int BN, int BK, int stages, int x3) {
+  const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
+  const int stage = (BM + BN) * BK * eb;
+  return stage * (stages + ((eb == 4 && x3) ? tc_lo_stages(stages) : 0));
+}
+
 // Shape rules of the tcgen05 kernels; returns 0 when the config is buildable.
 constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int x3) {
   const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
@@ -168,16 +183,13 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
   if ((BK % (32 / eb)) != 0 || (BK % 8) != 0) return 6;
   if (eb == 2 && (BK % 16) != 0) return 6;
   if (stages < 2 || stages > 12) return 7;
-  const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
-  if (stage * stages + 2048 + tc_staging_bytes(dtype, x3) > 227 * 1024) return 8;
+  if (tc_ring_bytes(dtype, BM, BN, BK, stages, x3) + 2048 + tc_staging_bytes(dtype, x3) > 227 * 1024) return 8;
   return 0;
 }
 
 constexpr int tc_smem_bytes(int dtype, int BM, int BN, int BK, int stages, int x3) {
-  const int eb = (dtype == KCG_DT_F32) ? 4 : 2;
-  const int stage = (BM + BN) * BK * eb * ((eb == 4 && x3) ? 2 : 1);
   // +1024 alignment slack, +1024 barriers / TMEM holder / flags, + epilogue staging
-  return stage * stages + 2048 + tc_staging_bytes(dtype, x3);
+  return tc_ring_bytes(dtype, BM, BN, BK, stages, x3) + 2048 + tc_staging_bytes(dtype, x3);
 }
 
 }  // namespace kcg

@@ -52,7 +52,12 @@ struct TcGemmF32x3 {
   static_assert(kBN % 64 == 0, "each epilogue warp drains whole 32-column pieces of its column half");
   static constexpr int TMEM_COLS = kc_pow2_ceil(2 * ACC_COLS);
   static constexpr int STAGE_HI = L.stage_hi_bytes;
-  static constexpr int STAGE_BYTES = 2 * STAGE_HI;
+  // Two rings: kStages stages of TMA-landed hi operands (deep, to cover the load latency) and
+  // LO_STAGES stages of their lo twins, written just in time by the splitter warps: lo stage
+  // it % LO_STAGES is free again as soon as the MMAs of K block it - LO_STAGES have retired.
+  static constexpr int LO_STAGES = tc_lo_stages(kStages);
+  static constexpr int LO_RING = kStages * STAGE_HI;  // byte offset of the lo ring
+  static constexpr int RING_BYTES = (kStages + LO_STAGES) * STAGE_HI;
   static constexpr int KSTEPS = kBK / UMMA_K;
   static constexpr int NUM_THREADS = 512;
   static constexpr int NUM_SPLIT_THREADS = 128;
@@ -67,7 +72,7 @@ struct TcGemmF32x3 {
   struct Barriers {
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    uint64_t split_full[kStages];
+    uint64_t split_full[LO_STAGES];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint32_t tmem_base;
@@ -141,7 +146,7 @@ struct TcGemmF32x3 {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-    Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + RING_BYTES);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -156,8 +161,9 @@ struct TcGemmF32x3 {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
-        mbar_init(&bars->split_full[s], 4 * NCTA);  // one arrival per splitter warp of each CTA
       }
+      for (int s = 0; s < LO_STAGES; ++s)
+        mbar_init(&bars->split_full[s], 4 * NCTA);  // one arrival per splitter warp of each CTA
       for (int a = 0; a < 2; ++a) {
         mbar_init(&bars->tmem_full[a], 1);
         mbar_init(&bars->tmem_empty[a], 8 * NCTA);  // one arrival per accumulating warp of each CTA
@@ -205,7 +211,7 @@ struct TcGemmF32x3 {
               ok = false;
               break;
             }
-            uint8_t* sa = smem + s * STAGE_BYTES;
+            uint8_t* sa = smem + s * STAGE_HI;
             uint8_t* sb = sa + L.a_bytes;
             mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
             const int k0 = (w.kb0 + kb) * kBK;
@@ -243,15 +249,19 @@ struct TcGemmF32x3 {
             const int kb1 = (kb0 + kChunk < w.kbn) ? kb0 + kChunk : w.kbn;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
               const uint32_t s = it % kStages;
-              const uint32_t ph = (it / kStages) & 1u;
-              if (!mbar_wait(&bars->split_full[s], ph, &bars->abort_flag)) {
+              const uint32_t sl = it % LO_STAGES;
+              const uint32_t phl = (it / LO_STAGES) & 1u;
+              // the lo twin is written after the hi stage has landed (in both CTAs of a pair)
+              if (!mbar_wait(&bars->split_full[sl], phl, &bars->abort_flag)) {
                 report(p, bars, KCG_ST_TIMEOUT_MMA, it, s);
                 ok = false;
                 break;
               }
               tc_fence_after_sync();
-              const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+              const uint32_t sa = smem_u32(smem + s * STAGE_HI);
               const uint32_t sb = sa + L.a_bytes;
+              const uint32_t sa_lo = smem_u32(smem + LO_RING + sl * STAGE_HI);
+              const uint32_t sb_lo = sa_lo + L.a_bytes;
 #pragma unroll
               for (int ks = 0; ks < KSTEPS; ++ks) {
                 uint32_t a_off;
@@ -265,14 +275,14 @@ struct TcGemmF32x3 {
                 const uint32_t first = (kb > kb0 || ks > 0) ? 1u : 0u;
                 const uint64_t bdesc = make_smem_desc(sb + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
                 const uint64_t bdesc_lo =
-                    make_smem_desc(sb + STAGE_HI + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
+                    make_smem_desc(sb_lo + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
 #pragma unroll
                 for (int t = 0; t < MT; ++t) {
                   const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
                                                : t * 128 * (L.a_box_bytes / R);
                   const uint64_t adesc =
                       make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
-                  const uint64_t adesc_lo = make_smem_desc(sa + STAGE_HI + a_t + a_off, L.a_lbo,
+                  const uint64_t adesc_lo = make_smem_desc(sa_lo + a_t + a_off, L.a_lbo,
                                                            L.a_sbo, L.a_desc_swizzle);
                   const uint32_t d = tmem_acc + t * kBN;
                   if constexpr (kPair) {
@@ -286,7 +296,9 @@ struct TcGemmF32x3 {
                   }
                 }
               }
-              if constexpr (kPair) {  // the stage is free in both CTAs once these MMAs retire
+              // the hi stage, and with it the lo stage of this K block, is free in both CTAs
+              // once these MMAs retire
+              if constexpr (kPair) {
                 umma_commit_pair(smem_u32(&bars->empty[s]));
                 umma_commit_pair(map_to_cta(smem_u32(&bars->empty[s]), 1u));
               } else {
@@ -315,13 +327,24 @@ struct TcGemmF32x3 {
         for (int kb = 0; kb < w.kbn; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
-          if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
+          const uint32_t sl = it % LO_STAGES;
+          // lo stage sl was last read by the MMAs of K block it - LO_STAGES; their retirement is
+          // what completes that block's phase of its hi stage's `empty` barrier. The MMA warp
+          // never runs ahead of this loop, so that barrier cannot be a whole phase further on.
+          bool got = true;
+          // (with rings of equal depth the landed hi stage already implies it)
+          if (LO_STAGES < kStages && it >= static_cast<uint32_t>(LO_STAGES)) {
+            const uint32_t prev = it - LO_STAGES;
+            got = mbar_wait(&bars->empty[prev % kStages], (prev / kStages) & 1u, &bars->abort_flag);
+          }
+          if (got) got = mbar_wait(&bars->full[s], ph, &bars->abort_flag);
+          if (!got) {
             if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_SPLITTER, it, s);
             ok = false;
             break;
           }
-          const uint4* hi = reinterpret_cast<const uint4*>(smem + s * STAGE_BYTES);
-          uint4* lo = reinterpret_cast<uint4*>(smem + s * STAGE_BYTES + STAGE_HI);
+          const uint4* hi = reinterpret_cast<const uint4*>(smem + s * STAGE_HI);
+          uint4* lo = reinterpret_cast<uint4*>(smem + LO_RING + sl * STAGE_HI);
 #pragma unroll 4
           for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
             const uint4 x = hi[i];
@@ -336,9 +359,9 @@ struct TcGemmF32x3 {
           __syncwarp();
           if (lane == 0) {
             if constexpr (kPair) {
-              mbar_arrive_cluster(map_to_cta(smem_u32(&bars->split_full[s]), 0u));
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars->split_full[sl]), 0u));
             } else {
-              mbar_arrive(&bars->split_full[s]);
+              mbar_arrive(&bars->split_full[sl]);
             }
           }
         }

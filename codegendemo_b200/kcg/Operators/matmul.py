@@ -224,9 +224,10 @@ class TuningSpaceChecker_Matmul:
             return False
         if bk % (32 // eb) or bk % 8 or (eb == 2 and bk % 16):
             return False
-        stage = (bm + bn) * bk * eb * (2 if eb == 4 else 1)
+        stage = (bm + bn) * bk * eb
+        lo = stages if eb == 4 else 0  # 3xTF32: a ring of lo twins as deep as the ring of hi stages
         staging = 0 if eb == 4 else 32768  # TMA-store staging of the 16-bit kernel's epilogue
-        return stage * stages + 2048 + staging <= MAX_SHARED_BYTES
+        return stage * (stages + lo) + 2048 + staging <= MAX_SHARED_BYTES
 
     @staticmethod
     def check_simt_loads(config: Dict) -> bool:

@@ -140,7 +140,8 @@ def test_pair_variant_launch_geometry():
                          BLOCK_SIZE_K=32, NUM_STAGES=3)
     i2 = compile_info(f32.compileArgs(), num_stages=3, kernel=4)
     assert i2.block[0] == 512 and list(i2.cluster) == [2, 1, 1]
-    assert i2.smem_bytes == 3 * 2 * (128 + 128) * 32 * 4 + 2048  # hi + lo twins of the per-CTA slices
+    # three TMA-fed hi stages of the per-CTA slices + a ring of three lo twins
+    assert i2.smem_bytes == (3 + 3) * (128 + 128) * 32 * 4 + 2048
 
 
 def test_cubin_cache_is_keyed_by_the_kernel_sources(tmp_path):
