@@ -94,12 +94,14 @@ int setup_device(int device, PerDevice** out) {
   return 0;
 }
 
-int encode(CUtensorMap* tm, uint64_t ptr, uint64_t inner, uint64_t outer, int box_inner, int box_outer, int swizzle) {
+int encode(CUtensorMap* tm, uint64_t ptr, uint64_t inner, uint64_t outer, int box_inner, int box_outer, int swizzle,
+           bool fp32 = false) {
   cuuint64_t gdim[2] = {inner, outer};
-  cuuint64_t gstride[1] = {inner * 2};
+  cuuint64_t gstride[1] = {inner * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_outer)};
   cuuint32_t estr[2] = {1, 1};
-  const CUresult r = g_encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptr), gdim, gstride,
+  const CUresult r = g_encode(tm, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                              reinterpret_cast<void*>(ptr), gdim, gstride,
                               box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(swizzle),
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(static_cast<int>(r), "cuTensorMapEncodeTiled failed");
@@ -137,6 +139,11 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
   constexpr kcg::TcLayout L = kcg::make_tc_layout(KCG_DT_BF16, kBM, kBN, kBK, 0);
   if (int e = encode(&p.tmA, A, K, M, L.a_box_inner, L.a_box_outer, L.a_tma_swizzle)) return e;
   if (int e = encode(&p.tmB, B, N, K, L.b_box_inner, L.b_box_outer, L.b_tma_swizzle)) return e;
+  // partial tiles leave through TMA stores: the scratch array as one tall fp32 matrix of kBN
+  // columns, 32 x 32 boxes with the 128B swizzle of the kernel's staging buffers
+  if (int e = encode(&p.tmWs, reinterpret_cast<uint64_t>(d->scratch), kBN, kPartialBytes / (kBN * 4), 32, 32,
+                     3 /*CU_TENSOR_MAP_SWIZZLE_128B*/, true))
+    return e;
   p.A = reinterpret_cast<const void*>(A);
   p.B = reinterpret_cast<const void*>(B);
   p.C = reinterpret_cast<void*>(C);

@@ -585,6 +585,91 @@ int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64
   return 0;
 }
 
+// How a tcgen05 launch cuts its tiles into work units (see kernels/work_iter.cuh).
+struct SplitPlan {
+  int tiles, first, factor, sk_per, sk_ranges, units_at_once;
+};
+
+SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue) {
+  const int M = info->m, N = info->n, K = info->k;
+  const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
+  const bool x3 = info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1;
+  // K splitting. LOCAL_SPLIT_U > 1 splits every tile evenly. Otherwise the tail of the persistent
+  // grid - the last, partially filled wave, together with the full wave before it when it is less
+  // than half full - runs as stream-K: the K blocks of those tiles, laid end to end, are cut into
+  // one contiguous range per CTA (pair), so that every SM works for the same time; tiles that fall
+  // into several ranges are reduced like an even split. KCG_TAIL_SPLIT=0 turns it off, =2 selects
+  // the even split of the last wave's tiles by floor(G / remainder) instead.
+  const int T = (M / info->bm) * (N / info->bn);
+  const int num_kb = K / info->bk;
+  const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
+  const int G = pair ? nsm / 2 : nsm;  // work units that run at once (CTAs, or CTA pairs)
+  int first = T, factor = 1, sk_per = 0, sk_ranges = 0;
+  if (info->splitk > 1) {
+    first = 0;
+    factor = info->splitk;
+  } else {
+    const char* e = getenv("KCG_TAIL_SPLIT");
+    // Default: stream-K for the single-pass kernel, whose partials move as full lines; the 3xTF32
+    // kernel stores its partials straight from registers and measured better with the even split
+    // of the last wave only (512x11008x11008 fp32: 214 vs 199 TFLOP/s, 4096^3: 228 vs 222).
+    const int mode = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : (e && e[0] == '1') ? 1 : (x3 ? 2 : 1);
+    const int rem = T % G;
+    if (mode != 0 && rem > 0) {
+      // Worth it only when the time saved exceeds the cost of the split: estimate a tile's
+      // main-loop time from a per-SM rate of ~10 MFLOP/us (16-bit) or ~1.4 MFLOP/us useful (fp32
+      // as 3xTF32).
+      const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1) ? 1.4
+                                  : (info->dtype == KCG_DTYPE_FLOAT32)                                     ? 4.5
+                                                                                                           : 10.0;
+      const double tile_us =
+          2.0 * (info->bm / (pair ? 2 : 1)) * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
+      // What a split costs a CTA: its fp32 partial goes to the workspace once, the reducing CTA
+      // reads two or three of them back and writes C, and each extra unit refills the pipeline.
+      // Measured on 512x11008x11008 bf16: ~28 us for a 128 KB partial (128 x 256 rows per CTA),
+      // ~51 us for 256 KB; the 3xTF32 kernel stores its partials straight from registers, about
+      // twice as slow. The saving has to beat that with a margin.
+      const double partial_kb = (info->bm / (pair ? 2 : 1)) * static_cast<double>(info->bn) * 4.0 / 1024.0;
+      const double overhead_us = (5.0 + 0.18 * partial_kb) * (x3 ? 2.0 : 1.0);
+      const double gate_us = 1.25 * overhead_us;
+      if (mode == 2) {
+        int f = G / rem;
+        if (f > 8) f = 8;
+        if (f > num_kb) f = num_kb;
+        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= gate_us) {
+          first = T - rem;
+          factor = f;
+        }
+      } else {
+        const int R = (T > G && 2 * rem < G) ? rem + G : rem;  // tiles handed to stream-K
+        long long ranges = G;
+        if (ranges > 8LL * R) ranges = 8LL * R;  // at most ~8 contributors per tile
+        const long long blocks = static_cast<long long>(R) * num_kb;
+        if (ranges > blocks) ranges = blocks;
+        const long long per = (blocks + ranges - 1) / ranges;
+        ranges = (blocks + per - 1) / per;  // no empty range
+        const double waves_without = static_cast<double>((R + G - 1) / G);
+        const double saved_us = tile_us * (waves_without - static_cast<double>(R) / static_cast<double>(ranges));
+        if (saved_us >= gate_us) {
+          first = T - R;
+          sk_per = static_cast<int>(per);
+          sk_ranges = static_cast<int>(ranges);
+        }
+      }
+    }
+  }
+  // The 3xTF32 kernel applies a fused epilogue in its reduction loop only (its register file is
+  // full of accumulators at the direct store), so a fused launch sends every tile through the
+  // workspace as a one-way split; the tail split is not combined with it.
+  const bool ws_epilogue = x3 && fused_epilogue;
+  if (ws_epilogue && info->splitk <= 1) {
+    first = 0;
+    factor = 1;
+    sk_per = 0;
+  }
+  return SplitPlan{T, first, factor, sk_per, sk_ranges, G};
+}
+
 }  // namespace
 
 // ============================================================================ C ABI
@@ -594,6 +679,19 @@ extern "C" {
 // kcg_last_error() and count their launches.
 int kcg_internal_fail(int code, const char* msg) { return fail(code, "%s", msg); }
 void kcg_internal_count_launch(void) { g_launches.fetch_add(1); }
+// Internal (tests): the work decomposition a launch of `info` would use:
+// {tiles, split_first_tile, split_factor, sk_per, stream-K ranges, units that run at once}.
+int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int out[6]) {
+  if (!info || !out) return fail(KCG_E_BAD_ARG, "null argument");
+  const SplitPlan pl = plan_split(info, fused_epilogue != 0);
+  out[0] = pl.tiles;
+  out[1] = pl.first;
+  out[2] = pl.factor;
+  out[3] = pl.sk_per;
+  out[4] = pl.sk_ranges;
+  out[5] = pl.units_at_once;
+  return 0;
+}
 
 const char* kcg_last_error(void) { return g_last_error.c_str(); }
 const char* kcg_version(void) { return "kcg-b200 0.1 (sm_100a)"; }
@@ -843,53 +941,20 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
                                128 / eb, 32, 3))
           return e;
     }
-    // K splitting: LOCAL_SPLIT_U > 1 splits every tile; otherwise only the tiles of the last,
-    // partially filled wave of the persistent grid are split so that it fills the GPU
-    // (KCG_TAIL_SPLIT=0 turns that off).
-    const int T = (M / info->bm) * (N / info->bn);
-    const int num_kb = K / info->bk;
-    const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
-    const int G = pair ? nsm / 2 : nsm;  // work units that run at once (CTAs, or CTA pairs)
-    int first = T, factor = 1;
-    if (info->splitk > 1) {
-      first = 0;
-      factor = info->splitk;
-    } else {
-      const char* e = getenv("KCG_TAIL_SPLIT");
-      const int rem = T % G;
-      if (!(e && e[0] == '0') && rem > 0) {
-        int f = G / rem;
-        if (f > 8) f = 8;
-        if (f > num_kb) f = num_kb;
-        // Worth it only when the time saved on the last wave exceeds the cost of the reduction
-        // (partials through L2, one extra round trip): estimate the tile's main-loop time from
-        // a per-SM rate of ~10 MFLOP/us (16-bit) or ~1.4 MFLOP/us useful (fp32 as 3xTF32).
-        const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1) ? 1.4
-                                    : (info->dtype == KCG_DTYPE_FLOAT32)                                     ? 4.5
-                                                                                                             : 10.0;
-        const double tile_us =
-            2.0 * (info->bm / (pair ? 2 : 1)) * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
-        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= 20.0) {
-          first = T - rem;
-          factor = f;
-        }
-      }
-    }
-    // The 3xTF32 kernel applies a fused epilogue in its reduction loop only (its register file is
-    // full of accumulators at the direct store), so a fused launch sends every tile through the
-    // workspace as a one-way split; the tail split is not combined with it.
+    const SplitPlan plan = plan_split(info, p.epi_flags != 0u);
+    const int T = plan.tiles, first = plan.first, factor = plan.factor, sk_per = plan.sk_per,
+              sk_ranges = plan.sk_ranges, G = plan.units_at_once;
     const bool ws_epilogue = x3 && p.epi_flags != 0u;
-    if (ws_epilogue && info->splitk <= 1) {
-      first = 0;
-      factor = 1;
-    }
-    const int units = first + (T - first) * factor;
+    const int units = sk_per > 0 ? sk_ranges : first + (T - first) * factor;
     grid0 = (units < G ? units : G) * (pair ? 2 : 1);
     p.split_first_tile = first;
     p.split_factor = factor;
-    if (factor > 1 || ws_epilogue) {
+    p.sk_per = sk_per;
+    if (factor > 1 || ws_epilogue || sk_per > 0) {
       std::lock_guard<std::mutex> g(g_dev_mutex);
-      const size_t slots = static_cast<size_t>(T - first) * factor;
+      // slots: one per (tile, split) of an even split; range index + tile index under stream-K
+      const size_t slots = sk_per > 0 ? static_cast<size_t>(sk_ranges) + (T - first)
+                                      : static_cast<size_t>(T - first) * factor;
       const size_t need = slots * info->bm * info->bn * sizeof(float);
       if (int e = grow(&s->ws, &s->ws_bytes, need)) return e;
       const size_t tiles = static_cast<size_t>(T - first) * (pair ? 2 : 1);  // one counter per CTA half
@@ -901,6 +966,15 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
       }
       p.splitk_ws = reinterpret_cast<float*>(s->ws);
       p.tile_counters = reinterpret_cast<unsigned int*>(s->counters);
+    }
+    if (!x3 && (factor > 1 || sk_per > 0)) {
+      // The single-pass kernel writes its partial tiles with TMA stores: the workspace as one tall
+      // fp32 matrix of BN columns (every row the buffer holds, so that the map is reused while the
+      // buffer is), 32 x 32 boxes with the 128B swizzle of the staging buffers.
+      const uint64_t row_bytes = static_cast<uint64_t>(info->bn) * 4;
+      if (int e = encode_map(s, &p.tmWs, KCG_DTYPE_FLOAT32, static_cast<uint64_t>(s->ws), info->bn,
+                             s->ws_bytes / row_bytes, row_bytes, 32, 32, 3))
+        return e;
     }
   }
   void* args[1] = {&p};

@@ -43,6 +43,7 @@ struct alignas(64) KcgGemmParams {
   CUtensorMap tmB;  // tiled map of B (K x N row-major)
   CUtensorMap tmC;  // C as 32-row x 128-byte boxes (128B swizzle): the TMA-store epilogue
   CUtensorMap tmPeer[KCG_MAX_PEERS];  // the same boxes over peerC[i] (fused all-gather)
+  CUtensorMap tmWs;  // K-split workspace as one tall fp32 matrix of BN columns, 32 x 32 boxes
   const void* A;
   const void* B;
   void* C;
@@ -56,6 +57,10 @@ struct alignas(64) KcgGemmParams {
   // (first = 0, factor = S); with LOCAL_SPLIT_U = 1 the launcher splits only the tiles of the last,
   // partially filled wave of the persistent grid (or nothing: factor = 1).
   int split_first_tile, split_factor;
+  // Stream-K over the tiles from split_first_tile on (instead of the even split) when > 0: their
+  // K blocks, laid end to end, are cut into one contiguous range of sk_per blocks per CTA (pair);
+  // the grid then has exactly as many CTAs (pairs) as there are ranges (work_iter.cuh).
+  int sk_per;
   // Fused epilogue, in force when epi_flags != 0: D = act(alpha * (A.B) + beta * C + bias[col]),
   // computed in fp32 before the rounding to C's type. beta * C reads C in place (skipped when
   // beta == 0, so C may then hold anything); bias has N values of C's type.

@@ -10,9 +10,10 @@
 //   warps 2..5    epilogue: tcgen05.ld the accumulator (one TMEM lane = one C
 //                 row per thread), convert, stage 32 x 128-byte blocks in swizzled
 //                 shared memory and write C with TMA stores (full 128-byte lines,
-//                 asynchronous). K-split partials go to the workspace with vector
-//                 stores. With two accumulator buffers the epilogue overlaps the
-//                 next tile's main loop.
+//                 asynchronous). K-split partials leave the same way as fp32 blocks
+//                 into the workspace; the last contributor of a tile sums them with
+//                 coalesced loads. With two accumulator buffers the epilogue overlaps
+//                 the next tile's main loop.
 //
 // fp32 data runs here as ONE TF32 pass (comparison only); the accurate fp32 path
 // is gemm_tcgen05_f32x3.cuh.
@@ -34,6 +35,7 @@
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
+#include "work_iter.cuh"
 
 namespace kcg {
 
@@ -88,50 +90,8 @@ struct TcGemm {
   };
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
-  struct Unit {
-    int m0, n0, tile, split, nsplit, slot, kb0, kbn;
-  };
-
-  // Work unit u -> output tile (grouped raster, matmul.cpp:79-86 semantics:
-  // groups of kGroup tile-rows walk N first so a wave shares A and B in L2)
-  // and K range of this split.
-  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb,
-                                                     int first_split, int factor) {
-    Unit w;
-    if (u < first_split) {
-      w.tile = u;
-      w.split = 0;
-      w.nsplit = 1;
-      w.slot = 0;
-    } else {
-      const int v = u - first_split;
-      w.tile = first_split + v / factor;
-      w.split = v - (w.tile - first_split) * factor;
-      w.nsplit = factor;
-      w.slot = v;
-    }
-    int mb, nb;
-    if constexpr (kGroup > 1) {
-      const int per_group = kGroup * tiles_n;
-      const int g = w.tile / per_group;
-      const int first_m = g * kGroup;
-      const int gsz = (tiles_m - first_m < kGroup) ? (tiles_m - first_m) : kGroup;
-      const int r = w.tile - g * per_group;
-      mb = first_m + (r % gsz);
-      nb = r / gsz;
-    } else {
-      mb = w.tile / tiles_n;
-      nb = w.tile - mb * tiles_n;
-    }
-    w.m0 = mb * kBM;
-    w.n0 = nb * kBN;
-    const int per = (num_kb + w.nsplit - 1) / w.nsplit;
-    w.kb0 = w.split * per;
-    int kb1 = w.kb0 + per;
-    if (kb1 > num_kb) kb1 = num_kb;
-    w.kbn = (kb1 > w.kb0) ? (kb1 - w.kb0) : 0;
-    return w;
-  }
+  using Unit = WorkUnit;
+  using Iter = WorkIter<kBM, kBN, kGroup>;  // units of this CTA (pair), in order: work_iter.cuh
 
   __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
                                                 uint32_t code, uint32_t d0, uint32_t d1) {
@@ -140,33 +100,6 @@ struct TcGemm {
       p.status[1] = blockIdx.x;
       p.status[2] = d0;
       p.status[3] = d1;
-    }
-  }
-
-  template <typename OutT>
-  __device__ static __forceinline__ void store_chunk(OutT* dst, const float (&v)[32]) {
-    if constexpr (sizeof(OutT) == 4) {
-      float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    } else {
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float lo = v[8 * i + 2 * j], hi = v[8 * i + 2 * j + 1];
-          if constexpr (kDType == KCG_DT_BF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-            w[j] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(lo, hi);
-            w[j] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-        d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
     }
   }
 
@@ -185,8 +118,6 @@ struct TcGemm {
     const int tiles_n = (p.N + kBN - 1) / kBN;
     const int num_kb = (p.K + kBK - 1) / kBK;
     const int first_split = p.split_first_tile;
-    const int split_factor = p.split_factor > 0 ? p.split_factor : 1;
-    const int num_units = first_split + (tiles_m * tiles_n - first_split) * split_factor;
 
     if (threadIdx.x == 0) {
       for (int s = 0; s < kStages; ++s) {
@@ -229,8 +160,9 @@ struct TcGemm {
         tma_prefetch_desc(&p.tmB);
         uint32_t it = 0;
         bool ok = true;
-        for (int u = unit0; u < num_units && ok; u += unit_stride) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+        Unit w;
+        while (ok && units.next(w)) {
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
@@ -280,8 +212,9 @@ struct TcGemm {
       if (lane == 0 && rank == 0u) {
         uint32_t it = 0, acc_it = 0;
         bool ok = true;
-        for (int u = unit0; u < num_units && ok; u += unit_stride, ++acc_it) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+        Unit w;
+        for (; ok && units.next(w); ++acc_it) {
           const uint32_t ab = acc_it % NACC;
           const uint32_t aph = (acc_it / NACC) & 1u;
           if (!mbar_wait(&bars->tmem_empty[ab], aph ^ 1u, &bars->abort_flag)) {
@@ -352,14 +285,14 @@ struct TcGemm {
       // ------------------------------------------------------------ epilogue
       const int q = warp & 3;  // TMEM lane quarter this warp may read
       const int epi_tid = (warp - 2) * 32 + lane;
-      const int row_in_acc = q * 32 + lane;
       uint32_t acc_it = 0;
       OutT* Cout = reinterpret_cast<OutT*>(p.C);
       uint8_t* stg = smem + kStages * STAGE_BYTES + 1024 + (warp - 2) * (2 * STG_BYTES);
       uint32_t stg_it = 0;  // staging buffers this warp has filled
       if (warp == 2 && lane == 0) tma_prefetch_desc(&p.tmC);
-      for (int u = unit0; u < num_units; u += unit_stride, ++acc_it) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+      Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+      Unit w;
+      for (; units.next(w); ++acc_it) {
         const uint32_t ab = acc_it % NACC;
         const uint32_t aph = (acc_it / NACC) & 1u;
         // The warp must leave the wait as one: tcgen05.ld below is warp-collective.
@@ -436,30 +369,40 @@ struct TcGemm {
             }
           }
         } else {
+          // K-split partial: the fp32 accumulators leave through the same staging buffers, as
+          // 32-row x 32-column blocks (128 bytes per row), and TMA stores into the workspace,
+          // whose slots form one tall matrix of kBN columns. Full 128-byte lines: 16-byte stores
+          // straight from each thread's row made L2 read-modify-write every sector and cost
+          // tens of microseconds per partial tile.
 #pragma unroll 1
-        for (int t = 0; t < MT; ++t) {
-          const int row = w.m0 + row_base + t * 128 + row_in_acc;
+          for (int t = 0; t < MT; ++t) {
+            const int wrow0 = w.slot * kBM + row_base + t * 128 + q * 32;
 #pragma unroll 1
-          for (int c = 0; c < kBN / 32; ++c) {
-            float v[32];
-            if (w.kbn > 0) {
+            for (int c = 0; c < kBN / 32; ++c, ++stg_it) {
+              uint8_t* buf = stg + (stg_it & 1u) * STG_BYTES;
+              if (lane == 0) tma_store_wait_read<1>();
+              __syncwarp();
               uint32_t r[32];
-              tmem_ld_32x32b_x32(tmem_acc + t * kBN + c * 32, r);
-              tmem_ld_wait();
+              if (w.kbn > 0) {
+                tmem_ld_32x32b_x32(tmem_acc + t * kBN + c * 32, r);
+                tmem_ld_wait();
+              } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-            } else {
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
+              uint8_t* rowp = buf + lane * 128;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            }
-            const int col = w.n0 + c * 32;
-            if (row < p.M && col < p.N) {
-              float* dst = p.splitk_ws +
-                           (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN + c * 32;
-              store_chunk<float>(dst, v);
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) =
+                    make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&p.tmWs, buf, c * 32, wrow0);
+                tma_store_commit();
+              }
             }
           }
-        }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -475,6 +418,8 @@ struct TcGemm {
           // Publish this split's partial tile; the last split to arrive sums all
           // partials in split order (bitwise reproducible) and writes C.
           const int ctr = (w.tile - first_split) * NCTA + static_cast<int>(rank);  // per CTA half
+          if (lane == 0) tma_store_wait_all<0>();  // this warp's blocks of the partial are written
+          fence_proxy_async_all();                 // ... and ordered before the generic-proxy release below
           __threadfence();
           named_bar_sync(1, NUM_EPI_THREADS);
           if (epi_tid == 0) {
@@ -486,49 +431,73 @@ struct TcGemm {
           const bool last = bars->last_flag != 0u;
           if (last) {
             __threadfence();
-            for (int t = 0; t < MT; ++t) {
-              const int row = w.m0 + row_base + t * 128 + row_in_acc;
-              if (row >= p.M) continue;
-              for (int c = 0; c < kBN / 32; ++c) {
-                const int col = w.n0 + c * 32;
-                if (col >= p.N) continue;
-                float v[32];
+            // Cooperative reduction of this CTA's R rows of the tile: they are contiguous in every
+            // partial, so consecutive threads read consecutive 16-byte pieces (whole 128-byte lines
+            // per quarter warp) and write C the same way. Eight pieces of up to four partials are
+            // fetched before any is added, so that the L2 round trips overlap; the adds run in K order.
+            constexpr int F4_PER_ROW = kBN / 4;
+            constexpr int TOTAL = R * F4_PER_ROW;
+            constexpr int UNR = 8;
+            const size_t slot0 = static_cast<size_t>(w.slot - w.split);
+            for (int base = epi_tid; base < TOTAL; base += NUM_EPI_THREADS * UNR) {
+              float4 acc[UNR];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                // Partials of up to four splits are fetched before any is added, so that
-                // the L2 round trips overlap; the adds still run in split order.
-                for (int s0 = 0; s0 < w.nsplit; s0 += 4) {
-                  float4 x[4][8];
+              for (int u = 0; u < UNR; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s0 = 0; s0 < w.nsplit; s0 += 4) {
+                float4 x[4][UNR];
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    if (s0 + j < w.nsplit) {
-                      const float4* src = reinterpret_cast<const float4*>(
-                          p.splitk_ws +
-                          ((static_cast<size_t>(w.tile - first_split) * w.nsplit + s0 + j) * kBM + row_base +
-                           t * 128 + row_in_acc) *
-                              kBN +
-                          c * 32);
+                for (int j = 0; j < 4; ++j) {
+                  if (s0 + j < w.nsplit) {
+                    const float4* src = reinterpret_cast<const float4*>(
+                        p.splitk_ws + ((slot0 + s0 + j) * kBM + row_base) * kBN);
 #pragma unroll
-                      for (int i = 0; i < 8; ++i) x[j][i] = __ldcg(src + i);
-                    }
-                  }
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    if (s0 + j < w.nsplit) {
-#pragma unroll
-                      for (int i = 0; i < 8; ++i) {
-                        v[4 * i] += x[j][i].x;
-                        v[4 * i + 1] += x[j][i].y;
-                        v[4 * i + 2] += x[j][i].z;
-                        v[4 * i + 3] += x[j][i].w;
-                      }
+                    for (int u = 0; u < UNR; ++u) {
+                      const int idx = base + u * NUM_EPI_THREADS;
+                      if (idx < TOTAL) x[j][u] = __ldcg(src + idx);
                     }
                   }
                 }
-                if (p.epi_flags != 0u) epi_span<OutT, 32>(p, v, row, col);
-                store_chunk<OutT>(Cout + static_cast<size_t>(row) * p.ldc + col, v);
-                for (int pe = 0; pe < p.n_peers; ++pe)
-                  store_chunk<OutT>(reinterpret_cast<OutT*>(p.peerC[pe]) + static_cast<size_t>(row) * p.ldc + col, v);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (s0 + j < w.nsplit) {
+#pragma unroll
+                    for (int u = 0; u < UNR; ++u) {
+                      acc[u].x += x[j][u].x;
+                      acc[u].y += x[j][u].y;
+                      acc[u].z += x[j][u].z;
+                      acc[u].w += x[j][u].w;
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int u = 0; u < UNR; ++u) {
+                const int idx = base + u * NUM_EPI_THREADS;
+                if (idx >= TOTAL) continue;
+                const int row = w.m0 + row_base + idx / F4_PER_ROW;
+                const int col = w.n0 + (idx % F4_PER_ROW) * 4;
+                if (row >= p.M || col >= p.N) continue;
+                float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+                if (p.epi_flags != 0u) epi_span<OutT, 4>(p, o, row, col);
+                const size_t off = static_cast<size_t>(row) * p.ldc + col;
+                if constexpr (sizeof(OutT) == 4) {
+                  const float4 out = make_float4(o[0], o[1], o[2], o[3]);
+                  *reinterpret_cast<float4*>(Cout + off) = out;
+                  for (int pe = 0; pe < p.n_peers; ++pe)
+                    *reinterpret_cast<float4*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+                } else {
+                  uint2 out;
+                  if constexpr (kDType == KCG_DT_BF16) {
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
+                    out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                  } else {
+                    __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
+                    out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                  }
+                  *reinterpret_cast<uint2*>(Cout + off) = out;
+                  for (int pe = 0; pe < p.n_peers; ++pe)
+                    *reinterpret_cast<uint2*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+                }
               }
             }
           }

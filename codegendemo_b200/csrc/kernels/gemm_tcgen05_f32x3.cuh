@@ -26,6 +26,7 @@
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
+#include "work_iter.cuh"
 
 namespace kcg {
 
@@ -81,47 +82,8 @@ struct TcGemmF32x3 {
   };
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
-  struct Unit {
-    int m0, n0, tile, split, nsplit, slot, kb0, kbn;
-  };
-
-  __device__ static __forceinline__ Unit decode_unit(int u, int tiles_m, int tiles_n, int num_kb,
-                                                     int first_split, int factor) {
-    Unit w;
-    if (u < first_split) {
-      w.tile = u;
-      w.split = 0;
-      w.nsplit = 1;
-      w.slot = 0;
-    } else {
-      const int v = u - first_split;
-      w.tile = first_split + v / factor;
-      w.split = v - (w.tile - first_split) * factor;
-      w.nsplit = factor;
-      w.slot = v;
-    }
-    int mb, nb;
-    if constexpr (kGroup > 1) {
-      const int per_group = kGroup * tiles_n;
-      const int g = w.tile / per_group;
-      const int first_m = g * kGroup;
-      const int gsz = (tiles_m - first_m < kGroup) ? (tiles_m - first_m) : kGroup;
-      const int r = w.tile - g * per_group;
-      mb = first_m + (r % gsz);
-      nb = r / gsz;
-    } else {
-      mb = w.tile / tiles_n;
-      nb = w.tile - mb * tiles_n;
-    }
-    w.m0 = mb * kBM;
-    w.n0 = nb * kBN;
-    const int per = (num_kb + w.nsplit - 1) / w.nsplit;
-    w.kb0 = w.split * per;
-    int kb1 = w.kb0 + per;
-    if (kb1 > num_kb) kb1 = num_kb;
-    w.kbn = (kb1 > w.kb0) ? (kb1 - w.kb0) : 0;
-    return w;
-  }
+  using Unit = WorkUnit;
+  using Iter = WorkIter<kBM, kBN, kGroup>;  // units of this CTA (pair), in order: work_iter.cuh
 
   __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
                                                 uint32_t code, uint32_t d0, uint32_t d1) {
@@ -154,8 +116,6 @@ struct TcGemmF32x3 {
     const int tiles_n = (p.N + kBN - 1) / kBN;
     const int num_kb = (p.K + kBK - 1) / kBK;
     const int first_split = p.split_first_tile;
-    const int split_factor = p.split_factor > 0 ? p.split_factor : 1;
-    const int num_units = first_split + (tiles_m * tiles_n - first_split) * split_factor;
 
     if (threadIdx.x == 0) {
       for (int s = 0; s < kStages; ++s) {
@@ -201,8 +161,9 @@ struct TcGemmF32x3 {
         tma_prefetch_desc(&p.tmB);
         uint32_t it = 0;
         bool ok = true;
-        for (int u = unit0; u < num_units && ok; u += unit_stride) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+        Unit w;
+        while (ok && units.next(w)) {
           for (int kb = 0; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
@@ -234,8 +195,9 @@ struct TcGemmF32x3 {
         // ---------------------------- MMA issuer (in a pair: the leader CTA only)
         uint32_t it = 0, chunk_it = 0;
         bool ok = true;
-        for (int u = unit0; u < num_units && ok; u += unit_stride) {
-          const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+        Unit w;
+        while (ok && units.next(w)) {
           for (int kb0 = 0; kb0 < w.kbn && ok; kb0 += kChunk, ++chunk_it) {
             const uint32_t ab = chunk_it & 1u;
             const uint32_t aph = (chunk_it >> 1) & 1u;
@@ -322,8 +284,9 @@ struct TcGemmF32x3 {
       const int stid = threadIdx.x - 128;
       uint32_t it = 0;
       bool ok = true;
-      for (int u = unit0; u < num_units && ok; u += unit_stride) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+      Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+      Unit w;
+      while (ok && units.next(w)) {
         for (int kb = 0; kb < w.kbn; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
@@ -377,8 +340,9 @@ struct TcGemmF32x3 {
       float* Cout = reinterpret_cast<float*>(p.C);
       uint32_t chunk_it = 0;
       bool ok = true;
-      for (int u = unit0; u < num_units && ok; u += unit_stride) {
-        const Unit w = decode_unit(u, tiles_m, tiles_n, num_kb, first_split, split_factor);
+      Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+      Unit w;
+      while (ok && units.next(w)) {
         float acc[ACC_PER_THREAD];
 #pragma unroll
         for (int i = 0; i < ACC_PER_THREAD; ++i) acc[i] = 0.f;
@@ -476,7 +440,7 @@ struct TcGemmF32x3 {
                 for (int s = 0; s < w.nsplit; ++s) {
                   const float4* src = reinterpret_cast<const float4*>(
                       p.splitk_ws +
-                      ((static_cast<size_t>(w.tile - first_split) * w.nsplit + s) * kBM + row_base + t * 128 +
+                      ((static_cast<size_t>(w.slot - w.split) + s) * kBM + row_base + t * 128 +
                        row_in_acc) *
                           kBN +
                       col_half0 + c * 32);

@@ -94,6 +94,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders accesses made through the async proxy (bulk stores to global memory) with the generic
+// proxy's, e.g. before a release that publishes what a TMA store wrote.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void tc_fence_before_sync() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }

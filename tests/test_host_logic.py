@@ -211,6 +211,57 @@ def test_fused_allgather_targets_and_argument_checks():
     assert rc == _lib.E_BAD_ARG and b"aligned" in lib.kcg_last_error()
 
 
+WORK_PLANS = [
+    # (M, N, K, dtype, keys, expected layer: "whole" | "even" | "streamk")
+    (8192, 8192, 8192, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
+    # 50 of 74 pairs busy in the last of 28 waves: the saving is below the cost of 256 KB partials
+    (32768, 8192, 8192, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
+    (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
+    # 86 pair tiles on 74 pairs: all of them go to stream-K (1.16 waves become one)
+    (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=4), "streamk"),
+    (2048, 4096, 4096, E.bfloat16, dict(), "whole"),      # 108 tiles in the last wave: the saving is below the gate
+    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk"),  # small tiles: cheap partials
+    (128, 4096, 4096, E.bfloat16, dict(BLOCK_SIZE_N=128), "whole"),   # too little work per tile to pay for a reduction
+    (128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=4, BLOCK_SIZE_N=256), "even"),
+    # 3xTF32 kernel: even split of the last wave's 68 tiles by two, not stream-K
+    (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4), "even"),
+    (256, 512, 1280, E.bfloat16, dict(LOCAL_SPLIT_U=3), "even"),
+]
+
+
+@pytest.mark.parametrize("case", WORK_PLANS, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-{c[5]}")
+def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
+    """The launcher's plan (whole tiles / even K split / stream-K over the tail) fed to the kernels' own
+    iterator, compiled for the host: every CTA's unit sequence is walked and coverage, contributor numbering
+    and workspace slots are checked (tests/work_iter_check.cpp)."""
+    import ctypes
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    M, N, K, dt, keys, layer = case
+    kpm = default_config(M, N, K, dt, **keys)
+    info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT)
+    out = (ctypes.c_int * 6)()
+    lib = _lib.get_lib()
+    lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
+    assert lib.kcg_internal_plan_split(ctypes.byref(info), 0, out) == 0
+    tiles, first, factor, sk_per, ranges, at_once = list(out)
+    got = "streamk" if sk_per > 0 else "even" if factor > 1 else "whole"
+    assert got == layer, (got, list(out))
+    if sk_per > 0:
+        grid, slots = ranges, ranges + (tiles - first)
+        assert ranges <= at_once and first % at_once == 0
+    else:
+        grid, slots = min(first + (tiles - first) * factor, at_once), (tiles - first) * factor
+    exe = tmp_path / "work_iter_check"
+    kdir = os.path.join(ROOT, "codegendemo_b200", "csrc", "kernels")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-I/usr/local/cuda/include", "-I" + kdir, f"-DWIC_BM={info.bm}",
+                    f"-DWIC_BN={info.bn}", f"-DWIC_BK={info.bk}", f"-DWIC_GROUP={info.group}", "-o", str(exe),
+                    os.path.join(ROOT, "tests", "work_iter_check.cpp")], check=True)
+    r = subprocess.run([str(exe), str(M), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.startswith("OK"), r.stdout + r.stderr
+
+
 def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     from codegendemo_b200.kcg.InfoDb import KernelDb
     from codegendemo_b200.kcg.matmul_op import tuned_config

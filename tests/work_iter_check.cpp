@@ -1,0 +1,88 @@
+// Host-side check of the kernels' work decomposition (kernels/work_iter.cuh), built and run by
+// tests/test_host_logic.py. Walks every CTA's unit sequence for one plan and verifies that
+//   * each tile's K blocks are covered exactly once;
+//   * a tile's contributors are numbered 0..nsplit-1 in K order and all agree on nsplit;
+//   * their workspace slots are slot0 + split, distinct from every other tile's, and below `slots`.
+// usage: work_iter_check M N K first factor sk_per grid slots   (tile and raster group are macros)
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <vector>
+
+#include "work_iter.cuh"
+
+#ifndef WIC_BM
+#define WIC_BM 128
+#endif
+#ifndef WIC_BN
+#define WIC_BN 256
+#endif
+#ifndef WIC_BK
+#define WIC_BK 64
+#endif
+#ifndef WIC_GROUP
+#define WIC_GROUP 8
+#endif
+
+int main(int argc, char** argv) {
+  if (argc != 9) return 2;
+  KcgGemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = atoi(argv[1]);
+  p.N = atoi(argv[2]);
+  p.K = atoi(argv[3]);
+  p.split_first_tile = atoi(argv[4]);
+  p.split_factor = atoi(argv[5]);
+  p.sk_per = atoi(argv[6]);
+  const int grid = atoi(argv[7]), slots = atoi(argv[8]);
+  const int tiles_m = p.M / WIC_BM, tiles_n = p.N / WIC_BN, num_kb = p.K / WIC_BK, tiles = tiles_m * tiles_n;
+  std::vector<int> cover(static_cast<size_t>(tiles) * num_kb, 0);
+  struct Piece { int split, nsplit, slot, kb0, kbn; };
+  std::map<int, std::vector<Piece>> by_tile;
+  std::map<int, int> slot_owner;
+  std::map<long long, int> origin_owner;
+  for (int c = 0; c < grid; ++c) {
+    kcg::WorkIter<WIC_BM, WIC_BN, WIC_GROUP> it(p, c, grid, tiles_m, tiles_n, num_kb);
+    kcg::WorkUnit w;
+    while (it.next(w)) {
+      if (w.tile < 0 || w.tile >= tiles || w.kb0 < 0 || w.kb0 + w.kbn > num_kb) return printf("FAIL range\n"), 1;
+      if (w.m0 % WIC_BM || w.n0 % WIC_BN || w.m0 >= p.M || w.n0 >= p.N) return printf("FAIL origin\n"), 1;
+      const long long key = static_cast<long long>(w.m0) * p.N + w.n0;
+      if (origin_owner.count(key) && origin_owner[key] != w.tile) return printf("FAIL two tiles share an origin\n"), 1;
+      origin_owner[key] = w.tile;
+      for (int kb = w.kb0; kb < w.kb0 + w.kbn; ++kb) cover[static_cast<size_t>(w.tile) * num_kb + kb]++;
+      by_tile[w.tile].push_back({w.split, w.nsplit, w.slot, w.kb0, w.kbn});
+    }
+  }
+  for (size_t i = 0; i < cover.size(); ++i)
+    if (cover[i] != 1) return printf("FAIL tile %zu block %zu covered %d times\n", i / num_kb, i % num_kb, cover[i]), 1;
+  if (static_cast<int>(origin_owner.size()) != tiles) return printf("FAIL raster misses tiles\n"), 1;
+  for (auto& kv : by_tile) {
+    auto& v = kv.second;
+    const int n = v[0].nsplit;
+    if (static_cast<int>(v.size()) != n) return printf("FAIL tile %d: %zu pieces, nsplit %d\n", kv.first, v.size(), n), 1;
+    std::vector<int> seen(n, 0);
+    int slot0 = v[0].slot - v[0].split;
+    for (auto& pc : v) {
+      if (pc.nsplit != n || pc.split < 0 || pc.split >= n || seen[pc.split]++) return printf("FAIL tile %d numbering\n", kv.first), 1;
+      if (pc.slot - pc.split != slot0) return printf("FAIL tile %d slot0\n", kv.first), 1;
+      if (n > 1) {
+        if (pc.slot < 0 || pc.slot >= slots) return printf("FAIL slot %d outside %d\n", pc.slot, slots), 1;
+        if (slot_owner.count(pc.slot)) return printf("FAIL slot %d reused\n", pc.slot), 1;
+        slot_owner[pc.slot] = kv.first;
+      }
+    }
+    // K order: split s ends where split s + 1 begins
+    std::vector<Piece> ord(n);
+    for (auto& pc : v) ord[pc.split] = pc;
+    int at = 0;
+    for (int s = 0; s < n; ++s) {
+      if (ord[s].kbn > 0 && ord[s].kb0 != at) return printf("FAIL tile %d K order\n", kv.first), 1;
+      at += ord[s].kbn;
+    }
+    if (at != num_kb) return printf("FAIL tile %d K total\n", kv.first), 1;
+  }
+  printf("OK tiles %d split_tiles %zu\n", tiles, slot_owner.empty() ? size_t(0) : by_tile.size());
+  return 0;
+}
