@@ -394,15 +394,19 @@ struct TcGemmF32x3 {
           for (int c = 0; c < PIECES; ++c) {
             const int col = w.n0 + col_half0 + c * 32;
             if (row < p.M && col < p.N) {
-              float* dst = via_ws ? p.splitk_ws +
-                                        (static_cast<size_t>(w.slot) * kBM + row_base + t * 128 + row_in_acc) * kBN +
-                                        col_half0 + c * 32
-                                  : Cout + static_cast<size_t>(row) * p.ldc + col;
-              float4* d4 = reinterpret_cast<float4*>(dst);
+              // A partial is private to this kernel, so it is not stored as a matrix: the CTA's
+              // R x kBN floats are laid out [16-byte piece of a thread][thread], which makes every
+              // warp store (and the reducer's loads) 512 contiguous bytes. Row-major partials, 16
+              // bytes per lane at a 1 KB stride, made L2 merge every sector.
+              float4* d4 = via_ws ? reinterpret_cast<float4*>(p.splitk_ws +
+                                                             (static_cast<size_t>(w.slot) * kBM + row_base) * kBN) +
+                                        (t * PIECES + c) * 8 * NUM_EPI_THREADS + epi_tid
+                                  : reinterpret_cast<float4*>(Cout + static_cast<size_t>(row) * p.ldc + col);
+              const int step = via_ws ? NUM_EPI_THREADS : 1;
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const int b = (t * PIECES + c) * 32 + 4 * i;
-                d4[i] = make_float4(acc[b], acc[b + 1], acc[b + 2], acc[b + 3]);
+                d4[i * step] = make_float4(acc[b], acc[b + 1], acc[b + 2], acc[b + 3]);
               }
             }
           }
@@ -438,15 +442,13 @@ struct TcGemmF32x3 {
                 for (int i = 0; i < 32; ++i) v[i] = 0.f;
 #pragma unroll 1
                 for (int s = 0; s < w.nsplit; ++s) {
-                  const float4* src = reinterpret_cast<const float4*>(
-                      p.splitk_ws +
-                      ((static_cast<size_t>(w.slot - w.split) + s) * kBM + row_base + t * 128 +
-                       row_in_acc) *
-                          kBN +
-                      col_half0 + c * 32);
+                  const float4* src =
+                      reinterpret_cast<const float4*>(
+                          p.splitk_ws + ((static_cast<size_t>(w.slot - w.split) + s) * kBM + row_base) * kBN) +
+                      (t * PIECES + c) * 8 * NUM_EPI_THREADS + epi_tid;
 #pragma unroll
                   for (int i = 0; i < 8; ++i) {
-                    const float4 x = __ldcg(src + i);
+                    const float4 x = __ldcg(src + i * NUM_EPI_THREADS);
                     v[4 * i] += x.x;
                     v[4 * i + 1] += x.y;
                     v[4 * i + 2] += x.z;
