@@ -21,7 +21,7 @@ E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_L
 EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
-    "kcg_launch_gemm_ex", "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
+    "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
     "kcg_peer_free", "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
     "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
 )
@@ -127,6 +127,9 @@ def get_lib() -> ctypes.CDLL:
                                        ctypes.POINTER(Epilogue)]
     lib.kcg_launch_gemm_allgather.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64,
                                               ctypes.POINTER(Epilogue), ctypes.POINTER(u64), ctypes.c_int]
+    lib.kcg_launch_gemm_batched.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64,
+                                            ctypes.c_int, ctypes.POINTER(Epilogue)]
+    lib.kcg_launch_gemm_batched.restype = ctypes.c_int
     lib.kcg_peer_alloc.argtypes = [ctypes.c_int, u64, ctypes.POINTER(u64), ctypes.c_char_p]
     lib.kcg_peer_open.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(u64)]
     lib.kcg_peer_close.argtypes = [ctypes.c_int, u64]

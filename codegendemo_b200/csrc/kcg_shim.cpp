@@ -590,8 +590,8 @@ struct SplitPlan {
   int tiles, first, factor, sk_per, sk_ranges, units_at_once;
 };
 
-SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue) {
-  const int M = info->m, N = info->n, K = info->k;
+SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch = 1) {
+  const int M = info->m * batch, N = info->n, K = info->k;  // a batched product is one tall problem
   const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
   const bool x3 = info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1;
   // K splitting. LOCAL_SPLIT_U > 1 splits every tile evenly. Otherwise the tail of the persistent
@@ -681,9 +681,9 @@ int kcg_internal_fail(int code, const char* msg) { return fail(code, "%s", msg);
 void kcg_internal_count_launch(void) { g_launches.fetch_add(1); }
 // Internal (tests): the work decomposition a launch of `info` would use:
 // {tiles, split_first_tile, split_factor, sk_per, stream-K ranges, units that run at once}.
-int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int out[6]) {
-  if (!info || !out) return fail(KCG_E_BAD_ARG, "null argument");
-  const SplitPlan pl = plan_split(info, fused_epilogue != 0);
+int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int batch, int out[6]) {
+  if (!info || !out || batch < 1) return fail(KCG_E_BAD_ARG, "null argument");
+  const SplitPlan pl = plan_split(info, fused_epilogue != 0, batch);
   out[0] = pl.tiles;
   out[1] = pl.first;
   out[2] = pl.factor;
@@ -867,9 +867,30 @@ int kcg_peer_free(int device, uint64_t dptr) {
   return 0;
 }
 
+static int launch_impl(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch);
+
 int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
                               uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers) {
+  return launch_impl(function, info, device, stream, A, B, C, epi, peer_c, n_peers, 1);
+}
+
+int kcg_launch_gemm_batched(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                            uint64_t B, uint64_t C, int batch, const kcg_epilogue* epi) {
+  if (batch < 1) return fail(KCG_E_BAD_ARG, "batch must be at least 1");
+  return launch_impl(function, info, device, stream, A, B, C, epi, nullptr, 0, batch);
+}
+
+static int launch_impl(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch) {
   if (!function || !info || !A || !B || !C) return fail(KCG_E_BAD_ARG, "null argument");
+  if (batch > 1) {
+    const bool tc = info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TCGEN05_PAIR ||
+                    info->kernel == KCG_KERNEL_TF32X1;
+    if (!tc) return fail(KCG_E_BAD_CONFIG, "batched launches need a tcgen05 kernel (KERNEL_VARIANT 2, 3 or 4)");
+    if (static_cast<int64_t>(info->m) * batch > 0x7fffffff || static_cast<int64_t>(info->k) * batch > 0x7fffffff)
+      return fail(KCG_E_TOO_LARGE, "batch * M and batch * K must fit 31 bits");
+  }
   if (n_peers < 0 || n_peers > KCG_MAX_PEERS || (n_peers > 0 && !peer_c))
     return fail(KCG_E_BAD_ARG, "n_peers must be 0..%d with their addresses", KCG_MAX_PEERS);
   if (n_peers > 0) {
@@ -887,7 +908,8 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
   if (int e = ensure_device(device, &s)) return e;
   KcgGemmParams p;
   memset(&p, 0, sizeof(p));
-  const int M = info->m, N = info->n, K = info->k;
+  // A batched product runs as one tall problem: M counts the rows of all batches
+  const int Mb = info->m, M = info->m * batch, N = info->n, K = info->k;
   const int eb = (info->dtype == KCG_DTYPE_FLOAT32) ? 4 : 2;
   p.A = reinterpret_cast<const void*>(A);
   p.B = reinterpret_cast<const void*>(B);
@@ -895,7 +917,8 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
   p.M = M;
   p.N = N;
   p.K = K;
-  p.lda = info->atrans ? M : K;
+  p.batch_rows = batch > 1 ? Mb : 0;
+  p.lda = info->atrans ? Mb : K;
   p.ldb = N;
   p.ldc = N;
   p.status = reinterpret_cast<unsigned int*>(s->status);
@@ -918,16 +941,17 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
     const kcg::TcLayout L = pair ? kcg::make_tc_layout(info->dtype, info->bm / 2, info->bn / 2, info->bk, info->atrans)
                                  : kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
     if (info->atrans) {
-      if (int e = encode_map(s, &p.tmA, info->dtype, A, M, K, static_cast<uint64_t>(M) * eb, L.a_box_inner,
-                             L.a_box_outer, L.a_tma_swizzle))
+      // K x M storage: the batches' matrices lie one under the other, K rows each
+      if (int e = encode_map(s, &p.tmA, info->dtype, A, Mb, static_cast<uint64_t>(K) * batch,
+                             static_cast<uint64_t>(Mb) * eb, L.a_box_inner, L.a_box_outer, L.a_tma_swizzle))
         return e;
     } else {
       if (int e = encode_map(s, &p.tmA, info->dtype, A, K, M, static_cast<uint64_t>(K) * eb, L.a_box_inner,
                              L.a_box_outer, L.a_tma_swizzle))
         return e;
     }
-    if (int e = encode_map(s, &p.tmB, info->dtype, B, N, K, static_cast<uint64_t>(N) * eb, L.b_box_inner,
-                           L.b_box_outer, L.b_tma_swizzle))
+    if (int e = encode_map(s, &p.tmB, info->dtype, B, N, static_cast<uint64_t>(K) * batch,
+                           static_cast<uint64_t>(N) * eb, L.b_box_inner, L.b_box_outer, L.b_tma_swizzle))
       return e;
     // The single-pass kernel writes C with TMA stores of 32-row x 128-byte boxes taken from
     // 128B-swizzled staging buffers; the 3xTF32 kernel stores from registers.
@@ -941,7 +965,7 @@ int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, in
                                128 / eb, 32, 3))
           return e;
     }
-    const SplitPlan plan = plan_split(info, p.epi_flags != 0u);
+    const SplitPlan plan = plan_split(info, p.epi_flags != 0u, batch);
     const int T = plan.tiles, first = plan.first, factor = plan.factor, sk_per = plan.sk_per,
               sk_ranges = plan.sk_ranges, G = plan.units_at_once;
     const bool ws_epilogue = x3 && p.epi_flags != 0u;

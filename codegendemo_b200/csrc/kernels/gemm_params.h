@@ -61,6 +61,10 @@ struct alignas(64) KcgGemmParams {
   // K blocks, laid end to end, are cut into one contiguous range of sk_per blocks per CTA (pair);
   // the grid then has exactly as many CTAs (pairs) as there are ranges (work_iter.cuh).
   int sk_per;
+  // Batched product when > 0: M counts the rows of all batches (A and C stacked by rows), K is one
+  // batch's, B holds the batches' K x N matrices one under the other (an A stored K x M likewise),
+  // and batch_rows is the M of one batch, a multiple of the tile height.
+  int batch_rows;
   // Fused epilogue, in force when epi_flags != 0: D = act(alpha * (A.B) + beta * C + bias[col]),
   // computed in fp32 before the rounding to C's type. beta * C reads C in place (skipped when
   // beta == 0, so C may then hold anything); bias has N values of C's type.

@@ -174,7 +174,9 @@ struct TcGemm {
             uint8_t* sa = smem + s * STAGE_BYTES;
             uint8_t* sb = sa + L.a_bytes;
             const int k0 = (w.kb0 + kb) * kBK;
-            const int am0 = w.m0 + row_base, bn0 = w.n0 + bcol_base;
+            // K x M storage: the batch selects K rows and M is counted inside the batch
+            const int am0 = (kATrans ? w.mcol : w.m0) + row_base, bn0 = w.n0 + bcol_base;
+            const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
             if constexpr (kPair) {
               // completion bytes of both CTAs land on the leader's barrier
               const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[s]), 0u);
@@ -182,27 +184,27 @@ struct TcGemm {
 #pragma unroll
               for (int j = 0; j < L.a_boxes; ++j) {
                 if constexpr (kATrans) {
-                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, am0 + j * L.atom, k0);
+                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, am0 + j * L.atom, ka);
                 } else {
-                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, k0 + j * L.a_box_inner, am0);
+                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, ka + j * L.a_box_inner, am0);
                 }
               }
 #pragma unroll
               for (int j = 0; j < L.b_boxes; ++j)
-                tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, k0);
+                tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, kb_row);
             } else {
               mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
 #pragma unroll
               for (int j = 0; j < L.a_boxes; ++j) {
                 if constexpr (kATrans) {
-                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, k0);
+                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
                 } else {
-                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], k0 + j * L.a_box_inner, am0);
+                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
                 }
               }
 #pragma unroll
               for (int j = 0; j < L.b_boxes; ++j)
-                tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, k0);
+                tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, kb_row);
             }
           }
         }

@@ -178,8 +178,9 @@ struct TcGemmF32x3 {
             const int k0 = (w.kb0 + kb) * kBK;
 #pragma unroll
             for (int j = 0; j < L.a_boxes; ++j) {
-              if constexpr (kATrans) {
-                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.m0 + row_base + j * L.atom, k0);
+              if constexpr (kATrans) {  // K x M storage: the batch selects K rows, M counts inside it
+                tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], w.mcol + row_base + j * L.atom,
+                            k0 + w.kofs);
               } else {
                 tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s],
                             k0 + j * L.a_box_inner, w.m0 + row_base);
@@ -187,7 +188,8 @@ struct TcGemmF32x3 {
             }
 #pragma unroll
             for (int j = 0; j < L.b_boxes; ++j) {
-              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + bcol_base + j * L.atom, k0);
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + bcol_base + j * L.atom,
+                          k0 + w.kofs);
             }
           }
         }

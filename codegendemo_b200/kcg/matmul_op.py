@@ -100,3 +100,28 @@ def matmul(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
         _KERNELS[key] = kern
     kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu)
     return c
+
+
+def bmm(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
+    """``c[i] = a[i] @ b[i]`` (``torch.bmm`` layout: a is batch x M x K, b is batch x K x N, both
+    contiguous) as ONE launch of the kernel compiled for a single batch's M, N, K: the persistent grid
+    walks the tiles of all batches, so that small per-batch problems fill the GPU together. The
+    epilogue keywords are those of ``matmul`` (a bias is shared by the batches)."""
+    import torch
+    batch, M, K = a.shape
+    batch2, K2, N = b.shape
+    assert batch == batch2 and K == K2 and a.is_contiguous() and b.is_contiguous()
+    if c is None:
+        if beta != 0.0:
+            raise ValueError("beta != 0 needs the c to scale")
+        c = torch.empty((batch, M, N), dtype=a.dtype, device=a.device)
+    dt = FromTorchType(a.dtype)
+    dev = a.device.index or 0
+    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())))
+    kern = _KERNELS.get(key)
+    if kern is None:
+        kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
+        _, kern = build_kernel(kpm, dev)
+        _KERNELS[key] = kern
+    kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu, batch=batch)
+    return c

@@ -148,6 +148,17 @@ typedef struct kcg_epilogue {
 } kcg_epilogue;
 int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
                        uint64_t A, uint64_t B, uint64_t C, const kcg_epilogue* epi);
+/* ---- batched product ---------------------------------------------------------------
+ * C[b] = A[b] * B[b] for b in [0, batch), every operand contiguous over the batches (torch.bmm
+ * layout: A is batch x M x K - or batch x K x M with IS_ATRANS - B is batch x K x N, C is batch x M
+ * x N), with the cubin compiled for ONE batch's M, N, K. No counterpart in the reference (batched
+ * GEMM is on its list of next operators, doc/结果汇总.md). One launch: the persistent kernel
+ * walks the tiles of all batches as one tall problem, so small per-batch problems fill the
+ * GPU together; tcgen05 kernels only (KERNEL_VARIANT 2, 3, 4). `epi` may be null; a bias is
+ * shared by all batches. */
+int kcg_launch_gemm_batched(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                            uint64_t A, uint64_t B, uint64_t C, int batch, const kcg_epilogue* epi);
+
 /* ---- M-sharded product with the all-gather of C fused into the kernel ---------------
  * No counterpart in the reference (it has no multi-GPU code). Rank r of G computes rows
  * [r*M/G, (r+1)*M/G) of C with the same cubin as kcg_launch_gemm; `C` is the address of that slab

@@ -111,11 +111,27 @@ FUSED = [
 ]
 
 
+# batched products: (id, batch, M, N, K of one batch, dtype, distribution, keys)
+BATCHED = [
+    ("bf16_batch6", 6, 256, 512, 512, E.bfloat16, "normal", dict()),
+    ("bf16_batch3_pair", 3, 512, 512, 1024, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4)),
+    ("bf16_batch5_atrans", 5, 128, 256, 384, E.bfloat16, "normal", dict(isATranspose=1)),
+    ("bf16_batch4_splitk", 4, 128, 256, 2048, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=2)),
+    ("fp16_batch2", 2, 256, 256, 256, E.float16, "normal", dict(BLOCK_SIZE_N=128)),
+    ("fp32_batch4_3xtf32", 4, 256, 256, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=128)),
+    ("fp32_batch3_3xtf32_atrans_pair", 3, 256, 512, 256, E.float32, "uniform",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=3, isATranspose=1)),
+]
+
+
 def all_configs():
     out = [default_config(4096, 4096, 4096, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3),
            default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64),
            default_config(256, 256, 256, E.bfloat16)]
     for (_, m, n, k, dt, _, keys) in SEEDED + FUSED:
+        out.append(default_config(m, n, k, dt, **keys))
+    for (_, _, m, n, k, dt, _, keys) in BATCHED:
         out.append(default_config(m, n, k, dt, **keys))
     for (name, dt, keys) in GOLDEN:
         m, n, k = GOLDEN_SHAPES[name]

@@ -119,6 +119,49 @@ def test_fused_epilogue_matches_oracle(case):
     assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.tolerance_for(tdt)
 
 
+@pytest.mark.parametrize("case", gpu_cases.BATCHED, ids=[c[0] for c in gpu_cases.BATCHED])
+def test_batched_product_matches_oracle_per_batch(case):
+    """kcg_launch_gemm_batched: one launch over all batches (torch.bmm layout), checked batch by batch
+    against the host oracle; then once more with a fused bias + ReLU."""
+    _, batch, M, N, K, dt, dist, keys = case
+    tdt = ToTorchType(dt)
+    pairs = [oracle.make_inputs(M, N, K, tdt, dist, seed=20 + i) for i in range(batch)]
+    A = torch.stack([p[0] for p in pairs])
+    B = torch.stack([p[1] for p in pairs])
+    kpm = default_config(M, N, K, dt, **keys)
+    _, kern = build_kernel(kpm, 0)
+    a = (A.transpose(1, 2).contiguous() if kpm.isATranspose else A).cuda()
+    b = B.cuda()
+    c = torch.full((batch, M, N), float("nan"), dtype=tdt, device="cuda:0")
+    kern.run(a, b, c, batch=batch)
+    kern.checkStatus()
+    for i in range(batch):
+        err = oracle.rel_errors(c[i], oracle.host_matmul(A[i], B[i]))
+        assert not err["nan"] and err["max_rel"] <= oracle.tolerance_for(tdt), (i, err)
+    bias = torch.linspace(-0.5, 0.5, N).to(tdt)
+    c.fill_(float("nan"))
+    kern.run(a, b, c, batch=batch, bias=bias.cuda(), relu=True)
+    kern.checkStatus()
+    for i in (0, batch - 1):
+        ref = oracle.host_matmul_fused(A[i], B[i], bias=bias, relu=True)
+        assert oracle.rel_errors(c[i], ref)["max_rel"] <= oracle.tolerance_for(tdt), i
+
+
+def test_bmm_op_and_batched_launch_rejects_simt():
+    from codegendemo_b200.kcg.matmul_op import bmm
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(8, 128, 256, generator=g) / 16).bfloat16()
+    y = (torch.randn(8, 256, 256, generator=g) / 16).bfloat16()
+    z = bmm(x.cuda(), y.cuda())
+    torch.cuda.synchronize()
+    assert oracle.rel_errors(z.reshape(-1, 256), torch.bmm(x.float(), y.float()).reshape(-1, 256))["max_rel"] <= 2e-2
+    _, simt = build_kernel(default_config(256, 256, 256, E.float32, **gpu_cases.SIMT_128), 0)
+    t = torch.zeros(2, 256, 256, device="cuda:0")
+    with pytest.raises(_lib.KCGError) as ei:
+        simt.run(t, t, t.clone(), batch=2)
+    assert ei.value.code == _lib.E_BAD_CONFIG
+
+
 def test_matmul_op_fuses_bias_relu_chain():
     """matmul -> bias + ReLU -> matmul, the chain the reference sketches, as two fused launches."""
     from codegendemo_b200.kcg.matmul_op import matmul

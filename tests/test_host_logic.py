@@ -226,10 +226,13 @@ WORK_PLANS = [
     # 3xTF32 kernel: even split of the last wave's 68 tiles by two, not stream-K
     (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4), "even"),
     (256, 512, 1280, E.bfloat16, dict(LOCAL_SPLIT_U=3), "even"),
+    # batched: 40 products of 256x512x16384 walked as one tall problem (320 tiles: the tail goes to stream-K)
+    (256, 512, 16384, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk", 40),
+    (128, 256, 2048, E.bfloat16, dict(LOCAL_SPLIT_U=2), "even", 4),
 ]
 
 
-@pytest.mark.parametrize("case", WORK_PLANS, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-{c[5]}")
+@pytest.mark.parametrize("case", WORK_PLANS, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-{c[5]}" + (f"-b{c[6]}" if len(c) > 6 else ""))
 def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     """The launcher's plan (whole tiles / even K split / stream-K over the tail) fed to the kernels' own
     iterator, compiled for the host: every CTA's unit sequence is walked and coverage, contributor numbering
@@ -237,13 +240,15 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     import ctypes
     from codegendemo_b200 import _lib
     from codegendemo_b200.kcg.KCGCompiler import compile_info
-    M, N, K, dt, keys, layer = case
+    M, N, K, dt, keys, layer = case[:6]
+    batch = case[6] if len(case) > 6 else 1
     kpm = default_config(M, N, K, dt, **keys)
     info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT)
     out = (ctypes.c_int * 6)()
     lib = _lib.get_lib()
-    lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
-    assert lib.kcg_internal_plan_split(ctypes.byref(info), 0, out) == 0
+    lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_int)]
+    assert lib.kcg_internal_plan_split(ctypes.byref(info), 0, batch, out) == 0
     tiles, first, factor, sk_per, ranges, at_once = list(out)
     got = "streamk" if sk_per > 0 else "even" if factor > 1 else "whole"
     assert got == layer, (got, list(out))
@@ -257,8 +262,10 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     subprocess.run(["g++", "-O1", "-std=c++17", "-I/usr/local/cuda/include", "-I" + kdir, f"-DWIC_BM={info.bm}",
                     f"-DWIC_BN={info.bn}", f"-DWIC_BK={info.bk}", f"-DWIC_GROUP={info.group}", "-o", str(exe),
                     os.path.join(ROOT, "tests", "work_iter_check.cpp")], check=True)
-    r = subprocess.run([str(exe), str(M), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots)],
-                       capture_output=True, text=True)
+    args = [str(exe), str(M * batch), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots)]
+    if batch > 1:
+        args.append(str(M))  # rows of one batch: the iterator's batch offsets are checked too
+    r = subprocess.run(args, capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.startswith("OK"), r.stdout + r.stderr
 
 

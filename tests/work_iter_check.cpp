@@ -26,7 +26,7 @@
 #endif
 
 int main(int argc, char** argv) {
-  if (argc != 9) return 2;
+  if (argc != 9 && argc != 10) return 2;  // optional 10th argument: rows of one batch (M is then all batches' rows)
   KcgGemmParams p;
   memset(&p, 0, sizeof(p));
   p.M = atoi(argv[1]);
@@ -36,6 +36,7 @@ int main(int argc, char** argv) {
   p.split_factor = atoi(argv[5]);
   p.sk_per = atoi(argv[6]);
   const int grid = atoi(argv[7]), slots = atoi(argv[8]);
+  p.batch_rows = argc == 10 ? atoi(argv[9]) : 0;
   const int tiles_m = p.M / WIC_BM, tiles_n = p.N / WIC_BN, num_kb = p.K / WIC_BK, tiles = tiles_m * tiles_n;
   std::vector<int> cover(static_cast<size_t>(tiles) * num_kb, 0);
   struct Piece { int split, nsplit, slot, kb0, kbn; };
@@ -48,6 +49,9 @@ int main(int argc, char** argv) {
     while (it.next(w)) {
       if (w.tile < 0 || w.tile >= tiles || w.kb0 < 0 || w.kb0 + w.kbn > num_kb) return printf("FAIL range\n"), 1;
       if (w.m0 % WIC_BM || w.n0 % WIC_BN || w.m0 >= p.M || w.n0 >= p.N) return printf("FAIL origin\n"), 1;
+      const int b = p.batch_rows > 0 ? w.m0 / p.batch_rows : 0;
+      if (w.kofs != b * p.K || w.mcol != w.m0 - b * p.batch_rows || (p.batch_rows > 0 && w.mcol + WIC_BM > p.batch_rows))
+        return printf("FAIL batch offsets of tile %d\n", w.tile), 1;
       const long long key = static_cast<long long>(w.m0) * p.N + w.n0;
       if (origin_owner.count(key) && origin_owner[key] != w.tile) return printf("FAIL two tiles share an origin\n"), 1;
       origin_owner[key] = w.tile;
