@@ -56,9 +56,18 @@ def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: i
     if M % 512 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 512) * (N // 256) >= 6 * pairs:
         return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
                               NUM_STAGES=4, isATranspose=isATranspose)
-    if M % 256 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 256) * (N // 256) >= 148:
+    tiles256 = (M // 256) * (N // 256) if M % 256 == 0 and N % 256 == 0 else 0
+    if K % 64 == 0 and pairs <= tiles256 < 6 * pairs:
+        # one to six waves of 256x256 pair tiles: the pair kernel with a stream-K tail measured best on the
+        # rectangular shapes (512 and 2048 rows x 11008^2), with 128-wide K blocks once K is long
+        return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
+                              BLOCK_SIZE_K=128 if (K % 128 == 0 and K >= 8192) else 64, isATranspose=isATranspose)
+    if K % 64 == 0 and tiles256 >= 148:
         return default_config(M, N, K, dtype, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3,
                               isATranspose=isATranspose)
+    if N % 128 == 0 and K % 128 == 0 and K >= 1024:
+        # few tiles: small tiles with long K blocks (best on the 128- and 512-row shapes)
+        return default_config(M, N, K, dtype, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, isATranspose=isATranspose)
     return default_config(M, N, K, dtype, isATranspose=isATranspose)
 
 
