@@ -126,10 +126,18 @@ def bmm(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
         c = torch.empty((batch, M, N), dtype=a.dtype, device=a.device)
     dt = FromTorchType(a.dtype)
     dev = a.device.index or 0
-    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())))
+    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())), 0 if keys else batch)
     kern = _KERNELS.get(key)
     if kern is None:
-        kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
+        if keys:
+            kpm = default_config(M, N, K, dt, **keys)
+        else:
+            # the launch walks all batches' tiles as one tall problem: pick the tile for that much work,
+            # as long as a batch holds a whole number of tile rows
+            kpm = tuned_config(batch * M, N, K, dt)
+            if M % kpm.BLOCK_SIZE_M:
+                kpm = tuned_config(M, N, K, dt)
+            kpm.M = M
         _, kern = build_kernel(kpm, dev)
         _KERNELS[key] = kern
     kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu, batch=batch)
