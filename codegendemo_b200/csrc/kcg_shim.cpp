@@ -1068,8 +1068,14 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
   const bool tensor_core = info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 ||
                            info->kernel == KCG_KERNEL_TCGEN05_PAIR;
   int nslabs = 1;
-  if (tensor_core && !info->atrans && bytes[0] + bytes[2] >= (64u << 20) && tiles_m >= 4)
-    nslabs = tiles_m < 8 ? tiles_m : 8;
+  if (tensor_core && !info->atrans && bytes[0] + bytes[2] >= (64u << 20) && tiles_m >= 4) {
+    // up to 16 slabs, none smaller than ~16 MiB of A + C: what is not overlapped is the first
+    // slab's copy-in and the last slab's kernel and copy-out, so more slabs shorten both ends
+    size_t want = (bytes[0] + bytes[2]) / (16u << 20);
+    if (want < 4) want = 4;
+    if (want > 16) want = 16;
+    nslabs = tiles_m < static_cast<int>(want) ? tiles_m : static_cast<int>(want);
+  }
   if (nslabs == 1) {
     DRV(cuMemcpyHtoDAsync(s->hbuf[0], hostA, bytes[0], st));
     DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], st));

@@ -187,7 +187,7 @@ int kcg_check_status(int device, uint64_t stream);
 /* Whole-operator call on HOST buffers: copies A and B to the device (async from the
  * caller's memory, pinned for full speed), runs the kernel and copies C back, ordered
  * after the work already queued on `stream`, then synchronises. Large problems move as
- * up to eight row slabs through three internal streams (copy-in, compute, copy-out) so
+ * up to sixteen row slabs through three internal streams (copy-in, compute, copy-out) so
  * that both transfer directions and the kernels overlap. Device buffers are owned and
  * reused by the library. */
 int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
