@@ -509,7 +509,8 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
     const int x3 = (r.kernel == KCG_KERNEL_TCGEN05) ? 1 : 0;
     const int units = tiles * lsu;
     out->grid[0] = units < r.num_sms ? units : r.num_sms;  // persistent CTAs
-    out->block[0] = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 512 : 192;
+    // single-pass kernel: producer, MMA, four epilogue warps, two push warps (fused all-gather)
+    out->block[0] = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32 && x3) ? 512 : 256;
     out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm, bn, bk, r.stages, x3);
   } else if (r.kernel == KCG_KERNEL_TCGEN05_PAIR) {
     const int f32 = (c[KCG_CFG_DATATYPE_A] == KCG_DTYPE_FLOAT32) ? 1 : 0;
@@ -517,7 +518,7 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
     const int pairs = units < r.num_sms / 2 ? units : r.num_sms / 2;
     out->grid[0] = 2 * pairs;  // persistent clusters of two CTAs
     out->cluster[0] = 2;
-    out->block[0] = f32 ? 512 : 192;
+    out->block[0] = f32 ? 512 : 256;
     out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm / 2, bn / 2, bk, r.stages, f32);
   } else if (r.kernel == KCG_KERNEL_SIMT) {
     // grid/block as the reference derives them (Optimizer.cc:20,336; Rewriter.cc:726-761)
@@ -962,10 +963,6 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
       if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(N) * eb, 128 / eb, 32,
                              3 /*CU_TENSOR_MAP_SWIZZLE_128B*/))
         return e;
-      for (int i = 0; i < n_peers; ++i)  // the same boxes over every peer's copy of this slab
-        if (int e = encode_map(s, &p.tmPeer[i], info->dtype, peer_c[i], N, M, static_cast<uint64_t>(N) * eb,
-                               128 / eb, 32, 3))
-          return e;
     }
     const SplitPlan plan = plan_split(info, p.epi_flags != 0u, batch);
     const int T = plan.tiles, first = plan.first, factor = plan.factor, sk_per = plan.sk_per,
@@ -1039,9 +1036,9 @@ int kcg_check_status(int device, uint64_t stream) {
     DRV(cuMemsetD32(s->status, 0, 4));
     // a timed-out split-K launch may leave counters mid-count
     if (s->counters) DRV(cuMemsetD32(s->counters, 0, s->counters_n));
-    static const char* role[] = {"", "TMA producer", "MMA issuer", "epilogue", "splitter", "shape"};
+    static const char* role[] = {"", "TMA producer", "MMA issuer", "epilogue", "splitter", "shape", "push warp"};
     return fail(KCG_E_DEVICE_TIMEOUT, "kernel gave up in a bounded wait: role %s (code %u), block %u, detail %u/%u",
-                st[0] < 6 ? role[st[0]] : "?", st[0], st[1], st[2], st[3]);
+                st[0] < 7 ? role[st[0]] : "?", st[0], st[1], st[2], st[3]);
   }
   return 0;
 }

@@ -37,12 +37,12 @@
 #define KCG_ST_TIMEOUT_EPILOGUE 3u
 #define KCG_ST_TIMEOUT_SPLITTER 4u
 #define KCG_ST_BAD_SHAPE 5u
+#define KCG_ST_TIMEOUT_PUSHER 6u
 
 struct alignas(64) KcgGemmParams {
   CUtensorMap tmA;  // tcgen05 variants: tiled map of A (or of A^T when IS_ATRANS=1)
   CUtensorMap tmB;  // tiled map of B (K x N row-major)
   CUtensorMap tmC;  // C as 32-row x 128-byte boxes (128B swizzle): the TMA-store epilogue
-  CUtensorMap tmPeer[KCG_MAX_PEERS];  // the same boxes over peerC[i] (fused all-gather)
   CUtensorMap tmWs;  // K-split workspace as one tall fp32 matrix of BN columns, 32 x 32 boxes
   const void* A;
   const void* B;
@@ -73,9 +73,9 @@ struct alignas(64) KcgGemmParams {
   unsigned int epi_flags;  // KCG_EPI_*
   // Fused all-gather of an M-sharded product: besides C, every finished tile is also written
   // to the same rows / columns of n_peers more matrices with C's pitch — this rank's slab inside
-  // the full C of every other GPU, mapped into this process (bulk tensor stores through tmPeer,
-  // 16-byte stores from the K-split reduction, over NVLink; no remote loads, no multicast, no
-  // flags: the data is in place when every rank's kernel has completed).
+  // the full C of every other GPU, mapped into this process (coalesced 16-byte stores over NVLink
+  // by the kernel's push warps, or by the reducer of a K-split tile; no remote loads, no multicast,
+  // no flags between GPUs: the data is in place when every rank's kernel has completed).
   int n_peers;
   void* peerC[KCG_MAX_PEERS];
 };

@@ -68,7 +68,8 @@ struct TcGemm {
   static constexpr int STAGE_BYTES = STAGE_HI;
   static constexpr int KSTEPS = kBK / UMMA_K;
   static constexpr int NUM_EPI_THREADS = 128;
-  static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
+  static constexpr int NUM_PUSH_WARPS = 2;  // fused all-gather: copy finished tiles to the peers' C
+  static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS + 32 * NUM_PUSH_WARPS;
   static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, R, BNL, kBK, kStages, 0);
   static constexpr int STG_BYTES = 32 * 128;       // one staging buffer: 32 rows x 128 bytes
   static constexpr int SCOLS = 128 / (kDType == KCG_DT_F32 ? 4 : 2);  // C columns per staging buffer
@@ -87,6 +88,7 @@ struct TcGemm {
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
     uint32_t last_flag;
+    uint32_t push_count;  // epilogue warps that have finished (and completed the stores of) a whole-K tile
   };
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
@@ -130,6 +132,7 @@ struct TcGemm {
       }
       bars->abort_flag = 0u;
       bars->last_flag = 0u;
+      bars->push_count = 0u;
       fence_mbar_init();
       fence_proxy_async_smem();
     }
@@ -283,6 +286,63 @@ struct TcGemm {
           }
         }
       }
+    } else if (warp >= 6) {
+      // ------------------------------------- push warps (fused all-gather only)
+      // They walk the same unit sequence; for every whole-K tile they wait until the four epilogue
+      // warps have completed its stores, then copy this CTA's rows of the tile from this GPU's C
+      // (still in L2) to the same place in every peer's C with coalesced 16-byte loads and
+      // stores. They lag behind the epilogue as far as NVLink makes them; nothing waits for them
+      // before the end of the kernel. K-split tiles are written to the peers by their reducer.
+      if (p.n_peers > 0) {
+        const int pw = warp - 6;
+        constexpr int ROW_U4 = kBN * static_cast<int>(sizeof(OutT)) / 16;  // 16-byte pieces per tile row
+        constexpr int TOTAL = R * ROW_U4;
+        constexpr int UNR = 8;
+        uint32_t whole = 0;  // whole-K tiles seen so far
+        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+        Unit w;
+        bool ok = true;
+        while (ok && units.next(w)) {
+          if (w.nsplit != 1) continue;
+          ++whole;
+          const uint32_t want = 4u * whole;
+          const uint64_t t0 = global_timer_ns();
+          uint32_t spins = 0;
+          while (*reinterpret_cast<volatile uint32_t*>(&bars->push_count) < want) {
+            if ((++spins & 63u) == 0u) {
+              if (bars->abort_flag != 0u || global_timer_ns() - t0 > KCG_WAIT_LIMIT_NS) {
+                if (lane == 0 && bars->abort_flag == 0u) report(p, bars, KCG_ST_TIMEOUT_PUSHER, whole, want);
+                ok = false;
+                break;
+              }
+              __nanosleep(200);
+            }
+          }
+          if (!ok) break;
+          __threadfence();  // acquire: the tile's rows as the epilogue warps published them
+          const OutT* src0 = reinterpret_cast<const OutT*>(p.C);
+          for (int base = pw * 32 + lane; base < TOTAL; base += 32 * NUM_PUSH_WARPS * UNR) {
+            uint4 v[UNR];
+            size_t off[UNR];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+              const int idx = base + u * 32 * NUM_PUSH_WARPS;
+              const int row = w.m0 + row_base + idx / ROW_U4;
+              const int col = w.n0 + (idx % ROW_U4) * (16 / static_cast<int>(sizeof(OutT)));
+              const bool in = idx < TOTAL && row < p.M && col < p.N;
+              off[u] = in ? static_cast<size_t>(row) * p.ldc + col : static_cast<size_t>(-1);
+              if (in) v[u] = __ldcg(reinterpret_cast<const uint4*>(src0 + off[u]));
+            }
+            for (int pe = 0; pe < p.n_peers; ++pe) {
+              OutT* dst = reinterpret_cast<OutT*>(p.peerC[pe]);
+#pragma unroll
+              for (int u = 0; u < UNR; ++u)
+                if (off[u] != static_cast<size_t>(-1)) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+            }
+          }
+        }
+        __threadfence_system();  // peer stores ordered before the kernel's completion
+      }
     } else {
       // ------------------------------------------------------------ epilogue
       const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -362,13 +422,21 @@ struct TcGemm {
               const int col0 = w.n0 + g * SCOLS;
               if (lane == 0 && row0 < p.M && col0 < p.N) {
                 tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
-                // Fused all-gather: the same staged block also goes to this rank's rows of every
-                // peer's C, one bulk store per peer (over NVLink). They read the same buffer and
-                // share the bulk group, so the buffer is reused only after all of them have read it.
-                for (int pe = 0; pe < p.n_peers; ++pe) tma_store_2d(&p.tmPeer[pe], buf, col0, row0);
                 tma_store_commit();
               }
             }
+          }
+          if (p.n_peers > 0) {
+            // Fused all-gather: once this warp's rows of the tile are in C (stores complete, and
+            // ordered before generic-proxy reads), tell the push warps, which copy the tile to
+            // every peer while the next tiles are computed.
+            if (lane == 0) {
+              tma_store_wait_all<0>();
+              fence_proxy_async_all();
+              __threadfence();
+              atomicAdd(&bars->push_count, 1u);
+            }
+            __syncwarp();
           }
         } else {
           // K-split partial: the fp32 accumulators leave through the same staging buffers, as

@@ -164,9 +164,10 @@ int kcg_launch_gemm_batched(uint64_t function, const kcg_kernel_info* info, int 
  * [r*M/G, (r+1)*M/G) of C with the same cubin as kcg_launch_gemm; `C` is the address of that slab
  * inside this GPU's full C, and peer_c[i] the address of the same slab inside the full C of
  * another GPU, mapped into this process (kcg_peer_open). Every finished tile is written to
- * all of them from the kernel's epilogue: one bulk tensor store (TMA, no multicast) per target
- * from the staged tile, over NVLink for the peers (the K-split reduction uses 16-byte stores);
- * no remote loads, no flags or waits; the full C is complete on a GPU once the kernels of all
+ * all of them inside the kernel: the epilogue stores it into this GPU's C and two push warps of
+ * the same CTA copy it from there (L2) to the peers with coalesced 16-byte stores over NVLink
+ * while later tiles multiply (the reducer of a K-split tile writes the peers itself); no remote
+ * loads, no flags or waits between GPUs; the full C is complete on a GPU once the kernels of all
  * ranks have completed (synchronise the streams, then barrier). 16-bit single-pass tcgen05
  * kernels only (KCG_KERNEL_TCGEN05 / _PAIR with fp16 / bf16 data); n_peers = 0 is
  * kcg_launch_gemm_ex. KCG_MAX_PEERS = 7. */

@@ -40,7 +40,7 @@ def test_compile_entry_returns_reference_shaped_tuple():
     path, name, gx, gy, gz, bx, by, bz = res[0]
     assert os.path.exists(path) and path.endswith(name + ".cubin")
     assert name.startswith("GEMM_MNK256x256x256_DTabcbfloat16xbfloat16xbfloat16_AT0_")
-    assert (gx, gy, gz) == (4, 1, 1) and (bx, by, bz) == (192, 1, 1)
+    assert (gx, gy, gz) == (4, 1, 1) and (bx, by, bz) == (256, 1, 1)
     # launch shared memory = what the kernel lays out: stages, barriers + slack, epilogue staging
     info = compile_info(kpm.compileArgs())
     assert info.smem_bytes == info.stages * (128 + 128) * 64 * 2 + 2048 + 32768 <= 227 * 1024
@@ -114,7 +114,7 @@ def test_no_cpu_fallback_without_a_driver():
 def test_kcgcompiler_class_mirrors_reference_usage():
     kpm = default_config(256, 512, 512, E.bfloat16)
     path, name, gx, gy, gz, bx, by, bz = KCGCompiler().compileKernel(kpm)[0]
-    assert os.path.exists(path) and gx * gy * gz >= 1 and bx == 192
+    assert os.path.exists(path) and gx * gy * gz >= 1 and bx == 256
 
 
 def test_every_gpu_test_config_cross_compiles():
@@ -133,7 +133,7 @@ def test_pair_variant_launch_geometry():
     kpm = default_config(8192, 8192, 8192, E.bfloat16, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4)
     info = compile_info(kpm.compileArgs(), num_stages=4, kernel=4)
     assert info.kernel == _lib.KERNEL_TCGEN05_PAIR and list(info.cluster) == [2, 1, 1]
-    assert info.grid[0] == 148 and info.block[0] == 192
+    assert info.grid[0] == 148 and info.block[0] == 256
     # per CTA: 256 rows of A, 128 columns of B, + 32 KiB of TMA-store staging for the epilogue
     assert info.smem_bytes == 4 * (256 + 128) * 64 * 2 + 2048 + 32768
     f32 = default_config(4096, 4096, 4096, E.float32, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
