@@ -630,10 +630,11 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
       // What a split costs a CTA: its fp32 partial goes to the workspace once, the reducing CTA
       // reads two or three of them back and writes C, and each extra unit refills the pipeline.
       // Measured on 512x11008x11008 bf16: ~28 us for a 128 KB partial (128 x 256 rows per CTA),
-      // ~51 us for 256 KB; the 3xTF32 kernel stores its partials straight from registers, about
-      // twice as slow. The saving has to beat that with a margin.
+      // ~51 us for 256 KB (the 3xTF32 kernel's thread-major partials cost about the same: 1024^3
+      // fp32 with 128 KB partials gains 21 us from a four-way split). The saving has to beat that
+      // with a margin.
       const double partial_kb = (info->bm / (pair ? 2 : 1)) * static_cast<double>(info->bn) * 4.0 / 1024.0;
-      const double overhead_us = (5.0 + 0.18 * partial_kb) * (x3 ? 2.0 : 1.0);
+      const double overhead_us = 5.0 + 0.18 * partial_kb;
       const double gate_us = 1.25 * overhead_us;
       if (mode == 2) {
         int f = G / rem;
