@@ -206,6 +206,14 @@ def test_fused_allgather_targets_and_argument_checks():
     assert rc == _lib.E_BAD_ARG and b"n_peers" in lib.kcg_last_error()
     rc = lib.kcg_launch_gemm_allgather(1, ctypes.byref(f32), 0, 0, 256, 256, 256, None, arr, 1)
     assert rc == _lib.E_BAD_CONFIG and b"single-pass" in lib.kcg_last_error()
+    # batched launches: tcgen05 kernels only, at least one batch
+    simt = compile_info(default_config(256, 256, 256, E.float32, KERNEL_VARIANT=1, BLOCK_SIZE_M=64, BLOCK_SIZE_N=64,
+                                       BLOCK_SIZE_K=16, THREAD_SIZE_M=4, THREAD_SIZE_N=4, BLOCK_LAYOUT_M=4,
+                                       BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8, WARP_SCATTER_WIDTH_A=4,
+                                       WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4,
+                                       GLOB_LOAD_WIDTH_A=2, GLOB_LOAD_WIDTH_B=2).compileArgs())
+    assert lib.kcg_launch_gemm_batched(1, ctypes.byref(simt), 0, 0, 256, 256, 256, 2, None) == _lib.E_BAD_CONFIG
+    assert lib.kcg_launch_gemm_batched(1, ctypes.byref(bf16), 0, 0, 256, 256, 256, 0, None) == _lib.E_BAD_ARG
     arr[0] = 0x108  # not 16-byte aligned
     rc = lib.kcg_launch_gemm_allgather(1, ctypes.byref(bf16), 0, 0, 256, 256, 256, None, arr, 1)
     assert rc == _lib.E_BAD_ARG and b"aligned" in lib.kcg_last_error()
