@@ -164,6 +164,9 @@ def other_workloads(device: int):
         ("fp32 4096^3 3xTF32 tcgen05", 4096, 4096, 4096, E.float32, torch.float32, None, "f32(3xtf32)"),
         ("fp32 4096^3 FFMA SIMT", 4096, 4096, 4096, E.float32, torch.float32, simt, "f32"),
         ("bf16 8192^3 tcgen05", 8192, 8192, 8192, E.bfloat16, torch.bfloat16, None, "bf16"),
+        ("fp32 1024^3 3xTF32 tcgen05 (fits L2)", 1024, 1024, 1024, E.float32, torch.float32, None, "f32(3xtf32)"),
+        ("bf16 512x11008x11008 (86 pair tiles, stream-K)", 512, 11008, 11008, E.bfloat16, torch.bfloat16, None, "bf16"),
+        ("bf16 2048x11008x11008", 2048, 11008, 11008, E.bfloat16, torch.bfloat16, None, "bf16"),
     ]
     for tag, m, n, k, edt, tdt, keys, dt in cases:
         try:

@@ -53,6 +53,7 @@ def prebuilt_configs():
                 WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
     cfgs = [tuned_config(1024, 1024, 1024, E.float32), tuned_config(4096, 4096, 4096, E.float32),
             default_config(4096, 4096, 4096, E.float32, **simt), tuned_config(8192, 8192, 8192, E.bfloat16)]
+    cfgs += [tuned_config(512, 11008, 11008, E.bfloat16), tuned_config(2048, 11008, 11008, E.bfloat16)]
     for g in (1, 2, 4, 8):
         cfgs.append(tuned_config(32768 // g, 8192, 8192, E.bfloat16))
         if g > 1:  # tile of the bench's fused GEMM + all-gather leg (two TMEM accumulator buffers)
