@@ -298,3 +298,13 @@ def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     assert other.KERNEL_VARIANT == 4 and other.BLOCK_SIZE_M == 512
     small = tuned_config(4096, 8192, 8192, E.bfloat16, db=db2)
     assert small.KERNEL_VARIANT == 0 and small.BLOCK_SIZE_M == 256
+    # one to six waves of 256x256 pair tiles: pair kernel, long K blocks once K is long
+    mid = tuned_config(2048, 8192, 8192, E.bfloat16, db=db2)
+    assert (mid.KERNEL_VARIANT, mid.BLOCK_SIZE_M, mid.BLOCK_SIZE_N, mid.BLOCK_SIZE_K) == (4, 256, 256, 128)
+    # short K: the tile with two TMEM accumulator buffers; few tiles: 128x128 with 128-wide K blocks
+    short = tuned_config(4096, 4096, 256, E.bfloat16, db=db2)
+    assert (short.KERNEL_VARIANT, short.BLOCK_SIZE_M, short.BLOCK_SIZE_N) == (0, 128, 256)
+    few = tuned_config(512, 1024, 4096, E.bfloat16, db=db2)
+    assert (few.BLOCK_SIZE_M, few.BLOCK_SIZE_N, few.BLOCK_SIZE_K) == (128, 128, 128)
+    for kpm in (mid, short, few):
+        kpm.check()
