@@ -277,6 +277,59 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     assert r.returncode == 0 and r.stdout.startswith("OK"), r.stdout + r.stderr
 
 
+def test_symmetric_c_bookkeeping_with_a_fake_peer_library(monkeypatch):
+    """SymmetricC's handle exchange, mapping order and close/free bookkeeping, on a stand-in for the four
+    kcg_peer_* entries (no GPU): rank r's own buffer is never opened, every other rank's is opened once, the slab
+    targets point at rank r's rows in every copy."""
+    import ctypes
+    from codegendemo_b200 import _lib
+
+    class FakeLib:
+        def __init__(self, rank):
+            self.rank, self.opened, self.closed, self.freed = rank, [], [], []
+
+        def kcg_peer_alloc(self, device, nbytes, ptr_ref, handle):
+            ptr_ref._obj.value = 0x10000000 * (self.rank + 1)
+            handle.raw = bytes([self.rank]) * 64
+            self.nbytes = nbytes.value
+            return 0
+
+        def kcg_peer_open(self, device, handle, ptr_ref):
+            owner = handle.value[0] if handle.value else 0
+            self.opened.append(owner)
+            ptr_ref._obj.value = 0x10000000 * (owner + 1) + 0x1000000  # the same buffer at another address
+            return 0
+
+        def kcg_peer_close(self, device, ptr):
+            self.closed.append(ptr)
+            return 0
+
+        def kcg_peer_free(self, device, ptr):
+            self.freed.append(ptr)
+            return 0
+
+    world, M, N = 3, 768, 256
+    handles = [bytes([r]) * 64 for r in range(world)]
+    for rank in range(world):
+        fake = FakeLib(rank)
+        monkeypatch.setattr(_lib, "get_lib", lambda fake=fake: fake)
+        sym = kdist.SymmetricC(M, N, 2, rank, world, 0, exchange=lambda mine: handles)
+        assert fake.nbytes == M * N * 2 and sym.slab_bytes == (M // world) * N * 2
+        assert fake.opened == [r for r in range(world) if r != rank]
+        own = 0x10000000 * (rank + 1)
+        assert sym.bases[rank] == own and sym.local_slab == own + rank * sym.slab_bytes
+        assert sym.peer_slabs == [0x10000000 * (r + 1) + 0x1000000 + rank * sym.slab_bytes
+                                  for r in range(world) if r != rank]
+        sym.close()
+        sym.close()  # idempotent
+        assert len(fake.closed) == world - 1
+        sym.free()
+        sym.free()
+        assert fake.freed == [own]
+    with pytest.raises(ValueError):
+        kdist.SymmetricC(100, N, 2, 0, 3, 0, exchange=lambda mine: handles)
+
+
 def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     from codegendemo_b200.kcg.InfoDb import KernelDb
     from codegendemo_b200.kcg.matmul_op import tuned_config
