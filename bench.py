@@ -3,17 +3,24 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (all N): the M-sharded bf16 GEMM M=32768, N=K=8192 (fp32 accumulate, bf16 out, inputs
-normal(0,1)/sqrt(K), seed 0): rank r of N computes rows [r*M/N, (r+1)*M/N) against a replicated B;
-no data-path collective. Total work is fixed, so scaling is "strong"; at N=1 one GPU computes the whole
-product. A "step" is one pass of the rank's slab through the tcgen05 kernel. At N=1 the line also
-carries short measurements of the other single-GPU configs (fp32 4096^3 as 3xTF32 and as FFMA SIMT,
-bf16 8192^3) under "other_workloads".
+Workload (all N): the M-sharded bf16 GEMM M=32768, N=K=8192 (fp32 accumulate, bf16 out). Inputs follow the
+seeded recipe of the parity tests: one CPU generator with seed 0 draws A (normal(0,1)/sqrt(K)) and then B, both
+cast to bf16, so every machine and every rank sees the same bytes; rank r of N takes rows
+[r*M/N, (r+1)*M/N) of A against a replicated B; no data-path collective. Total work is fixed, so scaling is
+"strong"; at N=1 one GPU computes the whole product. A "step" is one pass of the rank's slab through the
+tcgen05 kernel.
+
+Outside the timed region every rank checks its result against the CPU oracle (``oracle_check``): eight random
+128-row blocks of its slab at every N, and every row at N=1; a failed check ends the run with a non-zero exit
+code. At N=1 the line also carries, under ``other_workloads``, the other single-GPU configs - fp32 1024^3 and
+4096^3 (3xTF32 and FFMA SIMT), bf16 8192^3 and the rectangular sweep M in {128, 512, 2048} x N=K in {4096, 11008}
+x {fp32, bf16} - each with its roofline and the same shape through cuBLAS (``torch.matmul`` on the device) timed
+the same way.
 
 Prints ONE JSON line on rank 0 (metric: GEMM TFLOP/s, device-timed with CUDA events, max over ranks).
-``--impl reference`` times the reference's CPU path for the same metric: ``torch.matmul`` on host
-tensors (the reference's own correctness oracle, Runtime/python/kcg/KCGTask.py:94) with all host
-threads, on a bounded row slab of the same workload.
+``--impl reference`` times the reference's CPU path for the same metric: ``torch.matmul`` on host tensors (the
+reference's own correctness oracle, Runtime/python/kcg/KCGTask.py:94) with all host threads, operands built
+once before the clock starts, only the call between the two timestamps (KCGTask.py:124-130).
 """
 import argparse
 import json
@@ -30,6 +37,8 @@ sys.path.insert(0, ROOT)
 M_TOTAL, N_SIZE, K_SIZE = 32768, 8192, 8192
 METRIC = "GEMM TFLOP/s (device-timed) bf16 32768x8192x8192 M-sharded, fp32 accumulate"
 UNIT = "TFLOP/s"
+TOL_16BIT, TOL_FP32 = 2e-2, 1e-4  # max |c - ref| / max(|ref|, rms(ref)): bf16/fp16 vs fp32 accumulation, fp32 vs fp64
+L2_BYTES = 126e6
 
 
 def env_int(name, default):
@@ -40,25 +49,35 @@ def env_int(name, default):
 
 
 def measured_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            d = json.load(f)
-        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]),
-                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
-    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+    from codegendemo_b200.kcg import roofline as rl
+    return rl.load_peaks(os.path.join(ROOT, "MEASURED_PEAKS.json"))
+
+
+def seeded_operands(M, N, K, torch_dtype, dist, seed=0):
+    """A (M x K) then B (K x N) from one CPU generator: uniform[-1, 1) or normal(0,1)/sqrt(K), cast afterwards.
+    The same recipe as the parity tests' inputs; identical bytes on every machine."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    if dist == "uniform":
+        A = torch.rand(M, K, generator=g) * 2 - 1
+        B = torch.rand(K, N, generator=g) * 2 - 1
+    else:
+        A = torch.randn(M, K, generator=g) / math.sqrt(K)
+        B = torch.randn(K, N, generator=g) / math.sqrt(K)
+    return A.to(torch_dtype), B.to(torch_dtype)
 
 
 class ClockSampler:
     """Samples SM clock, power and throttle reasons with nvidia-smi while the GPU works.
 
-    Each sample carries nvidia-smi's own timestamp, so `stop()` can keep the samples that fall inside
-    the timed region; when that region is too short for three samples the window is widened to the
-    warm-up launches that run right before it (same kernel, same load) and the result says so.
+    Each sample carries nvidia-smi's own timestamp, so `window()` can keep the samples that fall inside a
+    timed region; when that region is too short for three samples `stop()` widens the window to the warm-up
+    launches that run right before it (same kernel, same load) and the result says so.
     """
     QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
@@ -89,17 +108,9 @@ class ClockSampler:
         except ValueError:
             return None
 
-    def stop(self, timed=(None, None), loaded=(None, None)) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        samples = []
-        for ln in self.lines:
+    def samples(self):
+        out = []
+        for ln in list(self.lines):
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 9:
                 continue
@@ -108,8 +119,33 @@ class ClockSampler:
                        "power": float(parts[3])}
             except ValueError:
                 continue
-            rec["reasons"] = [n for n, v in zip(names, parts[5:9]) if v.lower().startswith("active")]
-            samples.append(rec)
+            rec["reasons"] = [n for n, v in zip(self.NAMES, parts[5:9]) if v.lower().startswith("active")]
+            out.append(rec)
+        return out
+
+    @staticmethod
+    def summarise(used, label):
+        sm = sorted(r["sm"] for r in used)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
+                "sm_max_mhz": max((r["max"] for r in used), default=None),
+                "power_w_max": max((r["power"] for r in used), default=None),
+                "samples": len(used), "window": label,
+                "reasons": sorted({x for r in used for x in r["reasons"]})}
+
+    def window(self, lo, hi, label):
+        """Summary of the samples taken between two host timestamps (the sampler keeps running)."""
+        used = [r for r in self.samples() if r["t"] is not None and lo <= r["t"] <= hi]
+        return self.summarise(used, label)
+
+    def stop(self, timed=(None, None), loaded=(None, None)) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        samples = self.samples()
 
         def window(lo, hi):
             if lo is None:
@@ -121,12 +157,7 @@ class ClockSampler:
             used, label = window(*loaded), "warm-up + timed region"
         if len(used) < 1:
             used, label = samples, "whole run"
-        sm = sorted(r["sm"] for r in used)
-        reasons = sorted({x for r in used for x in r["reasons"]})
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None,
-                "sm_max_mhz": max((r["max"] for r in used), default=None),
-                "power_w_max": max((r["power"] for r in used), default=None),
-                "samples": len(used), "window": label, "reasons": reasons}
+        return self.summarise(used, label)
 
 
 def build_bf16_kernel(m_rows: int, device: int):
@@ -136,117 +167,224 @@ def build_bf16_kernel(m_rows: int, device: int):
     return kpm, build_kernel(kpm, device)
 
 
-def time_kernel(kern, a, b, c, steps, warmup):
-    """Per-launch device times (ms) from CUDA events on the launching stream."""
+# ------------------------------------------------------------------------------------ oracle check
+def rel_error(c, ref):
+    """max |c - ref| / max(|ref|, rms(ref)) on host tensors (the gate of the parity tests), and a NaN flag."""
     import torch
-    for _ in range(warmup):
-        kern.run(a, b, c)
-    torch.cuda.synchronize()
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    for s, e in evs:
-        s.record()
-        kern.run(a, b, c)
-        e.record()
-    torch.cuda.synchronize()
-    return [s.elapsed_time(e) for s, e in evs]
+    c, ref = c.double(), ref.double()
+    if torch.isnan(c).any().item():
+        return float("inf"), True
+    rms = ref.pow(2).mean().sqrt().clamp_min(1e-300)
+    return float(((c - ref).abs() / torch.maximum(ref.abs(), rms)).max().item()), False
 
 
-def other_workloads(device: int):
-    """Short device-timed figures for the remaining single-GPU configs (inputs > L2 or noted)."""
+def oracle_check(c_dev, A_slab, B, full: bool, blocks: int = 8, seed: int = 0):
+    """This rank's device result against the CPU oracle (``oracle.host_matmul``: the reference's ``torch.matmul``
+    check on host tensors, fp32 accumulation for bf16 data), outside any timed region: `blocks` random 128-row
+    blocks of the slab, and every row when `full`. Test infrastructure used as the checker only."""
     import torch
-    from codegendemo_b200.kcg.matmul_op import build_kernel, default_config, tuned_config
-    from codegendemo_b200.kcg.Utils import EnumKernelDType as E
-    out = []
-    simt = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
-                THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
-                WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
-    cases = [
-        ("fp32 4096^3 3xTF32 tcgen05", 4096, 4096, 4096, E.float32, torch.float32, None, "f32(3xtf32)"),
-        ("fp32 4096^3 FFMA SIMT", 4096, 4096, 4096, E.float32, torch.float32, simt, "f32"),
-        ("bf16 8192^3 tcgen05", 8192, 8192, 8192, E.bfloat16, torch.bfloat16, None, "bf16"),
-        ("fp32 1024^3 3xTF32 tcgen05 (fits L2)", 1024, 1024, 1024, E.float32, torch.float32, None, "f32(3xtf32)"),
-        ("bf16 512x11008x11008 (86 pair tiles, stream-K)", 512, 11008, 11008, E.bfloat16, torch.bfloat16, None, "bf16"),
-        ("bf16 2048x11008x11008", 2048, 11008, 11008, E.bfloat16, torch.bfloat16, None, "bf16"),
-    ]
-    for tag, m, n, k, edt, tdt, keys, dt in cases:
-        try:
-            kpm = tuned_config(m, n, k, edt) if keys is None else default_config(m, n, k, edt, **keys)
-            inc, kern = build_kernel(kpm, device)
-            g = torch.Generator(device=f"cuda:{device}").manual_seed(0)
-            a = (torch.randn(m, k, generator=g, device=f"cuda:{device}") / math.sqrt(k)).to(tdt)
-            b = (torch.randn(k, n, generator=g, device=f"cuda:{device}") / math.sqrt(k)).to(tdt)
-            c = torch.empty(m, n, dtype=tdt, device=f"cuda:{device}")
-            ts = time_kernel(kern, a, b, c, steps=10, warmup=3)
-            kern.checkStatus()
-            ts.sort()
-            med = ts[len(ts) // 2]
-            out.append({"workload": tag, "dtype": dt, "ms": round(med, 4),
-                        "tflops": round(2.0 * m * n * k / (med * 1e9), 1),
-                        "tile": f"{kpm.BLOCK_SIZE_M}x{kpm.BLOCK_SIZE_N}x{kpm.BLOCK_SIZE_K}",
-                        "kernel_variant": int(inc.kernelInfo["kernel"])})
-            del a, b, c
-        except Exception as e:  # a secondary figure must not lose the headline line
-            out.append({"workload": tag, "error": str(e)[:200]})
+    from oracle import oracle
+    rows = A_slab.shape[0]
+    nb = rows // 128
+    g = torch.Generator().manual_seed(1000 + seed)
+    pick = torch.randperm(nb, generator=g)[:min(blocks, nb)].sort().values.tolist()
+    worst, nan = 0.0, False
+    for b in pick:
+        ref = oracle.host_matmul(A_slab[b * 128:(b + 1) * 128], B)
+        e, n = rel_error(c_dev[b * 128:(b + 1) * 128].cpu().float(), ref)
+        worst, nan = max(worst, e), nan or n
+    out = {"blocks": len(pick), "block_rows": 128, "max_rel": worst}
+    if full:
+        t0 = time.perf_counter()
+        worst_full = 0.0
+        chunk = 4096
+        for r0 in range(0, rows, chunk):
+            ref = oracle.host_matmul(A_slab[r0:r0 + chunk], B)
+            e, n = rel_error(c_dev[r0:r0 + chunk].cpu().float(), ref)
+            worst_full, nan = max(worst_full, e), nan or n
+        out.update({"full_rows": rows, "full_max_rel": worst_full, "full_check_s": round(time.perf_counter() - t0, 1)})
+        worst = max(worst, worst_full)
+    out.update({"tol": TOL_16BIT, "ok": bool(worst <= TOL_16BIT and not nan),
+                "against": "oracle.host_matmul (torch.matmul on host tensors, fp32 accumulation)"})
     return out
 
 
-def cpu_sample(rows: int, threads: int, repeats: int = 1):
-    """torch.matmul on host tensors for a `rows`-row slab of the workload (bf16 inputs up-cast to
-    fp32, as the oracle computes); returns (seconds per pass, TFLOP/s)."""
+# ------------------------------------------------------------------------------------ timing helpers
+def time_launches(fn, launches, warmup):
+    """Per-launch device times (ms): CUDA events on the launching stream around every launch, launches queued
+    back to back (no host synchronisation in between)."""
     import torch
-    from oracle import oracle
-    torch.set_num_threads(threads)
-    A, B = oracle.make_inputs(rows, N_SIZE, K_SIZE, torch.bfloat16, dist="normal", seed=0)
-    Af, Bf = A.float(), B.float()
-    torch.matmul(Af[:64], Bf)  # warm the BLAS threads
-    best = float("inf")
-    for _ in range(repeats):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(launches + 1)]
+    evs[0].record()
+    for i in range(launches):
+        fn()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    return [evs[i].elapsed_time(evs[i + 1]) for i in range(launches)]
+
+
+def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches: int = 20):
+    """Device-timed figures for the remaining single-GPU configs. Per workload: our kernel (the config the
+    operator picks) and cuBLAS (``torch.matmul`` on the device, a comparison) timed the same way - median of
+    `launches` back-to-back launches; the roofline min(tensor peak, arithmetic intensity x measured HBM bandwidth);
+    the largest difference between the two results. Problems that fit the L2 rotate over copies of their operands
+    so that every launch starts cold. One clock sample per group of workloads."""
+    import torch
+    from codegendemo_b200.kcg import roofline as rl
+    from codegendemo_b200.kcg.matmul_op import build_kernel, default_config, tuned_config
+    from codegendemo_b200.kcg.Utils import EnumKernelDType as E
+    simt = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
+                THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
+                WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
+    f32, bf16 = (E.float32, torch.float32), (E.bfloat16, torch.bfloat16)
+    groups = [
+        ("square fp32", [("c1 fp32 1024^3 3xTF32", 1024, 1024, 1024, f32, "uniform", None),
+                         ("c2 fp32 4096^3 3xTF32", 4096, 4096, 4096, f32, "uniform", None),
+                         ("c2 fp32 4096^3 FFMA SIMT", 4096, 4096, 4096, f32, "uniform", simt)]),
+        ("square bf16", [("c3 bf16 8192^3", 8192, 8192, 8192, bf16, "normal", None)]),
+    ]
+    for nk in (4096, 11008):
+        for (edt, tdt), tag in ((bf16, "bf16"), (f32, "fp32")):
+            groups.append((f"c4 {tag} N=K={nk}",
+                           [(f"c4 {tag} {m}x{nk}x{nk}", m, nk, nk, (edt, tdt), "uniform", None) for m in (128, 512, 2048)]))
+    dev = f"cuda:{device}"
+    out, group_clocks = [], []
+    torch.backends.cuda.matmul.allow_tf32 = False  # the cuBLAS comparison of fp32 data is a true fp32 GEMM
+    for gname, cases in groups:
+        t_g0 = time.time()
+        for tag, m, n, k, (edt, tdt), dist, keys in cases:
+            try:
+                kpm = tuned_config(m, n, k, edt) if keys is None else default_config(m, n, k, edt, **keys)
+                inc, kern = build_kernel(kpm, device)
+                A, B = seeded_operands(m, n, k, tdt, dist, seed=0)
+                eb = A.element_size()
+                nbytes = eb * (m * k + k * n + m * n)
+                copies = 1 if nbytes > L2_BYTES else int(2 * L2_BYTES // nbytes) + 2
+                sets = [(A.to(dev), B.to(dev), torch.empty(m, n, dtype=tdt, device=dev)) for _ in range(copies)]
+                del A, B
+                turn = [0]
+
+                def ours():
+                    a, b, c = sets[turn[0] % copies]
+                    turn[0] += 1
+                    kern.run(a, b, c)
+
+                def cublas():
+                    a, b, c = sets[turn[0] % copies]
+                    turn[0] += 1
+                    torch.matmul(a, b, out=c)
+
+                ts = sorted(time_launches(ours, launches, 3))
+                kern.checkStatus()
+                a0, b0, c0 = sets[0]
+                kern.run(a0, b0, c0)
+                mine = c0.clone()
+                tl = sorted(time_launches(cublas, launches, 3))
+                torch.matmul(a0, b0, out=c0)
+                scale = c0.float().abs().max().clamp_min(1e-30)
+                diff = float(((mine.float() - c0.float()).abs().max() / scale).item())
+                med, lib_med = ts[len(ts) // 2], tl[len(tl) // 2]
+                flops = rl.gemm_flops(m, n, k)
+                variant = int(inc.kernelInfo["kernel"])
+                tensor_peak = rl.tensor_peak_tflops(str(tdt).replace("torch.", ""), variant == 1, peaks)
+                roof = rl.shape_roofline(m, n, k, eb, tensor_peak, peaks["hbm_gbs"])
+                bound, peak = roof["bound"], roof["peak"]
+                tfl = flops / (med * 1e9)
+                out.append({
+                    "workload": tag, "dtype": "f32(3xtf32)" if (tdt == torch.float32 and variant != 1) else
+                    ("f32" if tdt == torch.float32 else "bf16"), "ms": round(med, 4), "ms_best": round(ts[0], 4),
+                    "tflops": round(tfl, 1), "gbs": round(nbytes / med / 1e6, 0),
+                    "roofline": {"bound": bound, "peak": round(peak, 1), "frac": round(tfl / peak, 4),
+                                 "peak_source": ("FFMA pipe 74 TFLOP/s" if variant == 1 else
+                                                 "nominal TF32 1100 / 3" if tdt == torch.float32 else
+                                                 f"{peaks['source']} bf16_tflops") +
+                                                (f", capped by AI x {peaks['source']} hbm_gbs" if bound == "hbm" else "")},
+                    "cublas_tflops": round(flops / (lib_med * 1e9), 1), "vs_cublas": round(lib_med / med, 3),
+                    "max_diff_vs_cublas_rel": diff,
+                    "tile": f"{kpm.BLOCK_SIZE_M}x{kpm.BLOCK_SIZE_N}x{kpm.BLOCK_SIZE_K}", "split_k": int(kpm.LOCAL_SPLIT_U),
+                    "kernel_variant": variant, "launches": launches,
+                    "l2": "larger than L2" if copies == 1 else f"cold: rotates over {copies} operand sets",
+                    "group": gname})
+                del sets, mine, a0, b0, c0
+                torch.cuda.empty_cache()
+            except Exception as e:  # a secondary figure must not lose the headline line
+                out.append({"workload": tag, "group": gname, "error": str(e)[:300]})
+        group_clocks.append(dict(sampler.window(t_g0, time.time(), gname), group=gname))
+    return out, group_clocks
+
+
+# ------------------------------------------------------------------------------------ CPU legs
+class CpuGemm:
+    """The reference's CPU path for this workload: ``torch.matmul`` on host tensors, bf16 operands up-cast to
+    fp32 (as the oracle computes), all host threads. Operands are built ONCE here; `timed_pass` holds nothing
+    but the call between its two timestamps."""
+
+    def __init__(self, A_bf16, B_bf16, threads: int, budget_s: float, passes: int):
+        import torch
+        torch.set_num_threads(threads)
+        self.threads = threads
+        Bf = B_bf16.float()
+        probe = A_bf16[:256].float()
+        torch.matmul(probe, Bf)  # warm the BLAS threads
         t0 = time.perf_counter()
-        torch.matmul(Af, Bf)
-        best = min(best, time.perf_counter() - t0)
-    return best, 2.0 * rows * N_SIZE * K_SIZE / best / 1e12
+        torch.matmul(probe, Bf)
+        per_row = (time.perf_counter() - t0) / 256
+        # all rows if `passes` passes of them fit the budget, else the largest 128-row multiple that does
+        rows = A_bf16.shape[0]
+        if per_row * rows * passes > budget_s:
+            rows = max(1024, int(budget_s / passes / per_row) // 128 * 128)
+        self.rows = min(rows, A_bf16.shape[0])
+        self.Af, self.Bf = A_bf16[:self.rows].float(), Bf
+        self.flops = 2.0 * self.rows * Bf.shape[1] * Bf.shape[0]
+
+    def timed_pass(self) -> float:
+        import torch
+        t0 = time.perf_counter()
+        torch.matmul(self.Af, self.Bf)
+        return time.perf_counter() - t0
+
+    def sample(self) -> str:
+        what = "the whole product" if self.rows == M_TOTAL else f"a {self.rows}-row slab of A"
+        return (f"{what} ({self.rows}x{K_SIZE} times {K_SIZE}x{N_SIZE}) per pass, torch.matmul fp32 on host tensors "
+                f"(the reference's oracle call), operands resident before the clock starts")
 
 
-def pick_cpu_rows(threads: int, target_s: float):
-    """Row-slab size whose host GEMM takes about `target_s` seconds (probe with 128 rows first)."""
-    t, _ = cpu_sample(128, threads)
-    rows = int(128 * target_s / max(t, 1e-6))
-    rows = max(128, min(M_TOTAL, (rows // 128) * 128))
-    return rows
+def workload_config(n_gpus):
+    return {"workload": f"bf16 NN GEMM M=32768 N=8192 K=8192 sharded by M over {n_gpus} GPU(s), B replicated, "
+                        "C sharded (at 1 GPU the whole product); inputs normal(0,1)/sqrt(K), CPU generator seed 0",
+            "m": M_TOTAL, "n": N_SIZE, "k": K_SIZE, "rows_per_gpu": M_TOTAL // n_gpus,
+            "l2": "inputs larger than L2 (A slab + B + C slab >= 256 MiB per GPU); no flush"}
 
 
 def run_reference(args, rank, world):
     if rank != 0:
         return 0
+    import torch
     threads = os.cpu_count() or 1
-    rows = pick_cpu_rows(threads, target_s=max(1.0, 20.0 / max(1, args.steps + args.warmup)))
+    A, B = seeded_operands(M_TOTAL, N_SIZE, K_SIZE, torch.bfloat16, "normal", seed=0)
+    cpu = CpuGemm(A, B, threads, budget_s=120.0, passes=max(1, args.steps + args.warmup))
+    del A, B
     for _ in range(args.warmup):
-        cpu_sample(rows, threads)
-    t0 = time.perf_counter()
+        cpu.timed_pass()
+    total = 0.0
     for _ in range(args.steps):
-        cpu_sample(rows, threads)
-    dt = (time.perf_counter() - t0) / max(1, args.steps)
-    val = 2.0 * rows * N_SIZE * K_SIZE / dt / 1e12
-    sample = f"{rows}-row slab of A ({rows}x{K_SIZE}) times full B per step, torch.matmul fp32 on host"
+        total += cpu.timed_pass()
+    dt = total / max(1, args.steps)
+    val = cpu.flops / dt / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": round(val, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": round(val, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": round(val, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": cpu.sample()},
         "e2e": {"value": round(val, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
     return 0
-
-
-def workload_config(n_gpus):
-    return {"workload": f"bf16 NN GEMM M=32768 N=8192 K=8192 sharded by M over {n_gpus} GPU(s), B replicated, "
-                        "C sharded (BASELINE.json configs[4]; at 1 GPU the whole product)",
-            "m": M_TOTAL, "n": N_SIZE, "k": K_SIZE, "rows_per_gpu": M_TOTAL // n_gpus,
-            "tile": "chosen per slab shape from the kernel database / rule of thumb (see config.kernel)",
-            "l2": "inputs larger than L2 (A slab + B + C slab >= 256 MiB per GPU); no flush"}
 
 
 def main():
@@ -255,7 +393,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-extras", action="store_true", help="skip other_workloads and cpu_baseline")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -280,13 +418,15 @@ def main():
     row0, row1 = kdist.shard_rows(M_TOTAL, n_gpus, rank, 256)
     rows = row1 - row0
 
-    # Seeded synthetic operands, generated on the device per slab (values: normal(0,1)/sqrt(K)).
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    a = (torch.randn(rows, K_SIZE, generator=g, device=dev) / math.sqrt(K_SIZE)).to(torch.bfloat16)
-    gb = torch.Generator(device=dev).manual_seed(99)
-    b = (torch.randn(K_SIZE, N_SIZE, generator=gb, device=dev) / math.sqrt(K_SIZE)).to(torch.bfloat16)
-    kdist.replicate_b(b, src=0)  # every rank holds the same B before timing
-    c = torch.empty(rows, N_SIZE, dtype=torch.bfloat16, device=dev)
+    # Seeded synthetic operands (see seeded_operands): every rank draws the same A and B and keeps its row slab.
+    A_full, B_host = seeded_operands(M_TOTAL, N_SIZE, K_SIZE, torch.bfloat16, "normal", seed=0)
+    A_host = A_full[row0:row1].contiguous()
+    if n_gpus > 1:
+        del A_full
+    a = A_host.to(dev)
+    b = B_host.to(dev)
+    kdist.replicate_b(b, src=0)  # every rank holds the same B before timing (the bytes already agree)
+    c = torch.full((rows, N_SIZE), float("nan"), dtype=torch.bfloat16, device=dev)
 
     kpm, (inc, kern) = build_bf16_kernel(rows, local_rank)
     kernel_desc = (f"tile {kpm.BLOCK_SIZE_M}x{kpm.BLOCK_SIZE_N}x{kpm.BLOCK_SIZE_K}, {inc.kernelInfo['stages']} stages, "
@@ -334,14 +474,22 @@ def main():
     t_cont1 = time.time()
     clocks = None
     if rank == 0:
-        clocks = sampler.stop((t_timed0, t_timed1), (t_loaded0, t_cont1))
-        if clocks.get("window") == "warm-up + timed region" and t_cont1 - t_cont0 > 0.05:
-            clocks["window"] = "warm-up + timed region + untimed continuation of the same launches"
+        used = sampler.window(t_timed0, t_timed1, "timed region")
+        if used["samples"] < 3:
+            used = sampler.window(t_loaded0, t_cont1, "warm-up + timed region" + (
+                " + untimed continuation of the same launches" if t_cont1 - t_cont0 > 0.05 else ""))
+        clocks = used
     kern.checkStatus()
     total_ms = kdist.max_over_ranks(total_ms, device=dev)
     ms_per_step = total_ms / args.steps
     flops_total = 2.0 * M_TOTAL * N_SIZE * K_SIZE
     value = flops_total / (ms_per_step * 1e9)
+
+    # ---- parity, outside the timed region: this rank's slab against the CPU oracle
+    check = oracle_check(c, A_host, B_host, full=(n_gpus == 1), blocks=8, seed=rank)
+    check["max_rel"] = kdist.max_over_ranks(check["max_rel"], device=dev)
+    check["ok"] = kdist.max_over_ranks(0.0 if check["ok"] else 1.0, device=dev) == 0.0
+    check["ranks_checked"] = n_gpus
 
     # roofline of the one kernel in the step (this rank's launches)
     peaks = measured_peaks()
@@ -362,8 +510,8 @@ def main():
                 "frac_of_nominal_2250": round(achieved / 2250.0, 4), "kernel_ms": round(avg_launch_ms, 4)}
 
     # end to end through the C ABI with host buffers: H2D(A slab, B) + kernel + D2H(C slab) per step
-    hA = a.cpu().pin_memory()
-    hB = b.cpu().pin_memory()
+    hA = A_host.pin_memory()
+    hB = B_host.pin_memory()
     hC = torch.empty(rows, N_SIZE, dtype=torch.bfloat16).pin_memory()
     kern.runHost(hA, hB, hC)  # warm-up (allocates the library's device buffers)
     barrier()
@@ -373,16 +521,27 @@ def main():
         kern.runHost(hA, hB, hC)
     e1.record()
     barrier()
-    e2e_ms = kdist.max_over_ranks(e0.elapsed_time(e1) / args.e2e_steps, device=dev)
+    own_e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+    e2e_ms = kdist.max_over_ranks(own_e2e_ms, device=dev)
+    h2d_rank, d2h_rank = int(hA.numel() * 2 + hB.numel() * 2), int(hC.numel() * 2)
     e2e = {"value": round(flops_total / (e2e_ms * 1e9), 2), "unit": UNIT, "ms_per_step": round(e2e_ms, 3),
-           "h2d_bytes_per_step": int(hA.numel() * 2 + hB.numel() * 2) * n_gpus,
-           "d2h_bytes_per_step": int(hC.numel() * 2) * n_gpus, "steps": args.e2e_steps,
+           "h2d_bytes_per_step": h2d_rank * n_gpus, "d2h_bytes_per_step": d2h_rank * n_gpus, "steps": args.e2e_steps,
+           # copies in both directions overlap inside a step, so each rate is that direction's bytes over the whole step
+           "per_rank": {"h2d_bytes": h2d_rank, "d2h_bytes": d2h_rank,
+                        "h2d_gbs": round(h2d_rank / e2e_ms / 1e6, 1), "d2h_gbs": round(d2h_rank / e2e_ms / 1e6, 1),
+                        "note": "every rank re-sends the replicated B each step; all ranks share one host"},
            "api": "kcg_matmul_host (CompiledKernel.runHost), pinned host buffers"}
     # The host entry runs row slabs, whose last-wave K split can differ from the whole-slab launch:
     # equal up to fp32 summation order, i.e. a rare last-bit difference after rounding to bf16.
     dev_c = c.cpu().float()
     e2e_diff = float(((hC.float() - dev_c).abs().max() / dev_c.abs().max().clamp_min(1e-30)).item())
     same = bool(e2e_diff <= 1e-2)
+    # and the host-buffer result against the oracle too (same sampled blocks)
+    e2e_check = oracle_check(hC, A_host, B_host, full=False, blocks=8, seed=rank)
+    e2e["oracle_check"] = {"blocks": e2e_check["blocks"],
+                           "max_rel": kdist.max_over_ranks(e2e_check["max_rel"], device=dev),
+                           "tol": TOL_16BIT,
+                           "ok": kdist.max_over_ranks(0.0 if e2e_check["ok"] else 1.0, device=dev) == 0.0}
 
     # Optional collective, timed apart from the GEMM: all-gather of the C slabs (NCCL over NVLink).
     allgather = None
@@ -405,14 +564,14 @@ def main():
                      "bus_gbs": round(recv / ag_ms / 1e6, 1),  # all-gather bus bandwidth = (n-1)/n * total / t
                      "correct": bool(torch.equal(c_full[row0:row1], c)), "note": "not part of value / ms_per_step"}
         # The same product with the all-gather fused into the kernel: every finished tile is stored
-        # into the full C of all GPUs (peer buffers mapped through CUDA IPC, bulk tensor stores over NVLink).
+        # into the full C of all GPUs (peer buffers mapped through CUDA IPC, stores over NVLink).
         # Nothing waits inside the kernel; a step is complete when every rank's launch has completed.
         sym = kdist.SymmetricC(M_TOTAL, N_SIZE, 2, rank, world, local_rank)
         full = sym.full(torch.bfloat16)
         full.zero_()
         barrier()
         # Two tiles are tried: the GEMM's own, and 128x256 whose two TMEM accumulator buffers let the
-        # epilogue (now bounded by NVLink) overlap the next tile's main loop.
+        # epilogue overlap the next tile's main loop.
         from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
         from codegendemo_b200.kcg.Utils import EnumKernelDType as E
         _, kern_ov = build_kernel(default_config(rows, N_SIZE, K_SIZE, E.bfloat16), local_rank)
@@ -440,6 +599,15 @@ def main():
             ok_here = bool(torch.equal(full, c_full)) if label == "gemm_tile" else diff <= 1e-2
             fused_ok[label] = kdist.max_over_ranks(0.0 if ok_here else 1.0, device=dev) == 0.0
             barrier()
+        # ... and against the CPU oracle: a 128-row block of ANOTHER rank's rows, as this GPU received it
+        other = (rank + 1) % world
+        A_all, _ = seeded_operands(M_TOTAL, N_SIZE, K_SIZE, torch.bfloat16, "normal", seed=0)
+        r_chk = other * rows + 128 * (rank % max(1, rows // 128))
+        from oracle import oracle
+        ref_blk = oracle.host_matmul(A_all[r_chk:r_chk + 128], B_host)
+        del A_all
+        g_err, g_nan = rel_error(full[r_chk:r_chk + 128].cpu().float(), ref_blk)
+        gathered_ok = kdist.max_over_ranks(0.0 if (g_err <= TOL_16BIT and not g_nan) else 1.0, device=dev) == 0.0
         fused_ms = min(fused_by_tile.values())
         sent = (n_gpus - 1) * rows * N_SIZE * 2
         allgather["fused_into_gemm"] = {
@@ -449,6 +617,8 @@ def main():
             "nvlink_gbs_per_rank": round(sent / fused_ms / 1e6, 1),
             "nvlink_floor_ms_at_770_gbs": round(sent / 770e9 * 1e3, 4),
             "correct": all(fused_ok.values()), "correct_by_tile": fused_ok,
+            "oracle_check_of_received_rows": {"max_rel": kdist.max_over_ranks(g_err, device=dev), "tol": TOL_16BIT,
+                                              "ok": gathered_ok},
             "api": "kcg_launch_gemm_allgather (kcg.dist.matmul_allgather)"}
         barrier()
         sym.close()
@@ -456,33 +626,36 @@ def main():
         sym.free()
         del c_full, full
 
-    extras, cpu_base = None, None
+    extras, group_clocks, cpu_base = None, None, None
     if rank == 0 and n_gpus == 1 and not args.no_extras:
         del hA, hB, hC
-        extras = other_workloads(local_rank)
+        extras, group_clocks = other_workloads(local_rank, peaks, sampler)
         threads = os.cpu_count() or 1
-        crow = pick_cpu_rows(threads, target_s=12.0)
-        sec, tf = cpu_sample(crow, threads)
-        reps = max(1, min(8, int(10.0 / max(sec, 1e-3))))  # about 10 s of host work in total
-        if reps > 1:
-            sec, tf = cpu_sample(crow, threads, repeats=reps)
-        cpu_base = {"value": round(tf, 4), "unit": UNIT, "cores": threads, "kind": "port",
-                    "sample": f"{crow}-row slab ({crow}x{K_SIZE} times {K_SIZE}x{N_SIZE}), torch.matmul fp32 on host "
-                              f"(the reference's oracle call), best of {reps} passes of {sec:.2f} s"}
+        cpu = CpuGemm(A_full, B_host, threads, budget_s=20.0, passes=4)
+        secs = [cpu.timed_pass() for _ in range(4)]
+        best = min(secs)
+        cpu_base = {"value": round(cpu.flops / best / 1e12, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                    "sample": cpu.sample() + f"; best of {len(secs)} passes of {best:.2f} s"}
     if rank == 0:
+        sampler.stop()
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(n_gpus), kernel=kernel_desc), "roofline": roofline, "cpu_baseline": cpu_base, "e2e": e2e,
+            "config": workload_config(n_gpus), "kernel": kernel_desc, "roofline": roofline,
+            "oracle_check": check, "cpu_baseline": cpu_base, "e2e": e2e,
             "gpu_launches": int(launches), "clocks": clocks, "e2e_matches_device_result": same,
             "e2e_max_diff_vs_device_rel": e2e_diff,
-            "other_workloads": extras, "allgather_c": allgather,
+            "other_workloads": extras, "other_workloads_clocks": group_clocks, "allgather_c": allgather,
         }
         print(json.dumps(line), flush=True)
+    ok = check["ok"] and e2e["oracle_check"]["ok"]
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        sys.stderr.write(f"oracle check FAILED: {check} / e2e {e2e['oracle_check']}\n")
+        return 1
     return 0
 
 

@@ -12,7 +12,8 @@ import os
 NUM_CFG_KEYS = 31
 LIB_NAME = "libkcg_b200.so"
 
-KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TF32X1, KERNEL_TCGEN05_PAIR, KERNEL_NAIVE, KERNEL_WAIT_PROBE = 0, 1, 2, 3, 4, 100, 101
+KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, KERNEL_TF32X1, KERNEL_TCGEN05_PAIR, KERNEL_TCGEN05_CLUSTERK = 0, 1, 2, 3, 4, 5
+KERNEL_NAIVE, KERNEL_WAIT_PROBE = 100, 101
 
 E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_LARGE = (
     -1, -2, -3, -4, -5, -6, -7)
@@ -21,7 +22,8 @@ E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_L
 EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
-    "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
+    "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_strided", "kcg_softmax_rows",
+    "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
     "kcg_peer_free", "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
     "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
 )
@@ -49,6 +51,7 @@ class KernelInfo(ctypes.Structure):
 
     _SCALARS = ("smem_bytes", "kernel", "dtype", "bm", "bn", "bk", "stages", "splitk", "group",
                 "atrans", "m", "n", "k")
+    _RESERVED = {"num_sms": 0, "b_trans": 1}  # named slots of `reserved`
 
     def to_dict(self) -> dict:
         """Plain, picklable form (compile workers hand it to the process that owns the GPU)."""
@@ -58,6 +61,8 @@ class KernelInfo(ctypes.Structure):
         d["grid"] = list(self.grid)
         d["block"] = list(self.block)
         d["cluster"] = list(self.cluster)
+        for name, i in self._RESERVED.items():
+            d[name] = int(self.reserved[i])
         return d
 
     @classmethod
@@ -71,13 +76,16 @@ class KernelInfo(ctypes.Structure):
             o.cluster[i] = d["cluster"][i]
         for k in cls._SCALARS:
             setattr(o, k, d[k])
+        for name, i in cls._RESERVED.items():
+            o.reserved[i] = int(d.get(name, 0))
         return o
 
 
 class CompileOpts(ctypes.Structure):
     """``kcg_compile_opts``."""
     _fields_ = [("kernel", ctypes.c_int32), ("num_stages", ctypes.c_int32),
-                ("num_sms", ctypes.c_int32), ("force", ctypes.c_int32)]
+                ("num_sms", ctypes.c_int32), ("force", ctypes.c_int32), ("b_trans", ctypes.c_int32),
+                ("reserved", ctypes.c_int32 * 3)]
 
 
 class Epilogue(ctypes.Structure):
@@ -130,6 +138,13 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_launch_gemm_batched.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64,
                                             ctypes.c_int, ctypes.POINTER(Epilogue)]
     lib.kcg_launch_gemm_batched.restype = ctypes.c_int
+    lib.kcg_launch_gemm_strided.argtypes = [u64, ctypes.POINTER(KernelInfo), ctypes.c_int, u64, u64, u64, u64,
+                                            ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int,
+                                            ctypes.POINTER(Epilogue)]
+    lib.kcg_launch_gemm_strided.restype = ctypes.c_int
+    lib.kcg_softmax_rows.argtypes = [ctypes.c_int, u64, u64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
+                                     ctypes.c_float, ctypes.c_int]
+    lib.kcg_softmax_rows.restype = ctypes.c_int
     lib.kcg_peer_alloc.argtypes = [ctypes.c_int, u64, ctypes.POINTER(u64), ctypes.c_char_p]
     lib.kcg_peer_open.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(u64)]
     lib.kcg_peer_close.argtypes = [ctypes.c_int, u64]

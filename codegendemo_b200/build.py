@@ -3,8 +3,10 @@
     python -m codegendemo_b200.build            # library + default cubins
     python -m codegendemo_b200.build --lib-only
 
-The library's host code is plain C++ (g++) that binds the CUDA driver lazily; kernels are compiled by
-the library's own compile entry with ``nvcc -cubin -gencode arch=compute_100a,code=sm_100a``.
+The library is built with nvcc for sm_100a: its host code binds the CUDA driver lazily (so it loads without a GPU),
+and two pieces of device code are linked into it (the allocation-free split-K entry and the row softmax). The GEMM
+kernels themselves are compiled per config by the library's own compile entry with
+``nvcc -cubin -gencode arch=compute_100a,code=sm_100a``.
 """
 import os
 import subprocess
@@ -27,19 +29,15 @@ def build_library(force: bool = False) -> str:
     kdir = os.path.join(HERE, "csrc", "kernels")  # the allocation-free entry instantiates a kernel from these
     deps = srcs + [os.path.join(kdir, f) for f in sorted(os.listdir(kdir))] + [
         os.path.join(os.path.dirname(HERE), "include", "kcg_b200.h")]
-    extra = os.path.join(HERE, "csrc", "kcg_noalloc.cu")
-    if os.path.exists(extra):
-        deps.append(extra)
+    # device code linked into the library itself: the allocation-free split-K entry and the row softmax
+    extra = [os.path.join(HERE, "csrc", f) for f in ("kcg_noalloc.cu", "kcg_softmax.cu")]
+    deps += extra
     if not force and _newer(out, deps):
         return out
-    if os.path.exists(extra):
-        nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
-        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
-               "-Xcompiler", "-fPIC", "-cudart", "static", "-I" + os.path.join(HERE, "csrc", "kernels"),
-               "-o", out, *srcs, extra, "-ldl", "-lpthread"]
-    else:
-        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I" + os.path.join(CUDA_HOME, "include"),
-               "-o", out, *srcs, "-ldl", "-lpthread"]
+    nvcc = os.path.join(CUDA_HOME, "bin", "nvcc")
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-shared",
+           "-Xcompiler", "-fPIC", "-cudart", "static", "-I" + os.path.join(HERE, "csrc", "kernels"),
+           "-o", out, *srcs, *extra, "-ldl", "-lpthread"]
     subprocess.check_call(cmd)
     return out
 
@@ -53,7 +51,9 @@ def prebuilt_configs():
                 WARP_SCATTER_WIDTH_A=4, WARP_SCATTER_WIDTH_B=4, THREAD_SCATTER_WIDTH_A=4, THREAD_SCATTER_WIDTH_B=4)
     cfgs = [tuned_config(1024, 1024, 1024, E.float32), tuned_config(4096, 4096, 4096, E.float32),
             default_config(4096, 4096, 4096, E.float32, **simt), tuned_config(8192, 8192, 8192, E.bfloat16)]
-    cfgs += [tuned_config(512, 11008, 11008, E.bfloat16), tuned_config(2048, 11008, 11008, E.bfloat16)]
+    # the rectangular sweep the benchmark line carries
+    cfgs += [tuned_config(m, nk, nk, dt) for nk in (4096, 11008) for m in (128, 512, 2048)
+             for dt in (E.float32, E.bfloat16)]
     for g in (1, 2, 4, 8):
         cfgs.append(tuned_config(32768 // g, 8192, 8192, E.bfloat16))
         if g > 1:  # tile of the bench's fused GEMM + all-gather leg (two TMEM accumulator buffers)
@@ -75,17 +75,27 @@ def prune_stale_cubins() -> None:
             shutil.rmtree(full) if os.path.isdir(full) else os.remove(full)
 
 
-def prebuild_kernels(verbose: bool = True) -> int:
+def compile_many(kpms, workers: int = 0, verbose: bool = False):
+    """Compiles a list of configs on a thread pool (the compile entry is reentrant and runs nvcc in a child
+    process, so threads suffice); returns [(path, name)] in input order. Cached cubins cost nothing."""
+    from concurrent.futures import ThreadPoolExecutor
     from codegendemo_b200.kcg.KCGCompiler import KCGCompiler
-    prune_stale_cubins()
-    n = 0
-    for kpm in prebuilt_configs():
+
+    def one(kpm):
         kpm.check()
-        path = KCGCompiler().compileKernel(kpm)[0][0]
-        n += 1
+        path, name = KCGCompiler().compileKernel(kpm)[0][:2]
         if verbose:
             print("cubin:", os.path.basename(path))
-    return n
+        return path, name
+
+    workers = workers or min(16, os.cpu_count() or 1)
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        return list(pool.map(one, kpms))
+
+
+def prebuild_kernels(verbose: bool = True) -> int:
+    prune_stale_cubins()
+    return len(compile_many(prebuilt_configs(), verbose=verbose))
 
 
 if __name__ == "__main__":

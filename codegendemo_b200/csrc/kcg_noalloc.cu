@@ -32,7 +32,8 @@ using Gemm = kcg::TcGemm<KCG_DT_BF16, kBM, kBN, kBK, kStages, /*ATrans*/ 0, kSpl
 constexpr size_t kPartialBytes = static_cast<size_t>(KCG_NOALLOC_MAX_PARTIAL_FLOATS) * sizeof(float);
 constexpr size_t kCounterBytes = static_cast<size_t>(KCG_NOALLOC_MAX_TILES) * sizeof(unsigned int);
 
-// The whole scratch: [ partial tiles | tile counters | 4 status words ]. Host code must not
+// The whole scratch: [ partial tiles | tile counters | 4 status words ]. Static device memory
+// starts out zeroed. Host code must not
 // pass `g_scratch` itself to a kernel - in host code the name is only a handle for
 // cudaGetSymbolAddress, which yields the address the device sees.
 static __device__ __align__(256) unsigned char g_scratch[kPartialBytes + kCounterBytes + 256];
@@ -62,15 +63,32 @@ int cuda_fail(cudaError_t e, const char* what) {
   return fail(static_cast<int>(e), std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-// One-time set-up per device, with that device current: resolve the device address of the
-// scratch array and opt the kernel in to its dynamic shared memory. Nothing is allocated.
+// Makes `device` current for the length of a call and puts the caller's device back afterwards.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev == device) return cudaSuccess;
+    e = cudaSetDevice(device);
+    switched = (e == cudaSuccess);
+    return e;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+// One-time set-up per device, with that device current (the caller holds a DeviceGuard): resolve
+// the device address of the scratch array and opt the kernel in to its dynamic shared memory.
+// No allocation call is made; with CUDA's lazy module loading this is, however, the moment the
+// library's device image (the scratch array included) is materialised on the GPU.
 int setup_device(int device, PerDevice** out) {
-  if (device < 0 || device >= 16) return fail(KCG_E_BAD_ARG, "device out of range");
   std::lock_guard<std::mutex> lock(g_mutex);
   PerDevice& d = g_state[device];
   if (!d.ready) {
-    cudaError_t e = cudaSetDevice(device);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    cudaError_t e;
     void* ptr = nullptr;
     e = cudaGetSymbolAddress(&ptr, g_scratch);
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(scratch)");
@@ -128,10 +146,12 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
              kSplitK, partial_floats, KCG_NOALLOC_MAX_PARTIAL_FLOATS, tiles, KCG_NOALLOC_MAX_TILES);
     return fail(KCG_E_TOO_LARGE, buf);
   }
+  if (device < 0 || device >= 16) return fail(KCG_E_BAD_ARG, "device out of range");
+  DeviceGuard guard;  // the caller's current device is restored on every return path
+  cudaError_t ce = guard.enter(device);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
   PerDevice* d = nullptr;
   if (int e = setup_device(device, &d)) return e;
-  cudaError_t ce = cudaSetDevice(device);
-  if (ce != cudaSuccess) return cuda_fail(ce, "cudaSetDevice");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
   KcgGemmParams p;
@@ -139,6 +159,9 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
   constexpr kcg::TcLayout L = kcg::make_tc_layout(KCG_DT_BF16, kBM, kBN, kBK, 0);
   if (int e = encode(&p.tmA, A, K, M, L.a_box_inner, L.a_box_outer, L.a_tma_swizzle)) return e;
   if (int e = encode(&p.tmB, B, N, K, L.b_box_inner, L.b_box_outer, L.b_tma_swizzle)) return e;
+  // every tile is K-split here, so C is written by the reducing CTA with plain stores; the map is
+  // still a valid one because the kernel prefetches its descriptor
+  if (int e = encode(&p.tmC, C, N, M, 64, 32, 3 /*CU_TENSOR_MAP_SWIZZLE_128B*/)) return e;
   // partial tiles leave through TMA stores: the scratch array as one tall fp32 matrix of kBN
   // columns, 32 x 32 boxes with the 128B swizzle of the kernel's staging buffers
   if (int e = encode(&p.tmWs, reinterpret_cast<uint64_t>(d->scratch), kBN, kPartialBytes / (kBN * 4), 32, 32,
@@ -158,9 +181,11 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
   p.splitk_ws = reinterpret_cast<float*>(d->scratch);
   p.tile_counters = reinterpret_cast<unsigned int*>(d->scratch + kPartialBytes);
   p.status = reinterpret_cast<unsigned int*>(d->scratch + kPartialBytes + kCounterBytes);
-  // The array keeps whatever the previous call left: counters and status must start at zero
-  // (partials are fully rewritten before they are read).
-  ce = cudaMemsetAsync(d->scratch + kPartialBytes, 0, kCounterBytes + 256, st);
+  // The array keeps whatever the previous call left: the counters must start at zero (partials
+  // are fully rewritten before they are read). The status words are NOT cleared here: a kernel of
+  // an earlier asynchronous call that gave up in a bounded wait stays on record until a
+  // synchronising call reads (and clears) it below.
+  ce = cudaMemsetAsync(d->scratch + kPartialBytes, 0, kCounterBytes, st);
   if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(counters)");
   const int units = static_cast<int>(tiles) * kSplitK;
   const int grid = units < d->num_sms ? units : d->num_sms;
@@ -175,6 +200,8 @@ int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64
     ce = cudaMemcpy(status, p.status, sizeof(status), cudaMemcpyDeviceToHost);
     if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemcpy(status)");
     if (status[0] != 0) {
+      ce = cudaMemset(p.status, 0, sizeof(status));
+      if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemset(status)");
       char buf[128];
       snprintf(buf, sizeof(buf), "kernel gave up in a bounded wait (code %u, block %u)", status[0], status[1]);
       return fail(KCG_E_DEVICE_TIMEOUT, buf);

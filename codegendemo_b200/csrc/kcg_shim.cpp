@@ -121,14 +121,28 @@ int need_driver() {
 }
 
 // ------------------------------------------------------------- per-device state
-struct DeviceState {
-  bool init = false;
-  CUcontext ctx = nullptr;
+// What a launch needs besides its operands - the 4-word status block its bounded waits report
+// to, the split-K workspace and the tile counters - belongs to the STREAM it is queued on:
+// launches on one stream run in order and may share them, launches on different streams of one
+// GPU may overlap and must not. Slots are created on a stream's first launch and recycled
+// least-recently-used beyond kMaxStreamSlots (a freed buffer is released with cuMemFree, which
+// waits for the work that still uses it).
+struct StreamSlot {
+  CUstream stream = nullptr;
   CUdeviceptr status = 0;      // 4 x u32
   CUdeviceptr ws = 0;          // split-K partials
   size_t ws_bytes = 0;
   CUdeviceptr counters = 0;    // split-K tile counters
   size_t counters_n = 0;
+  uint64_t last_use = 0;
+};
+constexpr size_t kMaxStreamSlots = 32;
+
+struct DeviceState {
+  bool init = false;
+  CUcontext ctx = nullptr;
+  std::vector<StreamSlot> slots;
+  uint64_t use_clock = 0;
   CUdeviceptr hbuf[3] = {0, 0, 0};  // device copies for kcg_matmul_host
   size_t hbuf_bytes[3] = {0, 0, 0};
   CUstream hstream[3] = {nullptr, nullptr, nullptr};  // kcg_matmul_host: copy-in, compute, copy-out
@@ -137,26 +151,26 @@ struct DeviceState {
 };
 constexpr int kMaxDevices = 16;
 DeviceState g_dev[kMaxDevices];
-std::mutex g_dev_mutex;
+std::mutex g_dev_mutex;  // guards g_dev[*] (slots, buffers, tensor-map cache)
 std::atomic<uint64_t> g_launches{0};
 
 int ensure_device(int device, DeviceState** out) {
   if (int e = need_driver()) return e;
   if (device < 0 || device >= kMaxDevices) return fail(KCG_E_BAD_ARG, "device %d out of range", device);
   DeviceState& s = g_dev[device];
-  if (!s.init) {
-    CUdevice dev;
-    DRV(cuDeviceGet(&dev, device));
-    DRV(cuDevicePrimaryCtxRetain(&s.ctx, dev));
+  {
+    std::lock_guard<std::mutex> g(g_dev_mutex);
+    if (!s.init) {
+      CUdevice dev;
+      DRV(cuDeviceGet(&dev, device));
+      DRV(cuDevicePrimaryCtxRetain(&s.ctx, dev));
+      s.slots.reserve(kMaxStreamSlots);
+      s.init = true;
+    }
   }
   CUcontext cur = nullptr;
   DRV(cuCtxGetCurrent(&cur));
   if (cur != s.ctx) DRV(cuCtxSetCurrent(s.ctx));
-  if (!s.init) {
-    DRV(cuMemAlloc(&s.status, 16));
-    DRV(cuMemsetD32(s.status, 0, 4));
-    s.init = true;
-  }
   *out = &s;
   return 0;
 }
@@ -168,6 +182,46 @@ int grow(CUdeviceptr* p, size_t* have, size_t need) {
   *have = 0;
   DRV(cuMemAlloc(p, need));
   *have = need;
+  return 0;
+}
+
+int free_slot(StreamSlot& sl) {
+  if (sl.status) DRV(cuMemFree(sl.status));
+  if (sl.ws) DRV(cuMemFree(sl.ws));
+  if (sl.counters) DRV(cuMemFree(sl.counters));
+  sl = StreamSlot();
+  return 0;
+}
+
+// The slot of `stream` on this device (created on first use). Call with g_dev_mutex held.
+int slot_for(DeviceState* s, CUstream stream, bool create, StreamSlot** out) {
+  *out = nullptr;
+  for (StreamSlot& sl : s->slots)
+    if (sl.status && sl.stream == stream) {
+      sl.last_use = ++s->use_clock;
+      *out = &sl;
+      return 0;
+    }
+  if (!create) return 0;
+  StreamSlot* dst = nullptr;
+  for (StreamSlot& sl : s->slots)
+    if (!sl.status) dst = &sl;
+  if (!dst && s->slots.size() >= kMaxStreamSlots) {
+    dst = &s->slots[0];
+    for (StreamSlot& sl : s->slots)
+      if (sl.last_use < dst->last_use) dst = &sl;
+    if (int e = free_slot(*dst)) return e;
+    s->tmaps.clear();  // maps of the freed workspace
+  }
+  if (!dst) {
+    s->slots.emplace_back();
+    dst = &s->slots.back();
+  }
+  dst->stream = stream;
+  DRV(cuMemAlloc(&dst->status, 16));
+  DRV(cuMemsetD32(dst->status, 0, 4));
+  dst->last_use = ++s->use_clock;
+  *out = dst;
   return 0;
 }
 
@@ -190,6 +244,7 @@ struct Resolved {
   int kernel = 0;
   int stages = 0;
   int num_sms = 148;
+  int btrans = 0;
 };
 
 // The reference's KernelArgMatmul.check() (Operators/matmul.py:180-194) for the
@@ -259,6 +314,13 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     want = (kcg::tc_config_error(dt, bm, bn, bk, st, 1) == 0) ? KCG_KERNEL_TCGEN05 : KCG_KERNEL_SIMT;
   }
   r->kernel = want;
+  r->btrans = (opts && opts->b_trans) ? 1 : 0;
+  if (r->btrans) {
+    const bool single_pass16 = (want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TCGEN05_PAIR) && dt != KCG_DTYPE_FLOAT32;
+    if (!single_pass16)
+      return fail(KCG_E_BAD_CONFIG, "a B stored N x K (b_trans) needs a single-pass tcgen05 kernel with fp16 / bf16 data");
+    if (K % 8) return fail(KCG_E_BAD_CONFIG, "K must be a multiple of 8 for the TMA row stride of an N x K stored B");
+  }
   if (want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TF32X1) {
     if (want == KCG_KERNEL_TF32X1 && dt != KCG_DTYPE_FLOAT32)
       return fail(KCG_E_BAD_CONFIG, "the single-pass TF32 kernel needs float32 data");
@@ -282,6 +344,24 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if (!(opts && opts->num_stages > 0) && c[KCG_CFG_SHARED_PREFETCH])
       while (st < 7 && ok(st + 1)) ++st;
     if (!ok(st)) return fail(KCG_E_BAD_CONFIG, "tile %dx%dx%d / %d stages not buildable by the CTA-pair kernel", bm, bn, bk, st);
+    if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
+    r->stages = st;
+  } else if (want == KCG_KERNEL_TCGEN05_CLUSTERK) {
+    // one 128-row tile per cluster of LOCAL_SPLIT_U CTAs, partial tiles reduced in shared memory
+    const int split = c[KCG_CFG_LOCAL_SPLIT_U];
+    if (bm != 128) return fail(KCG_E_BAD_CONFIG, "the cluster split-K kernel needs BLOCK_SIZE_M = 128");
+    if (split > K / bk) return fail(KCG_E_BAD_CONFIG, "LOCAL_SPLIT_U %d exceeds the %d K blocks", split, K / bk);
+    auto ok = [&](int st) { return kcg::ck_config_error(dt, bn, bk, st, split) == 0; };
+    int st = (opts && opts->num_stages > 0) ? opts->num_stages : 2;
+    if (!(opts && opts->num_stages > 0)) {
+      while (st < 8 && !ok(st)) ++st;                                   // the ring must hold the received slices
+      if (c[KCG_CFG_SHARED_PREFETCH]) while (st < 8 && ok(st + 1)) ++st;  // then as deep as fits
+    }
+    if (!ok(st))
+      return fail(KCG_E_BAD_CONFIG,
+                  "tile 128x%dx%d / %d stages / LOCAL_SPLIT_U %d not buildable by the cluster split-K kernel (rule %d: "
+                  "fp16 / bf16, split 2, 4 or 8, BLOCK_SIZE_N a multiple of 32 * split, ring >= 512 * BLOCK_SIZE_N bytes)",
+                  bn, bk, st, split, kcg::ck_config_error(dt, bn, bk, st, split));
     if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
     r->stages = st;
   } else if (want == KCG_KERNEL_SIMT) {
@@ -320,6 +400,7 @@ std::string kernel_name(const Cfg& c, const Resolved& r) {
   ss << "LC" << c[KCG_CFG_LOAD_CONTINUOUS] << "_";
   ss << "RC" << c[KCG_CFG_REDUCE_C_CONTINUOUS] << "_";
   ss << "ST" << r.stages << "_V" << r.kernel;
+  if (r.btrans) ss << "_BT1";
   return ss.str();
 }
 
@@ -463,8 +544,11 @@ std::vector<std::string> macro_flags(const Cfg& c, const Resolved& r, const std:
     D("GLWB", pos(c[KCG_CFG_GLOB_LOAD_WIDTH_B]));
     D("GSW", pos(c[KCG_CFG_GLOB_STORE_WIDTH]));
     D("SHMP", c[KCG_CFG_SHARED_PREFETCH] ? 1 : 0);
-    D("REGP", c[KCG_CFG_REG_PREFETCH] ? 1 : 0);
   }
+  // SIMT: register double buffer of the fragments; single-pass tcgen05 kernels: overlap of the
+  // accumulator drain with the next tile's main loop
+  D("REGP", c[KCG_CFG_REG_PREFETCH] ? 1 : 0);
+  D("BTRANS", r.btrans);
   return f;
 }
 
@@ -520,6 +604,11 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
     out->cluster[0] = 2;
     out->block[0] = f32 ? 512 : 256;
     out->smem_bytes = kcg::tc_smem_bytes(c[KCG_CFG_DATATYPE_A], bm / 2, bn / 2, bk, r.stages, f32);
+  } else if (r.kernel == KCG_KERNEL_TCGEN05_CLUSTERK) {
+    out->grid[0] = tiles * lsu;  // one cluster of LOCAL_SPLIT_U CTAs per tile
+    out->cluster[0] = lsu;
+    out->block[0] = 192;  // producer, MMA, four epilogue warps
+    out->smem_bytes = kcg::ck_smem_bytes(bn, bk, r.stages);
   } else if (r.kernel == KCG_KERNEL_SIMT) {
     // grid/block as the reference derives them (Optimizer.cc:20,336; Rewriter.cc:726-761)
     out->grid[0] = tiles;
@@ -550,6 +639,7 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
   out->n = N;
   out->k = K;
   out->reserved[0] = r.num_sms;
+  out->reserved[1] = r.btrans;
   return 0;
 }
 
@@ -559,13 +649,10 @@ int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64
   snprintf(key, sizeof(key), "%d:%llx:%llu:%llu:%llu:%d:%d:%d", dtype, (unsigned long long)ptr,
            (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_bytes, box_inner,
            box_outer, swizzle);
-  {
-    std::lock_guard<std::mutex> g(g_dev_mutex);
-    auto it = s->tmaps.find(key);
-    if (it != s->tmaps.end()) {
-      *out = it->second;
-      return 0;
-    }
+  auto it = s->tmaps.find(key);  // the caller holds g_dev_mutex
+  if (it != s->tmaps.end()) {
+    *out = it->second;
+    return 0;
   }
   const CUtensorMapDataType dt = dtype == KCG_DTYPE_FLOAT32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : dtype == KCG_DTYPE_FLOAT16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -580,7 +667,6 @@ int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64
   DRV(cuTensorMapEncodeTiled(out, dt, 2, reinterpret_cast<void*>(ptr), gdim, gstride, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, static_cast<CUtensorMapSwizzle>(swizzle),
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
-  std::lock_guard<std::mutex> g(g_dev_mutex);
   if (s->tmaps.size() > 4096) s->tmaps.clear();
   s->tmaps[key] = *out;
   return 0;
@@ -871,8 +957,12 @@ int kcg_peer_free(int device, uint64_t dptr) {
   return 0;
 }
 
+struct LeadingDims {
+  int64_t lda = 0, ldb = 0, ldc = 0;  // elements between rows as stored; 0 = contiguous
+};
 static int launch_impl(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
-                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch);
+                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch,
+                       const LeadingDims& ld = LeadingDims());
 
 int kcg_launch_gemm_allgather(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
                               uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers) {
@@ -885,13 +975,26 @@ int kcg_launch_gemm_batched(uint64_t function, const kcg_kernel_info* info, int 
   return launch_impl(function, info, device, stream, A, B, C, epi, nullptr, 0, batch);
 }
 
+int kcg_launch_gemm_strided(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
+                            uint64_t B, uint64_t C, int64_t lda, int64_t ldb, int64_t ldc, int batch,
+                            const kcg_epilogue* epi) {
+  if (batch < 1) return fail(KCG_E_BAD_ARG, "batch must be at least 1");
+  if (lda < 0 || ldb < 0 || ldc < 0) return fail(KCG_E_BAD_ARG, "leading dimensions must not be negative");
+  LeadingDims ld;
+  ld.lda = lda;
+  ld.ldb = ldb;
+  ld.ldc = ldc;
+  return launch_impl(function, info, device, stream, A, B, C, epi, nullptr, 0, batch, ld);
+}
+
 static int launch_impl(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream, uint64_t A,
-                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch) {
+                       uint64_t B, uint64_t C, const kcg_epilogue* epi, const uint64_t* peer_c, int n_peers, int batch,
+                       const LeadingDims& ld) {
   if (!function || !info || !A || !B || !C) return fail(KCG_E_BAD_ARG, "null argument");
   if (batch > 1) {
     const bool tc = info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TCGEN05_PAIR ||
-                    info->kernel == KCG_KERNEL_TF32X1;
-    if (!tc) return fail(KCG_E_BAD_CONFIG, "batched launches need a tcgen05 kernel (KERNEL_VARIANT 2, 3 or 4)");
+                    info->kernel == KCG_KERNEL_TF32X1 || info->kernel == KCG_KERNEL_TCGEN05_CLUSTERK;
+    if (!tc) return fail(KCG_E_BAD_CONFIG, "batched launches need a tcgen05 kernel (KERNEL_VARIANT 2, 3, 4 or 5)");
     if (static_cast<int64_t>(info->m) * batch > 0x7fffffff || static_cast<int64_t>(info->k) * batch > 0x7fffffff)
       return fail(KCG_E_TOO_LARGE, "batch * M and batch * K must fit 31 bits");
   }
@@ -910,6 +1013,11 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   if (epi && info->kernel == KCG_KERNEL_WAIT_PROBE) return fail(KCG_E_BAD_ARG, "the wait probe has no epilogue");
   DeviceState* s = nullptr;
   if (int e = ensure_device(device, &s)) return e;
+  // Held up to the launch: the stream's slot (status, workspace, counters) and the tensor-map
+  // cache must not move under a launch another thread is putting together.
+  std::lock_guard<std::mutex> guard(g_dev_mutex);
+  StreamSlot* slot = nullptr;
+  if (int e = slot_for(s, reinterpret_cast<CUstream>(stream), true, &slot)) return e;
   KcgGemmParams p;
   memset(&p, 0, sizeof(p));
   // A batched product runs as one tall problem: M counts the rows of all batches
@@ -922,10 +1030,25 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   p.N = N;
   p.K = K;
   p.batch_rows = batch > 1 ? Mb : 0;
-  p.lda = info->atrans ? Mb : K;
-  p.ldb = N;
-  p.ldc = N;
-  p.status = reinterpret_cast<unsigned int*>(s->status);
+  // Rows as stored: A is M x K (K x M when IS_ATRANS), B is K x N (N x K when compiled with b_trans),
+  // C is M x N. A leading dimension larger than the row length addresses a sub-matrix of a wider
+  // array; in a batched launch the batches still follow one another row after row at that pitch.
+  const int btrans = info->reserved[1] ? 1 : 0;
+  const int64_t row_a = info->atrans ? Mb : K, row_b = btrans ? K : N, row_c = N;
+  const int64_t lda = ld.lda ? ld.lda : row_a, ldb = ld.ldb ? ld.ldb : row_b, ldc = ld.ldc ? ld.ldc : row_c;
+  if (lda < row_a || ldb < row_b || ldc < row_c)
+    return fail(KCG_E_BAD_ARG, "leading dimensions %lld, %lld, %lld are below the row lengths %lld, %lld, %lld",
+                (long long)lda, (long long)ldb, (long long)ldc, (long long)row_a, (long long)row_b, (long long)row_c);
+  if (lda > 0x7fffffff || ldb > 0x7fffffff || ldc > 0x7fffffff)
+    return fail(KCG_E_TOO_LARGE, "leading dimensions must fit 31 bits");
+  if ((lda * eb) % 16 || (ldb * eb) % 16 || (ldc * eb) % 16)
+    return fail(KCG_E_BAD_ARG, "leading dimensions must keep every row 16-byte aligned");
+  if ((ld.lda || ld.ldb || ld.ldc) && n_peers > 0)
+    return fail(KCG_E_BAD_ARG, "the fused all-gather takes contiguous operands");
+  p.lda = static_cast<int>(lda);
+  p.ldb = static_cast<int>(ldb);
+  p.ldc = static_cast<int>(ldc);
+  p.status = reinterpret_cast<unsigned int*>(slot->status);
   p.split_first_tile = (M / (info->bm > 0 ? info->bm : 1)) * (N / (info->bn > 0 ? info->bn : 1));
   p.split_factor = 1;
   p.alpha = 1.f;
@@ -940,28 +1063,41 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   for (int i = 0; i < n_peers; ++i) p.peerC[i] = reinterpret_cast<void*>(peer_c[i]);
   int grid0 = info->grid[0];
   const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
-  if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 || pair) {
-    // the pair kernel loads per-CTA slices: BM/2 rows of A, BN/2 columns of B
-    const kcg::TcLayout L = pair ? kcg::make_tc_layout(info->dtype, info->bm / 2, info->bn / 2, info->bk, info->atrans)
-                                 : kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans);
+  // Tensor maps of A and B for a tcgen05 kernel whose per-CTA operand slices have layout L.
+  auto encode_operands = [&](const kcg::TcLayout& L) -> int {
     if (info->atrans) {
       // K x M storage: the batches' matrices lie one under the other, K rows each
       if (int e = encode_map(s, &p.tmA, info->dtype, A, Mb, static_cast<uint64_t>(K) * batch,
-                             static_cast<uint64_t>(Mb) * eb, L.a_box_inner, L.a_box_outer, L.a_tma_swizzle))
+                             static_cast<uint64_t>(lda) * eb, L.a_box_inner, L.a_box_outer, L.a_tma_swizzle))
         return e;
     } else {
-      if (int e = encode_map(s, &p.tmA, info->dtype, A, K, M, static_cast<uint64_t>(K) * eb, L.a_box_inner,
+      if (int e = encode_map(s, &p.tmA, info->dtype, A, K, M, static_cast<uint64_t>(lda) * eb, L.a_box_inner,
                              L.a_box_outer, L.a_tma_swizzle))
         return e;
     }
-    if (int e = encode_map(s, &p.tmB, info->dtype, B, N, static_cast<uint64_t>(K) * batch,
-                           static_cast<uint64_t>(N) * eb, L.b_box_inner, L.b_box_outer, L.b_tma_swizzle))
+    if (btrans)  // N x K storage: the batches' matrices lie one under the other, N rows each
+      return encode_map(s, &p.tmB, info->dtype, B, K, static_cast<uint64_t>(N) * batch,
+                        static_cast<uint64_t>(ldb) * eb, L.b_box_inner, L.b_box_outer, L.b_tma_swizzle);
+    return encode_map(s, &p.tmB, info->dtype, B, N, static_cast<uint64_t>(K) * batch, static_cast<uint64_t>(ldb) * eb,
+                      L.b_box_inner, L.b_box_outer, L.b_tma_swizzle);
+  };
+  if (info->kernel == KCG_KERNEL_TCGEN05_CLUSTERK) {
+    // One cluster per tile; the K split and its reduction stay inside the cluster (no workspace).
+    if (int e = encode_operands(kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans))) return e;
+    grid0 = (M / info->bm) * (N / info->bn) * info->splitk;
+  }
+  if (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TF32X1 || pair) {
+    // the pair kernel loads per-CTA slices: BM/2 rows of A, BN/2 columns of B
+    if (int e = encode_operands(pair ? kcg::make_tc_layout(info->dtype, info->bm / 2, info->bn / 2, info->bk,
+                                                           info->atrans, btrans)
+                                     : kcg::make_tc_layout(info->dtype, info->bm, info->bn, info->bk, info->atrans,
+                                                           btrans)))
       return e;
     // The single-pass kernel writes C with TMA stores of 32-row x 128-byte boxes taken from
     // 128B-swizzled staging buffers; the 3xTF32 kernel stores from registers.
     const bool x3 = eb == 4 && info->kernel != KCG_KERNEL_TF32X1;
     if (!x3) {
-      if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(N) * eb, 128 / eb, 32,
+      if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(ldc) * eb, 128 / eb, 32,
                              3 /*CU_TENSOR_MAP_SWIZZLE_128B*/))
         return e;
     }
@@ -969,35 +1105,41 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
     const int T = plan.tiles, first = plan.first, factor = plan.factor, sk_per = plan.sk_per,
               sk_ranges = plan.sk_ranges, G = plan.units_at_once;
     const bool ws_epilogue = x3 && p.epi_flags != 0u;
-    const int units = sk_per > 0 ? sk_ranges : first + (T - first) * factor;
+    // Under stream-K the whole tiles before the tail are walked with the grid as stride: the grid
+    // stays at every unit that runs at once even when the tail is cut into fewer ranges (the CTAs
+    // beyond the last range then simply have no tail piece).
+    const int units = sk_per > 0 ? (first > 0 ? G : sk_ranges) : first + (T - first) * factor;
     grid0 = (units < G ? units : G) * (pair ? 2 : 1);
     p.split_first_tile = first;
     p.split_factor = factor;
     p.sk_per = sk_per;
     if (factor > 1 || ws_epilogue || sk_per > 0) {
-      std::lock_guard<std::mutex> g(g_dev_mutex);
       // slots: one per (tile, split) of an even split; range index + tile index under stream-K
       const size_t slots = sk_per > 0 ? static_cast<size_t>(sk_ranges) + (T - first)
                                       : static_cast<size_t>(T - first) * factor;
       const size_t need = slots * info->bm * info->bn * sizeof(float);
-      if (int e = grow(&s->ws, &s->ws_bytes, need)) return e;
-      const size_t tiles = static_cast<size_t>(T - first) * (pair ? 2 : 1);  // one counter per CTA half
-      if (s->counters_n < tiles) {
-        size_t have = s->counters_n * 4;
-        if (int e = grow(&s->counters, &have, tiles * 4)) return e;
-        s->counters_n = tiles;
-        DRV(cuMemsetD32(s->counters, 0, tiles));
+      if (slot->ws_bytes < need) {
+        s->tmaps.clear();  // drops the maps of the workspace that is about to move
+        if (int e = grow(&slot->ws, &slot->ws_bytes, need)) return e;
       }
-      p.splitk_ws = reinterpret_cast<float*>(s->ws);
-      p.tile_counters = reinterpret_cast<unsigned int*>(s->counters);
+      const size_t tiles = static_cast<size_t>(T - first) * (pair ? 2 : 1);  // one counter per CTA half
+      if (slot->counters_n < tiles) {
+        size_t have = slot->counters_n * 4;
+        slot->counters_n = 0;
+        if (int e = grow(&slot->counters, &have, tiles * 4)) return e;
+        slot->counters_n = tiles;
+        DRV(cuMemsetD32(slot->counters, 0, tiles));
+      }
+      p.splitk_ws = reinterpret_cast<float*>(slot->ws);
+      p.tile_counters = reinterpret_cast<unsigned int*>(slot->counters);
     }
     if (!x3 && (factor > 1 || sk_per > 0)) {
       // The single-pass kernel writes its partial tiles with TMA stores: the workspace as one tall
       // fp32 matrix of BN columns (every row the buffer holds, so that the map is reused while the
       // buffer is), 32 x 32 boxes with the 128B swizzle of the staging buffers.
       const uint64_t row_bytes = static_cast<uint64_t>(info->bn) * 4;
-      if (int e = encode_map(s, &p.tmWs, KCG_DTYPE_FLOAT32, static_cast<uint64_t>(s->ws), info->bn,
-                             s->ws_bytes / row_bytes, row_bytes, 32, 32, 3))
+      if (int e = encode_map(s, &p.tmWs, KCG_DTYPE_FLOAT32, static_cast<uint64_t>(slot->ws), info->bn,
+                             slot->ws_bytes / row_bytes, row_bytes, 32, 32, 3))
         return e;
     }
   }
@@ -1027,21 +1169,31 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   return 0;
 }
 
-int kcg_check_status(int device, uint64_t stream) {
-  DeviceState* s = nullptr;
-  if (int e = ensure_device(device, &s)) return e;
-  DRV(cuStreamSynchronize(reinterpret_cast<CUstream>(stream)));
+// Reads (and clears) the status block of a stream's slot after synchronising the stream.
+// Call with g_dev_mutex held.
+static int read_status(StreamSlot* sl) {
   unsigned int st[4] = {0, 0, 0, 0};
-  DRV(cuMemcpyDtoH(st, s->status, sizeof(st)));
+  DRV(cuMemcpyDtoH(st, sl->status, sizeof(st)));
   if (st[0] != 0) {
-    DRV(cuMemsetD32(s->status, 0, 4));
+    DRV(cuMemsetD32(sl->status, 0, 4));
     // a timed-out split-K launch may leave counters mid-count
-    if (s->counters) DRV(cuMemsetD32(s->counters, 0, s->counters_n));
+    if (sl->counters) DRV(cuMemsetD32(sl->counters, 0, sl->counters_n));
     static const char* role[] = {"", "TMA producer", "MMA issuer", "epilogue", "splitter", "shape", "push warp"};
     return fail(KCG_E_DEVICE_TIMEOUT, "kernel gave up in a bounded wait: role %s (code %u), block %u, detail %u/%u",
                 st[0] < 7 ? role[st[0]] : "?", st[0], st[1], st[2], st[3]);
   }
   return 0;
+}
+
+int kcg_check_status(int device, uint64_t stream) {
+  DeviceState* s = nullptr;
+  if (int e = ensure_device(device, &s)) return e;
+  DRV(cuStreamSynchronize(reinterpret_cast<CUstream>(stream)));
+  std::lock_guard<std::mutex> guard(g_dev_mutex);
+  StreamSlot* sl = nullptr;
+  if (int e = slot_for(s, reinterpret_cast<CUstream>(stream), false, &sl)) return e;
+  if (!sl) return 0;  // nothing was ever launched on this stream
+  return read_status(sl);
 }
 
 int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
@@ -1074,13 +1226,25 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
     if (want > 16) want = 16;
     nslabs = tiles_m < static_cast<int>(want) ? tiles_m : static_cast<int>(want);
   }
+  // The kernels report an expired wait to the status block of the stream they ran on.
+  auto kernel_status = [&](CUstream ran_on) -> int {
+    std::lock_guard<std::mutex> g(g_dev_mutex);
+    StreamSlot* sl = nullptr;
+    if (int e = slot_for(s, ran_on, false, &sl)) return e;
+    return sl ? read_status(sl) : 0;
+  };
   if (nslabs == 1) {
     DRV(cuMemcpyHtoDAsync(s->hbuf[0], hostA, bytes[0], st));
     DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], st));
-    if (int e = kcg_launch_gemm(function, info, device, stream, s->hbuf[0], s->hbuf[1], s->hbuf[2])) return e;
-    DRV(cuMemcpyDtoHAsync(hostC, s->hbuf[2], bytes[2], st));
-    DRV(cuStreamSynchronize(st));
-    return 0;
+    int rc = kcg_launch_gemm(function, info, device, stream, s->hbuf[0], s->hbuf[1], s->hbuf[2]);
+    if (rc == 0) {
+      const CUresult r = driver().p_cuMemcpyDtoHAsync(hostC, s->hbuf[2], bytes[2], st);
+      if (r != CUDA_SUCCESS) rc = drv_fail(r, "cuMemcpyDtoHAsync");
+    }
+    // also on an error path: nothing of this call is left in flight on the caller's buffers
+    const CUresult rs = driver().p_cuStreamSynchronize(st);
+    if (rc == 0 && rs != CUDA_SUCCESS) rc = drv_fail(rs, "cuStreamSynchronize");
+    return rc ? rc : kernel_status(st);
   }
   {
     std::lock_guard<std::mutex> g(g_dev_mutex);
@@ -1094,34 +1258,52 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
   }
   CUstream s_in = s->hstream[0], s_exec = s->hstream[1], s_out = s->hstream[2];
   CUevent ev_begin = s->hevents[2 * nslabs], ev_end = s->hevents[2 * nslabs + 1];
-  DRV(cuEventRecord(ev_begin, st));  // work already queued on the caller's stream comes first
-  DRV(cuStreamWaitEvent(s_in, ev_begin, 0));
-  DRV(cuStreamWaitEvent(s_exec, ev_begin, 0));
-  DRV(cuStreamWaitEvent(s_out, ev_begin, 0));
-  DRV(cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], s_in));
+  // Every step of the pipeline runs through `step`; after the first failure the rest is skipped
+  // and the three internal streams are drained before the error is returned, so that no copy or
+  // kernel of this call still touches the caller's buffers (or the library's) afterwards.
+  int rc = 0;
+  auto step = [&](CUresult r, const char* what) {
+    if (rc == 0 && r != CUDA_SUCCESS) rc = drv_fail(r, what);
+    return rc == 0;
+  };
+  Driver& d = driver();
+  step(d.p_cuEventRecord(ev_begin, st), "cuEventRecord");  // work already queued on the caller's stream comes first
+  if (rc == 0) step(d.p_cuStreamWaitEvent(s_in, ev_begin, 0), "cuStreamWaitEvent");
+  if (rc == 0) step(d.p_cuStreamWaitEvent(s_exec, ev_begin, 0), "cuStreamWaitEvent");
+  if (rc == 0) step(d.p_cuStreamWaitEvent(s_out, ev_begin, 0), "cuStreamWaitEvent");
+  if (rc == 0) step(d.p_cuMemcpyHtoDAsync(s->hbuf[1], hostB, bytes[1], s_in), "cuMemcpyHtoDAsync(B)");
   const int base_tiles = tiles_m / nslabs, extra = tiles_m % nslabs;
   size_t row0 = 0;
-  for (int i = 0; i < nslabs; ++i) {
+  for (int i = 0; i < nslabs && rc == 0; ++i) {
     const size_t rows = static_cast<size_t>(base_tiles + (i < extra ? 1 : 0)) * bm;
     const size_t a_off = row0 * info->k * eb, c_off = row0 * info->n * eb;
-    DRV(cuMemcpyHtoDAsync(s->hbuf[0] + a_off, static_cast<const char*>(hostA) + a_off, rows * info->k * eb, s_in));
-    DRV(cuEventRecord(s->hevents[2 * i], s_in));
-    DRV(cuStreamWaitEvent(s_exec, s->hevents[2 * i], 0));
+    if (!step(d.p_cuMemcpyHtoDAsync(s->hbuf[0] + a_off, static_cast<const char*>(hostA) + a_off, rows * info->k * eb,
+                                    s_in), "cuMemcpyHtoDAsync(A)"))
+      break;
+    if (!step(d.p_cuEventRecord(s->hevents[2 * i], s_in), "cuEventRecord")) break;
+    if (!step(d.p_cuStreamWaitEvent(s_exec, s->hevents[2 * i], 0), "cuStreamWaitEvent")) break;
     kcg_kernel_info slab = *info;  // same cubin: the kernels take M from the launch parameters
     slab.m = static_cast<int32_t>(rows);
-    if (int e = kcg_launch_gemm(function, &slab, device, reinterpret_cast<uint64_t>(s_exec), s->hbuf[0] + a_off,
-                                s->hbuf[1], s->hbuf[2] + c_off))
-      return e;
-    DRV(cuEventRecord(s->hevents[2 * i + 1], s_exec));
-    DRV(cuStreamWaitEvent(s_out, s->hevents[2 * i + 1], 0));
-    DRV(cuMemcpyDtoHAsync(static_cast<char*>(hostC) + c_off, s->hbuf[2] + c_off, rows * info->n * eb, s_out));
+    rc = kcg_launch_gemm(function, &slab, device, reinterpret_cast<uint64_t>(s_exec), s->hbuf[0] + a_off, s->hbuf[1],
+                         s->hbuf[2] + c_off);
+    if (rc != 0) break;
+    if (!step(d.p_cuEventRecord(s->hevents[2 * i + 1], s_exec), "cuEventRecord")) break;
+    if (!step(d.p_cuStreamWaitEvent(s_out, s->hevents[2 * i + 1], 0), "cuStreamWaitEvent")) break;
+    if (!step(d.p_cuMemcpyDtoHAsync(static_cast<char*>(hostC) + c_off, s->hbuf[2] + c_off, rows * info->n * eb, s_out),
+              "cuMemcpyDtoHAsync(C)"))
+      break;
     row0 += rows;
   }
-  DRV(cuEventRecord(ev_end, s_out));
-  DRV(cuStreamWaitEvent(st, ev_end, 0));
-  DRV(cuStreamSynchronize(s_out));
-  DRV(cuStreamSynchronize(st));
-  return 0;
+  if (rc == 0) step(d.p_cuEventRecord(ev_end, s_out), "cuEventRecord");
+  if (rc == 0) step(d.p_cuStreamWaitEvent(st, ev_end, 0), "cuStreamWaitEvent");
+  // drain (also after a failure)
+  const CUresult r_in = d.p_cuStreamSynchronize(s_in), r_exec = d.p_cuStreamSynchronize(s_exec),
+                 r_out = d.p_cuStreamSynchronize(s_out), r_st = d.p_cuStreamSynchronize(st);
+  step(r_in, "cuStreamSynchronize");
+  step(r_exec, "cuStreamSynchronize");
+  step(r_out, "cuStreamSynchronize");
+  step(r_st, "cuStreamSynchronize");
+  return rc ? rc : kernel_status(s_exec);
 }
 
 int kcg_shutdown(void) {
@@ -1132,9 +1314,11 @@ int kcg_shutdown(void) {
     DeviceState& s = g_dev[i];
     if (!s.init) continue;
     d.p_cuCtxSetCurrent(s.ctx);
-    if (s.status) d.p_cuMemFree(s.status);
-    if (s.ws) d.p_cuMemFree(s.ws);
-    if (s.counters) d.p_cuMemFree(s.counters);
+    for (StreamSlot& sl : s.slots) {
+      if (sl.status) d.p_cuMemFree(sl.status);
+      if (sl.ws) d.p_cuMemFree(sl.ws);
+      if (sl.counters) d.p_cuMemFree(sl.counters);
+    }
     for (int j = 0; j < 3; ++j) {
       if (s.hbuf[j]) d.p_cuMemFree(s.hbuf[j]);
       if (s.hstream[j]) d.p_cuStreamDestroy(s.hstream[j]);

@@ -14,6 +14,17 @@
 #error "KCG_VARIANT must be defined"
 #endif
 
+// REG_PREFETCH of the tuning config: overlap of the accumulator drain with the next tile's main
+// loop in the single-pass tcgen05 kernels (gemm_tcgen05.cuh); on unless the config turns it off.
+#ifndef KCG_REGP
+#define KCG_REGP 1
+#endif
+#define KCG_ACC_OVERLAP (KCG_REGP ? 1 : 0)
+// B stored N x K row-major (single-pass tcgen05 kernels, 16-bit types)
+#ifndef KCG_BTRANS
+#define KCG_BTRANS 0
+#endif
+
 #if KCG_DTYPE == KCG_DT_F32
 #define KCG_T float
 #elif KCG_DTYPE == KCG_DT_F16
@@ -36,7 +47,7 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 }
 #elif KCG_VARIANT == KCG_VARIANT_TCGEN05 || KCG_VARIANT == KCG_VARIANT_TF32X1
 #include "gemm_tcgen05.cuh"
-using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP>;
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 0, KCG_ACC_OVERLAP, KCG_BTRANS>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);
@@ -53,7 +64,14 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 }
 #elif KCG_VARIANT == KCG_VARIANT_TCGEN05_PAIR
 #include "gemm_tcgen05.cuh"
-using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 1>;
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 1, KCG_ACC_OVERLAP, KCG_BTRANS>;
+extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
+KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
+  Gemm::run(p);
+}
+#elif KCG_VARIANT == KCG_VARIANT_TCGEN05_CLUSTERK
+#include "gemm_tcgen05_clusterk.cuh"
+using Gemm = kcg::TcGemmClusterK<KCG_DTYPE, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);

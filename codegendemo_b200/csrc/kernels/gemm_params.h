@@ -22,6 +22,9 @@
 #define KCG_VARIANT_TF32X1 3   // tcgen05 single-pass TF32 (fp32 in, reduced accuracy; comparison only)
 
 #define KCG_VARIANT_TCGEN05_PAIR 4  // tcgen05 cta_group::2 on clusters of two CTAs (fp16 / bf16)
+// K split over a thread-block cluster of LOCAL_SPLIT_U CTAs, partial tiles reduced through
+// distributed shared memory (fp16 / bf16, 128-row tiles): no workspace, no counters
+#define KCG_VARIANT_TCGEN05_CLUSTERK 5
 
 #define KCG_MAX_PEERS 7  // other GPUs of one NVSwitch domain of eight
 
@@ -110,7 +113,9 @@ struct TcLayout {
   int stage_hi_bytes;  // one copy of A+B
 };
 
-constexpr TcLayout make_tc_layout(int dtype, int BM, int BN, int BK, int atrans) {
+// `btrans` = B is stored N x K row-major (the "NT" product C = A * Bt^T): its tile is then a K-major
+// operand laid out exactly like a K-major A tile; 16-bit types only.
+constexpr TcLayout make_tc_layout(int dtype, int BM, int BN, int BK, int atrans, int btrans = 0) {
   TcLayout L{};
   L.eb = (dtype == KCG_DT_F32) ? 4 : 2;
   L.umma_k = 32 / L.eb;
@@ -151,6 +156,17 @@ constexpr TcLayout make_tc_layout(int dtype, int BM, int BN, int BK, int atrans)
   L.b_desc_swizzle = mn_desc;
   L.b_lbo = BK * 128;
   L.b_sbo = mn_sbo;
+  if (btrans) {
+    const int swb = kc_min(128, BK * L.eb);
+    L.b_box_inner = swb / L.eb;
+    L.b_box_outer = BN;
+    L.b_boxes = (BK * L.eb) / swb;
+    L.b_box_bytes = BN * swb;
+    L.b_tma_swizzle = (swb == 128) ? 3 : (swb == 64) ? 2 : 1;
+    L.b_desc_swizzle = (swb == 128) ? 2 : (swb == 64) ? 4 : 6;
+    L.b_lbo = 16;
+    L.b_sbo = 8 * swb;
+  }
   L.stage_hi_bytes = L.a_bytes + L.b_bytes;
   return L;
 }
@@ -195,6 +211,23 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
   if (tc_ring_bytes(dtype, BM, BN, BK, stages, x3) + 2048 + tc_staging_bytes(dtype, x3) > 227 * 1024) return 8;
   return 0;
 }
+
+// Cluster split-K kernel (gemm_tcgen05_clusterk.cuh): a 128 x BN tile per cluster of `split` CTAs.
+// The operand ring doubles as the buffer that receives the cluster's fp32 partial slices
+// (128 x BN x 4 bytes), so the ring must be at least that large; no TMA-store staging.
+constexpr int ck_config_error(int dtype, int BN, int BK, int stages, int split) {
+  if (!(dtype == KCG_DT_F16 || dtype == KCG_DT_BF16)) return 1;
+  if (!(split == 2 || split == 4 || split == 8)) return 2;
+  if (BN < 64 || BN > 256 || (BN % 64) != 0 || (BN % (32 * split)) != 0) return 3;
+  const int rowb = BK * 2;
+  if (!(rowb == 32 || rowb == 64 || (rowb % 128) == 0) || rowb > 512 || (BK % 16) != 0) return 5;
+  if (stages < 2 || stages > 12) return 7;
+  const int ring = (128 + BN) * BK * 2 * stages;
+  if (ring + 2048 > 227 * 1024) return 8;
+  if (ring < 128 * BN * 4) return 10;
+  return 0;
+}
+constexpr int ck_smem_bytes(int BN, int BK, int stages) { return (128 + BN) * BK * 2 * stages + 2048; }
 
 constexpr int tc_smem_bytes(int dtype, int BM, int BN, int BK, int stages, int x3) {
   // +1024 alignment slack, +1024 barriers / TMEM holder / flags, + epilogue staging

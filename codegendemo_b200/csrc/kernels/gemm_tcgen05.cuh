@@ -48,21 +48,35 @@ namespace kcg {
 // barrier; stages are freed and accumulators published in both CTAs with one
 // tcgen05.commit per CTA; the peer's epilogue warps release TMEM with a remote arrive. No
 // TMA multicast is used: every load has one destination CTA.
+//
+// kAccOverlap (REG_PREFETCH; the reference's register double buffer, Optimizer.cc:438-447, whose
+// purpose is to overlap the drain of one result with the compute of the next) = 1 overlaps the
+// epilogue of tile i with the main loop of tile i + 1: through two TMEM accumulator buffers when
+// two fit the 512 columns; for the two-accumulator tile that fills all of TMEM (256 rows x 256
+// columns per CTA) by releasing the accumulator in halves - the MMA warp runs the first K blocks
+// of the next tile into half 0 while the epilogue still drains half 1. 0 = one buffer, released whole.
+//
+// kBTrans = 1: B is stored N x K row-major (C = A * Bt^T, the "NT" product: Q * K^T of attention
+// without a transposed copy of K); the B tile is then a K-major operand like a K-major A tile.
 template <int kDType, int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK,
-          int kGroup, int kPair = 0>
+          int kGroup, int kPair = 0, int kAccOverlap = 1, int kBTrans = 0>
 struct TcGemm {
   static constexpr int NCTA = kPair ? 2 : 1;
   static constexpr int R = kBM / NCTA;    // rows of the tile held by one CTA
   static constexpr int BNL = kBN / NCTA;  // B columns loaded by one CTA
   static_assert(tc_config_error(kDType, R, BNL, kBK, kStages, 0) == 0,
                 "config not buildable by the tcgen05 kernel");
-  static constexpr TcLayout L = make_tc_layout(kDType, R, BNL, kBK, kATrans);
+  static constexpr TcLayout L = make_tc_layout(kDType, R, BNL, kBK, kATrans, kBTrans);
   static constexpr int EB = L.eb;
   static constexpr bool kTf32 = (EB == 4);
+  static_assert(!(kBTrans && kTf32), "an N x K stored B is supported for 16-bit types only");
   static constexpr int UMMA_K = L.umma_k;
   static constexpr int MT = R / 128;
   static constexpr int ACC_COLS = MT * kBN;
-  static constexpr int NACC = (2 * ACC_COLS <= 512) ? 2 : 1;
+  static constexpr int NACC = (kAccOverlap && 2 * ACC_COLS <= 512) ? 2 : 1;
+  // one buffer of two accumulators, released half by half (tmem_empty[t] = accumulator t is drained)
+  static constexpr bool HALF = kAccOverlap && NACC == 1 && MT == 2;
+  static constexpr int HALF_KB = kStages - 1;  // K blocks run into half 0 ahead of half 1
   static constexpr int TMEM_COLS = kc_pow2_ceil(NACC * ACC_COLS);
   static constexpr int STAGE_HI = L.stage_hi_bytes;
   static constexpr int STAGE_BYTES = STAGE_HI;
@@ -78,7 +92,8 @@ struct TcGemm {
   static constexpr uint32_t FMT = (kDType == KCG_DT_F32)    ? FMT_TF32
                                   : (kDType == KCG_DT_BF16) ? FMT_BF16
                                                             : FMT_F16;
-  static constexpr uint32_t IDESC = make_instr_desc(FMT, kATrans ? 1u : 0u, 1u, kPair ? 256u : 128u, kBN);
+  static constexpr uint32_t IDESC =
+      make_instr_desc(FMT, kATrans ? 1u : 0u, kBTrans ? 0u : 1u, kPair ? 256u : 128u, kBN);
 
   struct Barriers {
     uint64_t full[kStages];
@@ -193,8 +208,14 @@ struct TcGemm {
                 }
               }
 #pragma unroll
-              for (int j = 0; j < L.b_boxes; ++j)
-                tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, kb_row);
+              for (int j = 0; j < L.b_boxes; ++j) {
+                if constexpr (kBTrans) {  // N x K storage: the batch selects N rows
+                  tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, k0 + j * L.b_box_inner,
+                                   bn0 + w.nofs);
+                } else {
+                  tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, kb_row);
+                }
+              }
             } else {
               mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
 #pragma unroll
@@ -206,8 +227,13 @@ struct TcGemm {
                 }
               }
 #pragma unroll
-              for (int j = 0; j < L.b_boxes; ++j)
-                tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, kb_row);
+              for (int j = 0; j < L.b_boxes; ++j) {
+                if constexpr (kBTrans) {
+                  tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], k0 + j * L.b_box_inner, bn0 + w.nofs);
+                } else {
+                  tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, kb_row);
+                }
+              }
             }
           }
         }
@@ -219,6 +245,53 @@ struct TcGemm {
         bool ok = true;
         Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
         Unit w;
+        // The MMAs of K block (it, kb) of the unit; accumulators [t0, t1) only.
+        auto issue = [&](uint32_t s, int kb, int t0, int t1, uint32_t tmem_acc) {
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + L.a_bytes;
+#pragma unroll
+          for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t a_off, b_off;
+            if constexpr (kATrans) {
+              a_off = ks * UMMA_K * 128;
+            } else {
+              constexpr int swb = (kBK * EB < 128) ? kBK * EB : 128;
+              a_off = ((ks * 32) / swb) * L.a_box_bytes + ((ks * 32) % swb);
+            }
+            if constexpr (kBTrans) {
+              constexpr int swb = (kBK * EB < 128) ? kBK * EB : 128;
+              b_off = ((ks * 32) / swb) * L.b_box_bytes + ((ks * 32) % swb);
+            } else {
+              b_off = ks * UMMA_K * 128;
+            }
+            const uint32_t acc_flag = (kb > 0 || ks > 0) ? 1u : 0u;
+            for (int t = t0; t < t1; ++t) {
+              // second accumulator: local A rows 128..255. Two accumulators also keep
+              // consecutive MMAs independent of each other, which the tensor pipe needs to
+              // stay full (a single accumulator chain measured ~10 % slower).
+              const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
+                                           : t * 128 * (L.a_box_bytes / R);
+              const uint64_t bdesc = make_smem_desc(sb + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
+              const uint64_t adesc =
+                  make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
+              const uint32_t d = tmem_acc + t * kBN;
+              if constexpr (kPair) {
+                umma_ss_pair<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
+              } else {
+                umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
+              }
+            }
+          }
+        };
+        // stage reusable (in both CTAs of a pair) once the MMAs issued so far retire
+        auto free_stage = [&](uint32_t s) {
+          if constexpr (kPair) {
+            umma_commit_pair(smem_u32(&bars->empty[s]));
+            umma_commit_pair(map_to_cta(smem_u32(&bars->empty[s]), 1u));
+          } else {
+            umma_commit(&bars->empty[s]);
+          }
+        };
         for (; ok && units.next(w); ++acc_it) {
           const uint32_t ab = acc_it % NACC;
           const uint32_t aph = (acc_it / NACC) & 1u;
@@ -228,7 +301,38 @@ struct TcGemm {
           }
           tc_fence_after_sync();
           const uint32_t tmem_acc = tmem_base + ab * ACC_COLS;
-          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
+          int kb = 0;
+          if constexpr (HALF) {
+            // Accumulator 0 is drained (the wait above), accumulator 1 maybe not yet: run the first
+            // K blocks into accumulator 0 alone, keeping their stages, then - once the epilogue has
+            // let go of accumulator 1 - the same blocks into accumulator 1, and free the stages.
+            const int pro = w.kbn < HALF_KB ? w.kbn : HALF_KB;
+            for (int j = 0; j < pro; ++j) {
+              const uint32_t s = (it + j) % kStages;
+              const uint32_t ph = ((it + j) / kStages) & 1u;
+              if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
+                report(p, bars, KCG_ST_TIMEOUT_MMA, it + j, s);
+                ok = false;
+                break;
+              }
+              tc_fence_after_sync();
+              issue(s, j, 0, 1, tmem_acc);
+            }
+            if (!ok) break;
+            if (!mbar_wait(&bars->tmem_empty[1], aph ^ 1u, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_MMA, 0x101u, acc_it);
+              break;
+            }
+            tc_fence_after_sync();
+            for (int j = 0; j < pro; ++j) {
+              const uint32_t s = (it + j) % kStages;
+              issue(s, j, 1, 2, tmem_acc);
+              free_stage(s);
+            }
+            it += pro;
+            kb = pro;
+          }
+          for (; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
             if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
@@ -237,44 +341,8 @@ struct TcGemm {
               break;
             }
             tc_fence_after_sync();
-            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-            const uint32_t sb = sa + L.a_bytes;
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-              uint32_t a_off, b_off;
-              if constexpr (kATrans) {
-                a_off = ks * UMMA_K * 128;
-              } else {
-                constexpr int swb = (kBK * EB < 128) ? kBK * EB : 128;
-                a_off = ((ks * 32) / swb) * L.a_box_bytes + ((ks * 32) % swb);
-              }
-              b_off = ks * UMMA_K * 128;
-              const uint32_t acc_flag = (kb > 0 || ks > 0) ? 1u : 0u;
-#pragma unroll
-              for (int t = 0; t < MT; ++t) {
-                // second accumulator: local A rows 128..255. Two accumulators also keep
-                // consecutive MMAs independent of each other, which the tensor pipe needs to
-                // stay full (a single accumulator chain measured ~10 % slower).
-                const uint32_t a_t = kATrans ? t * (128 / L.atom) * L.a_box_bytes
-                                             : t * 128 * (L.a_box_bytes / R);
-                const uint64_t bdesc = make_smem_desc(sb + b_off, L.b_lbo, L.b_sbo, L.b_desc_swizzle);
-                const uint64_t adesc =
-                    make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
-                const uint32_t d = tmem_acc + t * kBN;
-                if constexpr (kPair) {
-                  umma_ss_pair<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
-                } else {
-                  umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
-                }
-              }
-            }
-            // stage reusable (in both CTAs of a pair) once these MMAs retire
-            if constexpr (kPair) {
-              umma_commit_pair(smem_u32(&bars->empty[s]));
-              umma_commit_pair(map_to_cta(smem_u32(&bars->empty[s]), 1u));
-            } else {
-              umma_commit(&bars->empty[s]);
-            }
+            issue(s, kb, 0, MT, tmem_acc);
+            free_stage(s);
           }
           if (ok) {
             if constexpr (kPair) {
@@ -357,14 +425,29 @@ struct TcGemm {
       for (; units.next(w); ++acc_it) {
         const uint32_t ab = acc_it % NACC;
         const uint32_t aph = (acc_it / NACC) & 1u;
-        // The warp must leave the wait as one: tcgen05.ld below is warp-collective.
+        // The four epilogue warps leave the wait as one (named barrier 2 ANDs their outcomes):
+        // tcgen05.ld below is warp-collective, and the K-split path meets on named barrier 1, where
+        // a warp that had given up alone - by the abort flag or its own time limit - would leave
+        // the other three waiting for its threads for ever.
         const bool got = mbar_wait(&bars->tmem_full[ab], aph, &bars->abort_flag);
-        if (!__all_sync(0xffffffffu, got)) {
-          if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, acc_it, ab);
+        if (!named_bar_all(2, NUM_EPI_THREADS, got)) {
+          if (!got) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, acc_it, ab);
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
+        // This warp has read all it needs of accumulator buffer (or, in HALF mode, accumulator) `idx`.
+        auto release = [&](uint32_t idx) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (kPair) {
+              mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[idx]), 0u));
+            } else {
+              mbar_arrive(&bars->tmem_empty[idx]);
+            }
+          }
+        };
         if (w.nsplit == 1) {
           // Whole-K tile: each warp converts 32 rows x 128 bytes at a time into its own
           // staging buffer (16-byte units XOR-swizzled by row, so neither the writes nor the
@@ -425,6 +508,7 @@ struct TcGemm {
                 tma_store_commit();
               }
             }
+            if constexpr (HALF) release(static_cast<uint32_t>(t));
           }
           if (p.n_peers > 0) {
             // Fused all-gather: once this warp's rows of the tile are in C (stores complete, and
@@ -472,17 +556,10 @@ struct TcGemm {
                 tma_store_commit();
               }
             }
+            if constexpr (HALF) release(static_cast<uint32_t>(t));
           }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (kPair) {
-            mbar_arrive_cluster(map_to_cta(smem_u32(&bars->tmem_empty[ab]), 0u));
-          } else {
-            mbar_arrive(&bars->tmem_empty[ab]);
-          }
-        }
+        if constexpr (!HALF) release(ab);
 
         if (w.nsplit > 1) {
           // Publish this split's partial tile; the last split to arrive sums all

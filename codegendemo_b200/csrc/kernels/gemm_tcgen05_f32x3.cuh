@@ -351,12 +351,17 @@ struct TcGemmF32x3 {
         for (int kb0 = 0; kb0 < w.kbn; kb0 += kChunk, ++chunk_it) {
           const uint32_t ab = chunk_it & 1u;
           const uint32_t aph = (chunk_it >> 1) & 1u;
-          const bool got = mbar_wait(&bars->tmem_full[ab], aph, &bars->abort_flag);
-          if (!__all_sync(0xffffffffu, got)) {
-            if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, chunk_it, ab);
-            ok = false;
-            break;
+          // A warp whose wait ran out stops reading TMEM but keeps walking the unit's chunks (their
+          // waits return at once under the abort flag), so that all eight accumulating warps reach
+          // the vote below together.
+          if (ok) {
+            const bool got = mbar_wait(&bars->tmem_full[ab], aph, &bars->abort_flag);
+            if (!__all_sync(0xffffffffu, got)) {
+              if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, chunk_it, ab);
+              ok = false;
+            }
           }
+          if (!ok) continue;
           tc_fence_after_sync();
           const uint32_t tmem_acc =
               tmem_base + ab * ACC_COLS + col_half0 + (static_cast<uint32_t>(q * 32) << 16);
@@ -382,6 +387,10 @@ struct TcGemmF32x3 {
             }
           }
         }
+        // The accumulating warps leave a unit as one (named barrier 2 ANDs their outcomes): the
+        // store path below meets on named barrier 1, where a warp that had given up alone would
+        // leave the others waiting for its threads for ever.
+        ok = named_bar_all(2, NUM_EPI_THREADS, ok);
         if (!ok) break;
         // ---- tile (or split partial) complete in registers: store. A launch with a fused
         // epilogue sends whole-K tiles through the workspace too (every tile is then its own

@@ -35,6 +35,7 @@ struct WorkUnit {
   int m0, n0;   // origin of the output tile (m0 counts rows of the whole, possibly batched, C)
   int mcol;     // m0 within its batch: the M coordinate of an A stored K x M
   int kofs;     // batch * K: row offset of the batch's B (and of its A when stored K x M)
+  int nofs;     // batch * N: row offset of the batch's B when B is stored N x K
   int tile;     // tile index in raster order
   int split;    // index of this contributor within the tile, in K order
   int nsplit;   // contributors of the tile (1 = whole K here: store C directly)
@@ -47,13 +48,13 @@ struct WorkIter {
   int u, stride, first_split, factor, num_units;
   int tiles_m, tiles_n, num_kb;
   int sk_per, sk_c, sk_g0, sk_g1;
-  int batch_rows, k_size;
+  int batch_rows, k_size, n_size;
 
   KCG_HD WorkIter(const KcgGemmParams& p, int unit0, int unit_stride, int tiles_m_,
                                       int tiles_n_, int num_kb_)
       : u(unit0), stride(unit_stride), first_split(p.split_first_tile),
         factor(p.split_factor > 0 ? p.split_factor : 1), tiles_m(tiles_m_), tiles_n(tiles_n_),
-        num_kb(num_kb_), sk_per(p.sk_per), sk_c(unit0), batch_rows(p.batch_rows), k_size(p.K) {
+        num_kb(num_kb_), sk_per(p.sk_per), sk_c(unit0), batch_rows(p.batch_rows), k_size(p.K), n_size(p.N) {
     const int tiles = tiles_m * tiles_n;
     if (sk_per > 0) {
       num_units = first_split;
@@ -87,6 +88,7 @@ struct WorkIter {
     const int b = batch_rows > 0 ? w.m0 / batch_rows : 0;
     w.mcol = w.m0 - b * batch_rows;
     w.kofs = b * k_size;
+    w.nofs = b * n_size;
   }
 
   KCG_HD bool next(WorkUnit& w) {

@@ -54,7 +54,7 @@ class CudaLauncher:
         return self.m_runtime
 
     def launchKernel(self, device, *args, stream=None, alpha=1.0, beta=0.0, bias=None, relu=False, peers=None,
-                     batch=1):
+                     batch=1, lda=0, ldb=0, ldc=0):
         """(a, b, c) -> c = a.b on `stream` (torch's current stream by default). The keyword
         arguments fuse c = act(alpha * a.b + beta * c + bias) into the kernel's store; `peers` (up to 7
         device addresses or tensors shaped like c) also receive every finished tile: the fused
@@ -67,6 +67,18 @@ class CudaLauncher:
             stream = DeviceInfo.get_cuda_stream(device)
         a, b, c = (_pointer_of(x) for x in args)
         lib = _lib.get_lib()
+        if lda or ldb or ldc:
+            # operands that are sub-matrices of wider row-major arrays: elements between rows (0 = contiguous)
+            if peers:
+                raise ValueError("a strided launch has no fused all-gather")
+            fused = not (alpha == 1.0 and beta == 0.0 and bias is None and not relu)
+            epi = _lib.Epilogue(float(alpha), float(beta), _pointer_of(bias) if bias is not None else 0,
+                                int(bool(relu))) if fused else None
+            _lib.check(lib.kcg_launch_gemm_strided(ctypes.c_uint64(rt.m_function), ctypes.byref(self.m_cInfo),
+                                                   int(device), ctypes.c_uint64(int(stream)), ctypes.c_uint64(a),
+                                                   ctypes.c_uint64(b), ctypes.c_uint64(c), int(lda), int(ldb),
+                                                   int(ldc), int(batch), ctypes.byref(epi) if fused else None))
+            return
         if batch != 1:
             # (a, b, c) hold `batch` contiguous problems of the kernel's M, N, K (torch.bmm layout)
             if peers:

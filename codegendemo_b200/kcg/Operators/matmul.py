@@ -31,7 +31,8 @@ _ATTR_TO_KEY = {
     "LOAD_CONTINUOUS": ConfigKeywords.KEY_LOAD_CONTINUOUS,
     "REDUCE_C_CONTINUOUS": ConfigKeywords.KEY_REDUCE_C_CONTINUOUS,
 }
-_OPTIONAL = {"NUM_STAGES": ConfigKeywords.KEY_NUM_STAGES, "KERNEL_VARIANT": ConfigKeywords.KEY_KERNEL_VARIANT}
+_OPTIONAL = {"NUM_STAGES": ConfigKeywords.KEY_NUM_STAGES, "KERNEL_VARIANT": ConfigKeywords.KEY_KERNEL_VARIANT,
+             "IS_BTRANS": ConfigKeywords.KEY_IS_B_TRANSPOSE}
 
 # Shared memory one CTA may use on sm_100a (the reference asserts 64 KiB for gfx906).
 MAX_SHARED_BYTES = 227 * 1024
@@ -85,6 +86,7 @@ class KernelArgMatmul:
         # optional, B200-specific
         self.NUM_STAGES = 0       # 0 = derive from SHARED_PREFETCH
         self.KERNEL_VARIANT = 0   # 0 = auto
+        self.IS_BTRANS = 0        # 1 = B is stored N x K (tcgen05 16-bit kernels)
 
     def jsonfy(self) -> Dict:
         obj = {key: int(getattr(self, attr)) for attr, key in _ATTR_TO_KEY.items()}
@@ -113,7 +115,7 @@ class KernelArgMatmul:
 
     def usesTensorCores(self) -> bool:
         """True when the config's tile is one the tcgen05 kernel can build (what AUTO resolves to)."""
-        if self.KERNEL_VARIANT in (2, 3, 4):
+        if self.KERNEL_VARIANT in (2, 3, 4, 5):
             return True
         if self.KERNEL_VARIANT == 1:
             return False

@@ -90,29 +90,105 @@ def build_kernel(kpm: KernelArgMatmul, deviceId: int = 0):
 _KERNELS = {}
 
 
-def matmul(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
+def _row_pitch(t, what: str) -> int:
+    """Leading dimension (elements between rows) of a 2-D tensor whose rows are contiguous: a plain
+    matrix or a column block / row block view of a wider row-major one."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{what} must be a 2-D tensor with contiguous rows (a view with a row pitch is fine)")
+    return int(t.stride(0)) if t.shape[0] > 1 else int(t.shape[1])
+
+
+def matmul(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, b_transposed=False, **keys):
     """``c = a @ b`` on the current CUDA device through the kernel database's config for the shape
     (or a default config tuned by keyword). ``alpha``, ``beta``, ``bias`` (N values of c's dtype) and
-    ``relu`` fuse ``c = act(alpha * a @ b + beta * c + bias)`` into the kernel's store. Compiled and
-    loaded kernels are kept per (shape, dtype, device, keys)."""
+    ``relu`` fuse ``c = act(alpha * a @ b + beta * c + bias)`` into the kernel's store. The operands may
+    be views with a row pitch (column or row blocks of wider row-major tensors): their leading dimensions go
+    to the strided launch entry, nothing is copied. ``b_transposed=True`` takes ``b`` stored N x K and computes
+    ``a @ b.T`` (16-bit dtypes). Compiled and loaded kernels are kept per (shape, dtype, device, keys)."""
     import torch
     M, K = a.shape
-    K2, N = b.shape
-    assert K == K2 and a.is_contiguous() and b.is_contiguous()
+    if b_transposed:
+        N, K2 = b.shape
+    else:
+        K2, N = b.shape
+    assert K == K2
+    lda, ldb = _row_pitch(a, "a"), _row_pitch(b, "b")
     if c is None:
         if beta != 0.0:
             raise ValueError("beta != 0 needs the c to scale")
         c = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    ldc = _row_pitch(c, "c")
     dt = FromTorchType(a.dtype)
     dev = a.device.index or 0
-    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())))
+    key = (M, N, K, int(dt), dev, tuple(sorted(keys.items())), bool(b_transposed))
     kern = _KERNELS.get(key)
     if kern is None:
         kpm = default_config(M, N, K, dt, **keys) if keys else tuned_config(M, N, K, dt)
+        if b_transposed:
+            kpm = _single_pass_16bit(kpm, M, N, K, dt)
+            kpm.IS_BTRANS = 1
         _, kern = build_kernel(kpm, dev)
         _KERNELS[key] = kern
-    kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu)
+    contiguous = lda == K and ldb == (K if b_transposed else N) and ldc == N
+    if contiguous:
+        kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu)
+    else:
+        kern.run(a, b, c, alpha=alpha, beta=beta, bias=bias, relu=relu, lda=lda, ldb=ldb, ldc=ldc)
     return c
+
+
+def _single_pass_16bit(kpm, M, N, K, dt):
+    """An N x K stored B runs on the single-pass tcgen05 kernels (variants 2 and 4) only: keep a tuned config of
+    those families, else fall back to the default tile."""
+    if kpm.KERNEL_VARIANT in (2, 4) or (kpm.KERNEL_VARIANT == 0 and kpm.usesTensorCores()):
+        if kpm.KERNEL_VARIANT == 0:
+            kpm.KERNEL_VARIANT = 2
+        return kpm
+    return default_config(M, N, K, dt, KERNEL_VARIANT=2)
+
+
+def attention(q, k, v, scale=None, out=None):
+    """``softmax(scale * q @ k^T) @ v`` per head, the attention-shaped chain, as three launches on the current
+    stream: a batched product with k taken as stored (keys x head_dim, no transposed copy) whose epilogue applies
+    ``scale``; a row softmax in place (fp32 arithmetic); a batched product with v. ``q`` is (heads, Sq, d), ``k``
+    and ``v`` are (heads, Sk, d), all contiguous fp16 / bf16; ``heads`` may be batch * heads flattened. The
+    Sq x Sk score matrix is materialised in the inputs' dtype; returns (heads, Sq, d)."""
+    import ctypes
+    import math
+    import torch
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.Utils import DeviceInfo
+    H, Sq, D = q.shape
+    H2, Sk, D2 = k.shape
+    assert H == H2 and D == D2 and tuple(v.shape) == (H, Sk, D)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dt = FromTorchType(q.dtype)
+    dev = q.device.index or 0
+    key = ("attn", H, Sq, Sk, D, int(dt), dev)
+    kerns = _KERNELS.get(key)
+    if kerns is None:
+        def tile_for(m, n, kk, btrans):
+            kpm = tuned_config(H * m, n, kk, dt)
+            if m % kpm.BLOCK_SIZE_M or kpm.KERNEL_VARIANT not in (0, 2, 4):
+                kpm = default_config(m, n, kk, dt)
+            kpm.M = m
+            if btrans:
+                kpm = _single_pass_16bit(kpm, m, n, kk, dt)
+                kpm.IS_BTRANS = 1
+            return build_kernel(kpm, dev)[1]
+        kerns = (tile_for(Sq, Sk, D, True), tile_for(Sq, D, Sk, False))
+        _KERNELS[key] = kerns
+    scores = torch.empty((H, Sq, Sk), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((H, Sq, D), dtype=q.dtype, device=q.device)
+    kerns[0].run(q, k, scores, alpha=float(scale), batch=H)
+    _lib.check(_lib.get_lib().kcg_softmax_rows(dev, ctypes.c_uint64(DeviceInfo.get_cuda_stream(dev)),
+                                               ctypes.c_uint64(scores.data_ptr()), H * Sq, Sk, 0, 1.0, int(dt)))
+    kerns[1].run(scores, v, out, batch=H)
+    return out
 
 
 def bmm(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):

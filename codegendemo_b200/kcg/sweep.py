@@ -24,9 +24,7 @@ import time
 from codegendemo_b200.kcg.matmul_op import build_kernel, default_config, tuned_config
 from codegendemo_b200.kcg.Utils import EnumKernelDType as E
 
-# Dense peaks used as denominators (TFLOP/s): nominal bf16/fp16, nominal TF32 / 3 for fp32 run as
-# 3xTF32, FFMA for the SIMT kernel; HBM from the STREAM-style copy measured on this pool.
-PEAK_16BIT, PEAK_TF32, PEAK_FFMA, HBM_GBS = 2250.0, 1100.0, 74.0, 6457.0
+from codegendemo_b200.kcg import roofline as rl
 
 SIMT_128 = dict(KERNEL_VARIANT=1, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=16, THREAD_SIZE_M=8,
                 THREAD_SIZE_N=8, BLOCK_LAYOUT_M=4, BLOCK_LAYOUT_N=2, WARP_LAYOUT_M=4, WARP_LAYOUT_N=8,
@@ -50,7 +48,7 @@ def cases(which: str):
     return out
 
 
-def run_case(tag, M, N, K, edt, dist, keys, device, iters, cpu, cold=False):
+def run_case(tag, M, N, K, edt, dist, keys, device, iters, cpu, cold=False, peaks=None):
     import torch
     tdt = {E.float32: torch.float32, E.bfloat16: torch.bfloat16, E.float16: torch.float16}[edt]
     g = torch.Generator().manual_seed(0)
@@ -115,14 +113,17 @@ def run_case(tag, M, N, K, edt, dist, keys, device, iters, cpu, cold=False):
     diff = (c[:rows].to(ref.dtype) - ref).abs()
     rms = ref.pow(2).mean().sqrt()
     max_rel = float((diff / torch.maximum(ref.abs(), rms)).max().item())
-    flops = 2.0 * M * N * K
+    flops = rl.gemm_flops(M, N, K)
     eb = 4 if tdt == torch.float32 else 2
-    nbytes = eb * (M * K + K * N + M * N)
+    nbytes = rl.gemm_bytes(M, N, K, eb)
     variant = int(inc.kernelInfo["kernel"])
-    peak = PEAK_FFMA if variant == 1 else (PEAK_TF32 / 3 if tdt == torch.float32 else PEAK_16BIT)
-    roof = min(peak, flops / nbytes * HBM_GBS / 1e3)  # TFLOP/s
+    peaks = peaks or rl.load_peaks(None)
+    # "of dense peak" is quoted against the nominal figures, "of roofline" against min(that, AI x HBM bandwidth)
+    peak = rl.tensor_peak_tflops(str(tdt).replace("torch.", ""), variant == 1, peaks, nominal=True)
+    roof = rl.shape_roofline(M, N, K, eb, peak, peaks["hbm_gbs"])["peak"]  # TFLOP/s
     rec = {"case": tag, "m": M, "n": N, "k": K, "dtype": str(tdt).replace("torch.", ""),
-           "kernel": {1: "simt", 2: "tcgen05", 3: "tf32x1", 4: "tcgen05 pair"}.get(variant, str(variant)),
+           "kernel": {1: "simt", 2: "tcgen05", 3: "tf32x1", 4: "tcgen05 pair", 5: "tcgen05 cluster split-K"}.get(
+               variant, str(variant)),
            "tile": f"{kpm.BLOCK_SIZE_M}x{kpm.BLOCK_SIZE_N}x{kpm.BLOCK_SIZE_K}", "ms_median": med, "ms_best": best,
            "tflops": flops / med / 1e9, "gbs": nbytes / med / 1e6, "roofline_tflops": roof,
            "frac_roofline": flops / med / 1e9 / roof, "frac_peak": flops / med / 1e9 / peak,
@@ -160,14 +161,17 @@ def main(argv=None) -> int:
     ap.add_argument("--cold", action="store_true",
                     help="problems that fit L2 rotate over copies of their operands, so every launch starts cold")
     ap.add_argument("--json", default="")
+    ap.add_argument("--peaks", default="", help="JSON file with measured hbm_gbs / bf16_tflops of this machine "
+                    "(default: the stated fallback figures)")
     a = ap.parse_args(argv)
+    peaks = rl.load_peaks(a.peaks or None)
     torch.cuda.set_device(a.device)
     print("| case | kernel, tile | ms median / best | TFLOP/s | of dense peak | of roofline | GB/s | cuBLAS TFLOP/s | "
           "max rel err | CPU ms (threads) |")
     print("|---|---|---|---|---|---|---|---|---|---|")
     recs = []
     for (tag, M, N, K, edt, dist, keys) in cases(a.only):
-        r = run_case(tag, M, N, K, edt, dist, keys, a.device, a.iters, not a.no_cpu, cold=a.cold)
+        r = run_case(tag, M, N, K, edt, dist, keys, a.device, a.iters, not a.no_cpu, cold=a.cold, peaks=peaks)
         recs.append(r)
         print(to_row(r), flush=True)
     if a.json:

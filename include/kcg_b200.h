@@ -53,6 +53,8 @@ enum kcg_cfg_index {
 #define KCG_KERNEL_TCGEN05 2  /* TMA + tcgen05/TMEM; fp32 runs as 3xTF32 */
 #define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
 #define KCG_KERNEL_TCGEN05_PAIR 4 /* fp16/bf16 on CTA pairs (tcgen05 cta_group::2), BLOCK_SIZE_M = 256 */
+#define KCG_KERNEL_TCGEN05_CLUSTERK 5 /* fp16/bf16 128-row tiles; LOCAL_SPLIT_U (2, 4, 8) CTAs of a thread-block
+                                         cluster split K and reduce through distributed shared memory */
 #define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
 #define KCG_KERNEL_WAIT_PROBE 101 /* no GEMM: one bounded wait (20 ms) that expires -> KCG_E_DEVICE_TIMEOUT */
 
@@ -80,7 +82,7 @@ typedef struct kcg_kernel_info {
   int32_t group;      /* BLOCK_MAPPING */
   int32_t atrans;     /* IS_ATRANS */
   int32_t m, n, k;
-  int32_t reserved[8];
+  int32_t reserved[8]; /* [0] persistent grid cap (SMs), [1] b_trans */
 } kcg_kernel_info;
 
 typedef struct kcg_compile_opts {
@@ -88,6 +90,9 @@ typedef struct kcg_compile_opts {
   int32_t num_stages;  /* 0 = derive from SHARED_PREFETCH (0 -> 2 stages, 1 -> as many as fit, max 6) */
   int32_t num_sms;     /* persistent grid size cap; 0 = 148 (B200) */
   int32_t force;       /* 1 = recompile even when the cubin is cached */
+  int32_t b_trans;     /* 1 = B is stored N x K row-major (C = A * Bt^T); fp16 / bf16 with KCG_KERNEL_TCGEN05 / _PAIR.
+                          The reference stores B as K x N only (src/lib/Operators/Matmul.cc:93-121). */
+  int32_t reserved[3];
 } kcg_compile_opts;
 
 typedef struct kcg_device_props {
@@ -159,6 +164,30 @@ int kcg_launch_gemm_ex(uint64_t function, const kcg_kernel_info* info, int devic
 int kcg_launch_gemm_batched(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
                             uint64_t A, uint64_t B, uint64_t C, int batch, const kcg_epilogue* epi);
 
+/* ---- strided operands --------------------------------------------------------------
+ * kcg_launch_gemm / _ex / _batched with leading dimensions: lda, ldb, ldc are the distances, in
+ * elements, between consecutive rows of A, B and C as they are stored (A: M x K, or K x M with
+ * IS_ATRANS; B: K x N, or N x K when compiled with b_trans; C: M x N). 0 means contiguous (the row
+ * length); a larger value addresses a sub-matrix of a wider row-major array, e.g. a column block of
+ * a weight matrix or a head slice of a packed activation. Each must keep rows 16-byte aligned
+ * (TMA pitch rule). With batch > 1 the batches follow one another row after row at the same pitch.
+ * No counterpart in the reference: its kernels take the row length as the pitch
+ * (src/lib/Operators/Matmul.cc:93-121); strided GEMM is on its list of next operators
+ * (doc/结果汇总.md). */
+int kcg_launch_gemm_strided(uint64_t function, const kcg_kernel_info* info, int device, uint64_t stream,
+                            uint64_t A, uint64_t B, uint64_t C, int64_t lda, int64_t ldb, int64_t ldc, int batch,
+                            const kcg_epilogue* epi);
+
+/* ---- row softmax (middle step of the attention-shaped chain) ---------------------------
+ * In place: X[r, :] = softmax(scale * X[r, :]) for r in [0, rows), fp32 arithmetic; X is a
+ * row-major matrix of `dtype` (KCG_DTYPE_*) values with `ld` elements between rows (0 = cols).
+ * With it, softmax(scale * Q K^T) V runs as three launches on one stream: a batched GEMM compiled
+ * with b_trans (S = Q K^T, K stored keys x head_dim), this call, and a batched GEMM (P V). The
+ * reference has no such operator yet; it lists the flash-attention-shaped chain after batched
+ * GEMM among its next operators (doc/结果汇总.md). Rows must start and end on 16-byte boundaries. */
+int kcg_softmax_rows(int device, uint64_t stream, uint64_t X, int64_t rows, int cols, int64_t ld, float scale,
+                     int dtype);
+
 /* ---- M-sharded product with the all-gather of C fused into the kernel ---------------
  * No counterpart in the reference (it has no multi-GPU code). Rank r of G computes rows
  * [r*M/G, (r+1)*M/G) of C with the same cubin as kcg_launch_gemm; `C` is the address of that slab
@@ -204,17 +233,26 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
  *
  * The split-K workspace is a fixed array inside the library's device image (about 32 MiB per GPU
  * that loads the library, held until the process exits). Limits: M, N, K multiples of 128, 256, 64;
- * K >= 64*KCG_NOALLOC_SPLITK; KCG_NOALLOC_SPLITK*M*N <= KCG_NOALLOC_MAX_PARTIAL_FLOATS and
- * (M/128)*(N/256) <= KCG_NOALLOC_MAX_TILES, else KCG_E_TOO_LARGE. The call itself calls no
- * cudaMalloc/cudaFree or allocating library routine. The first call on a device resolves the
- * array's device address and raises the kernel's shared-memory limit; make that first call before
- * any stream capture begins. All calls on a device share the one array: two calls that overlap on the
- * GPU (different streams, no ordering) race on it and give wrong results; calls ordered on one
- * stream are safe. `synchronize` != 0 waits for the stream and reports a kernel that gave up in a
- * bounded wait as KCG_E_DEVICE_TIMEOUT; with 0 the call is asynchronous. */
+ * K >= 64*KCG_NOALLOC_SPLITK; KCG_NOALLOC_SPLITK*M*N <= KCG_NOALLOC_MAX_PARTIAL_FLOATS, else
+ * KCG_E_TOO_LARGE. That bound on the partial tiles is the one that binds: it allows M*N up to 2 Mi
+ * elements, i.e. at most KCG_NOALLOC_MAX_TILES = 64 tiles of 128x256, which is also the number of
+ * arrival counters in the array. The call itself calls no cudaMalloc/cudaFree or allocating
+ * library routine. The first call on a device resolves the array's device address and raises the
+ * kernel's shared-memory limit; under CUDA's default lazy module loading that first call is also
+ * what loads the library's device image - the 32 MiB array included - onto the GPU, an implicit
+ * device allocation made by the CUDA runtime that can fail when the GPU is already full. So make
+ * the first call per device at start-up, while memory is still free and before any stream
+ * capture begins; later calls leave the GPU's free memory untouched. The call makes `device`
+ * current while it runs and puts the caller's current device back before it returns. All calls on
+ * a device share the one array: two calls that overlap on the GPU (different streams, no
+ * ordering) race on it and give wrong results; calls ordered on one stream are safe.
+ * `synchronize` != 0 waits for the stream and reports a kernel that gave up in a bounded wait as
+ * KCG_E_DEVICE_TIMEOUT (and clears the record). With 0 the call is asynchronous and such a record
+ * is kept in the array until the next call with `synchronize` != 0 on that device reports it:
+ * kcg_check_status does not see it. */
 #define KCG_NOALLOC_SPLITK 4
 #define KCG_NOALLOC_MAX_PARTIAL_FLOATS (8 * 1024 * 1024)
-#define KCG_NOALLOC_MAX_TILES 4096
+#define KCG_NOALLOC_MAX_TILES 64
 int kcg_gemm_bf16_splitk_noalloc(int device, uint64_t stream, uint64_t A, uint64_t B, uint64_t C, int M, int N,
                                  int K, int synchronize);
 

@@ -16,7 +16,13 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REFERENCE_DIR = os.environ.get("KCG_REFERENCE_DIR", "/root/reference")
+def reference_dir() -> str:
+    """Where the reference's source tree lies: $KCG_REFERENCE_DIR, else a directory named `reference`
+    beside this repository. It may not exist (a GPU box has none)."""
+    return os.environ.get("KCG_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+REFERENCE_DIR = reference_dir()
 CFLAGS = ["-O2", "-ffp-contract=off", "-fPIC", "-shared"]
 
 

@@ -27,7 +27,7 @@ def run_config(kpm, A, B):
     inc, kern = build_kernel(kpm, 0)
     tdt = kpm.dtypeTorch('A')
     a = (A.t().contiguous() if kpm.isATranspose else A).to(tdt).cuda()
-    b = B.to(tdt).cuda()
+    b = (B.t().contiguous() if kpm.IS_BTRANS else B).to(tdt).cuda()  # N x K storage when IS_BTRANS=1
     c = torch.full((kpm.M, kpm.N), float("nan"), dtype=tdt, device="cuda:0")  # poisoned output
     before = _lib.get_lib().kcg_launch_count()
     kern.run(a, b, c)
@@ -319,6 +319,141 @@ def test_rectangular_sweep_points(case):
     rows = torch.randperm(M, generator=g)[:min(M, 64)].sort().values
     _check_row_blocks(c, A, B, rows, oracle.tolerance_for(tdt))
     assert _column_checksum_ok(c, a, b, 1e-6 if dt == E.float32 else 5e-3)
+
+
+def _random_row_blocks(M, blocks, seed, block=128):
+    """Row indices of `blocks` distinct, randomly chosen `block`-row blocks of an M-row matrix (all of them if M is small)."""
+    nb = M // block
+    g = torch.Generator().manual_seed(seed)
+    pick = torch.randperm(nb, generator=g)[:min(blocks, nb)].sort().values
+    return torch.cat([torch.arange(int(b) * block, (int(b) + 1) * block) for b in pick])
+
+
+@pytest.mark.parametrize("case", gpu_cases.TUNED_SHAPES, ids=[c[0] for c in gpu_cases.TUNED_SHAPES])
+def test_tuned_config_of_every_benchmarked_shape_matches_oracle(case):
+    """Every point of the rectangular sweep and every row-slab shape of the M-sharded headline product, run with
+    the config `tuned_config` hands the operator and the benchmark for that shape (kernel database entry or rule
+    of thumb) - the reference checks every config it times (Runtime/python/kcg/KCGTask.py:177-191). C starts as
+    NaN; eight random 128-row blocks are compared with the host oracle, all of C through the column checksum."""
+    from codegendemo_b200.kcg.matmul_op import tuned_config
+    _, M, N, K, dt, dist = case
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, N, K, tdt, dist, seed=0)
+    c, _, (a, b) = run_config(tuned_config(M, N, K, dt), A, B)
+    assert not torch.isnan(c).any().item(), "kernel left part of C unwritten"
+    rows = _random_row_blocks(M, 8, seed=M + N)
+    _check_row_blocks(c, A, B, rows, oracle.tolerance_for(tdt))
+    assert _column_checksum_ok(c, a, b, 1e-6 if dt == E.float32 else 5e-3)
+
+
+def test_two_streams_run_split_k_launches_side_by_side():
+    """Launches on different streams of one GPU own separate split-K workspaces, counters and status words: two
+    K-split products queued side by side (no ordering between the streams) give the bits of their serial runs."""
+    shapes = [(256, 512, 4096, dict(LOCAL_SPLIT_U=4)), (128, 1024, 8192, dict(LOCAL_SPLIT_U=8, BLOCK_SIZE_N=128))]
+    kerns, ops, serial = [], [], []
+    for i, (M, N, K, keys) in enumerate(shapes):
+        A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=30 + i)
+        c, kern, (a, b) = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
+        assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.TOL_16BIT
+        kerns.append(kern), ops.append((a, b)), serial.append(c)
+    streams = [torch.cuda.Stream(device=0) for _ in shapes]
+    outs = [torch.full_like(c, float("nan")) for c in serial]
+    torch.cuda.synchronize()
+    for _ in range(20):  # interleaved: the launches of the two streams overlap on the GPU
+        for st, kern, (a, b), out in zip(streams, kerns, ops, outs):
+            with torch.cuda.stream(st):
+                kern.run(a, b, out)
+    for st, kern in zip(streams, kerns):
+        with torch.cuda.stream(st):
+            kern.checkStatus()  # synchronises this stream and reads ITS status block
+    torch.cuda.synchronize()
+    for out, c in zip(outs, serial):
+        assert torch.equal(out, c)
+
+
+def test_strided_operands_are_read_and_written_in_place():
+    """kcg_launch_gemm_strided: A, B and C as column blocks of wider row-major arrays (leading dimension > row
+    length); what lies outside the C block is left untouched."""
+    from codegendemo_b200.kcg.matmul_op import matmul
+    M, N, K = 256, 512, 384
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=12)
+    wide_a = torch.zeros(M, K + 128, dtype=torch.bfloat16, device="cuda:0")
+    wide_b = torch.zeros(K, N + 256, dtype=torch.bfloat16, device="cuda:0")
+    wide_c = torch.full((M, N + 64), 7.0, dtype=torch.bfloat16, device="cuda:0")
+    wide_a[:, 64:64 + K] = A.cuda()
+    wide_b[:, 128:128 + N] = B.cuda()
+    before = _lib.get_lib().kcg_launch_count()
+    matmul(wide_a[:, 64:64 + K], wide_b[:, 128:128 + N], c=wide_c[:, 32:32 + N])
+    torch.cuda.synchronize()
+    assert _lib.get_lib().kcg_launch_count() == before + 1  # no hidden copy kernels of ours, one GEMM launch
+    ref = oracle.host_matmul(A, B)
+    assert oracle.rel_errors(wide_c[:, 32:32 + N], ref)["max_rel"] <= oracle.TOL_16BIT
+    assert (wide_c[:, :32] == 7.0).all().item() and (wide_c[:, 32 + N:] == 7.0).all().item()
+    # fp32 (3xTF32 kernel stores from registers with the pitch) and a K-split launch (reducer stores with the pitch)
+    Af, Bf = oracle.make_inputs(128, 256, 2048, torch.float32, "uniform", seed=13)
+    wc = torch.full((128, 256 + 32), -3.0, dtype=torch.float32, device="cuda:0")
+    wa = torch.zeros(128, 2048 + 8, dtype=torch.float32, device="cuda:0")
+    wa[:, 4:4 + 2048] = Af.cuda()
+    matmul(wa[:, 4:4 + 2048], Bf.cuda(), c=wc[:, 16:16 + 256], BLOCK_SIZE_N=128, LOCAL_SPLIT_U=2)
+    torch.cuda.synchronize()
+    assert oracle.rel_errors(wc[:, 16:16 + 256], oracle.host_matmul(Af, Bf))["max_rel"] <= oracle.TOL_FP32
+    assert (wc[:, :16] == -3.0).all().item() and (wc[:, 16 + 256:] == -3.0).all().item()
+    # rows that are not 16-byte aligned are refused, not mis-read
+    with pytest.raises(_lib.KCGError) as ei:
+        matmul(wide_a[:, 1:1 + K], wide_b[:, 128:128 + N])
+    assert ei.value.code == _lib.E_BAD_ARG
+
+
+def test_nt_product_takes_b_as_stored():
+    from codegendemo_b200.kcg.matmul_op import matmul
+    M, N, K = 512, 768, 256
+    A, B = oracle.make_inputs(M, N, K, torch.float16, "normal", seed=14)
+    bt = B.t().contiguous().cuda()  # N x K, as a key matrix is stored
+    c = matmul(A.cuda(), bt, b_transposed=True)
+    torch.cuda.synchronize()
+    assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.TOL_16BIT
+
+
+@pytest.mark.parametrize("shape", [(4, 256, 256, 64), (16, 2048, 2048, 128), (3, 128, 384, 128)],
+                         ids=["4x256x256x64", "16x2048x2048x128", "3x128x384x128"])
+def test_attention_chain_matches_host_composition(shape):
+    """softmax(scale * q k^T) v as batched NT product -> row softmax -> batched product. The reference has no
+    attention operator (it lists the chain among its next ones), so the checker is the composition of its
+    ``torch.matmul`` check with ``torch.softmax`` on the host in fp32: parity of this extension is pinned to
+    that composition, not to reference output. Tolerance: the 16-bit bound, 2e-2 on max_rel."""
+    import math
+    from codegendemo_b200.kcg.matmul_op import attention
+    H, Sq, Sk, D = shape
+    g = torch.Generator().manual_seed(21)
+    q = torch.randn(H, Sq, D, generator=g).bfloat16()
+    k = torch.randn(H, Sk, D, generator=g).bfloat16()
+    v = torch.randn(H, Sk, D, generator=g).bfloat16()
+    out = attention(q.cuda(), k.cuda(), v.cuda())
+    torch.cuda.synchronize()
+    heads = range(H) if H <= 4 else (0, H // 2, H - 1)
+    for h in heads:
+        s = torch.matmul(q[h].float(), k[h].float().t()) / math.sqrt(D)
+        ref = torch.matmul(torch.softmax(s, dim=-1), v[h].float())
+        err = oracle.rel_errors(out[h], ref)
+        assert not err["nan"] and err["max_rel"] <= oracle.TOL_16BIT, (h, err)
+
+
+def test_row_softmax_entry():
+    lib = _lib.get_lib()
+    from codegendemo_b200.kcg.Utils import DeviceInfo
+    g = torch.Generator().manual_seed(22)
+    for tdt, code, tol in ((torch.float32, 4, 1e-5), (torch.bfloat16, 62, 8e-3), (torch.float16, 2, 2e-3)):
+        x = (torch.randn(300, 1000 if tdt == torch.float32 else 1008, generator=g) * 3).to(tdt)
+        wide = torch.zeros(300, x.shape[1] + 24, dtype=tdt, device="cuda:0")
+        wide[:, :x.shape[1]] = x.cuda()
+        rc = lib.kcg_softmax_rows(0, ctypes.c_uint64(DeviceInfo.get_cuda_stream(0)), ctypes.c_uint64(wide.data_ptr()),
+                                  300, x.shape[1], wide.shape[1], ctypes.c_float(0.5), code)
+        assert rc == 0, lib.kcg_last_error()
+        torch.cuda.synchronize()
+        ref = torch.softmax(0.5 * x.float(), dim=-1)
+        assert (wide[:, :x.shape[1]].float().cpu() - ref).abs().max().item() <= tol
+        assert (wide[:, x.shape[1]:] == 0).all().item()
+    assert lib.kcg_softmax_rows(0, 0, 16, 4, 7, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG  # 14-byte rows
 
 
 def test_device_naive_reference_agrees_with_tensor_core_kernel():

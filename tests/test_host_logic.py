@@ -16,7 +16,9 @@ from codegendemo_b200.kcg.Operators.matmul import KernelArgMatmul, TuningSpaceCh
 from codegendemo_b200.kcg.Utils import ConfigKeywords as kw, EnumKernelDType as E, PathManager, sizeof, ToTorchType
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF_CFGS = "/root/reference/TuningConfigs"
+from oracle.build_oracle import reference_dir  # $KCG_REFERENCE_DIR, else `reference` beside the repository
+
+REF_CFGS = os.path.join(reference_dir(), "TuningConfigs")
 
 
 def test_dtype_enum_keeps_reference_codes_and_adds_bf16():
@@ -58,7 +60,7 @@ def test_reference_json_files_parse_and_run_through_the_pruners():
     kpm = KernelArgMatmul.fromJson(cfgs[0])
     assert kpm.WARP_SIZE == 64 and not kpm.usesTensorCores()
     kpm.check()
-    with open("/root/reference/TuningCombs/best_combs_1024.json") as f:
+    with open(os.path.join(reference_dir(), "TuningCombs", "best_combs_1024.json")) as f:
         best = json.load(f)["cfgs"]
     assert len(best) == 270
     ok = sum(1 for c in best if TuningSpaceChecker_Matmul.check_size(dict(c)) and TuningSpaceChecker_Matmul.check_warp(c))
@@ -227,6 +229,8 @@ WORK_PLANS = [
     (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
     # 86 pair tiles on 74 pairs: all of them go to stream-K (1.16 waves become one)
     (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=4), "streamk"),
+    # 224 tiles of 256x256: the 76-tile tail is cut into 147 ranges, one fewer than the 148 CTAs that walk the whole tiles
+    (1792, 8192, 11008, E.bfloat16, dict(BLOCK_SIZE_M=256, NUM_STAGES=3), "streamk"),
     (2048, 4096, 4096, E.bfloat16, dict(), "whole"),      # 108 tiles in the last wave: the saving is below the gate
     (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk"),  # small tiles: cheap partials
     (128, 4096, 4096, E.bfloat16, dict(BLOCK_SIZE_N=128), "whole"),   # too little work per tile to pay for a reduction
@@ -261,7 +265,9 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     got = "streamk" if sk_per > 0 else "even" if factor > 1 else "whole"
     assert got == layer, (got, list(out))
     if sk_per > 0:
-        grid, slots = ranges, ranges + (tiles - first)
+        # whole tiles before the tail are walked with the grid as stride, so the grid stays at every unit that runs
+        # at once even when the tail is cut into fewer ranges; with no whole tiles the grid is the ranges
+        grid, slots = (at_once if first > 0 else ranges), ranges + (tiles - first)
         assert ranges <= at_once and first % at_once == 0
     else:
         grid, slots = min(first + (tiles - first) * factor, at_once), (tiles - first) * factor
@@ -361,3 +367,84 @@ def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     assert (few.BLOCK_SIZE_M, few.BLOCK_SIZE_N, few.BLOCK_SIZE_K) == (128, 128, 128)
     for kpm in (mid, short, few):
         kpm.check()
+
+
+def test_roofline_arithmetic():
+    """The per-shape ceiling min(tensor peak, arithmetic intensity x HBM bandwidth) that bench.py and kcg.sweep report."""
+    from codegendemo_b200.kcg import roofline as rl
+    peaks = rl.load_peaks(None)
+    assert peaks["source"] == "fallback" and peaks["hbm_gbs"] == 6650.0
+    assert rl.gemm_flops(128, 11008, 11008) == 2.0 * 128 * 11008 * 11008
+    assert rl.gemm_bytes(128, 11008, 11008, 2) == 2 * (128 * 11008 + 11008 * 11008 + 128 * 11008)
+    skinny = rl.shape_roofline(128, 11008, 11008, 2, 1655.9, 6457.4)
+    assert skinny["bound"] == "hbm" and 120 < skinny["ai"] < 130
+    assert abs(skinny["peak"] - skinny["ai"] * 6457.4 / 1e3) < 1e-9 and skinny["peak"] < 1655.9
+    square = rl.shape_roofline(8192, 8192, 8192, 2, 1655.9, 6457.4)
+    assert square["bound"] == "tensor" and square["peak"] == 1655.9
+    assert rl.tensor_peak_tflops("float32", False, peaks) == 1100.0 / 3.0
+    assert rl.tensor_peak_tflops("float32", True, peaks) == 74.0
+    assert rl.tensor_peak_tflops("bfloat16", False, peaks) == peaks["bf16_tflops"]
+    assert rl.tensor_peak_tflops("bfloat16", False, peaks, nominal=True) == 2250.0
+
+
+def test_measured_peaks_file_is_read_when_given(tmp_path):
+    from codegendemo_b200.kcg import roofline as rl
+    f = tmp_path / "peaks.json"
+    f.write_text(json.dumps({"hbm_gbs": 6000.5, "bf16_tflops": 1600, "bf16_tflops_sustained": 1400}))
+    p = rl.load_peaks(str(f))
+    assert p == {"hbm_gbs": 6000.5, "bf16_tflops": 1600.0, "bf16_tflops_sustained": 1400.0, "source": "measured"}
+
+
+def test_cluster_split_k_config_rules_and_geometry():
+    """KERNEL_VARIANT 5: one cluster of LOCAL_SPLIT_U CTAs per 128-row tile; the operand ring doubles as the buffer
+    that receives the cluster's partial slices, so it must hold 128 x BLOCK_SIZE_N fp32 values."""
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    kpm = default_config(128, 4096, 4096, E.bfloat16, KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)
+    info = compile_info(kpm.compileArgs(), num_stages=0, kernel=5)
+    assert info.kernel == _lib.KERNEL_TCGEN05_CLUSTERK and list(info.cluster) == [4, 1, 1]
+    assert info.grid[0] == 32 * 4 and info.block[0] == 192 and info.splitk == 4
+    assert info.smem_bytes == info.stages * (128 + 128) * 64 * 2 + 2048
+    assert info.stages * (128 + 128) * 64 * 2 >= 128 * 128 * 4  # ring >= receive buffer
+    for bad in (dict(LOCAL_SPLIT_U=3), dict(LOCAL_SPLIT_U=1), dict(BLOCK_SIZE_M=256), dict(BLOCK_SIZE_N=64, LOCAL_SPLIT_U=4)):
+        keys = dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)
+        keys.update(bad)
+        with pytest.raises(_lib.KCGError) as ei:
+            compile_info(default_config(256, 4096, 4096, E.bfloat16, **keys).compileArgs(), kernel=5)
+        assert ei.value.code == _lib.E_BAD_CONFIG
+    with pytest.raises(_lib.KCGError):  # fp32 data runs on the 3xTF32 kernels only
+        compile_info(default_config(128, 512, 512, E.float32, KERNEL_VARIANT=5, BLOCK_SIZE_N=128,
+                                    LOCAL_SPLIT_U=2).compileArgs(), kernel=5)
+
+
+def test_b_transposed_is_a_compile_option_of_the_16bit_single_pass_kernels():
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    kpm = default_config(256, 512, 512, E.bfloat16, IS_BTRANS=1)
+    assert kpm.jsonfy()[kw.KEY_IS_B_TRANSPOSE] == 1 and KernelArgMatmul.fromJson(kpm.jsonfy()).IS_BTRANS == 1
+    nt = compile_info(kpm.compileArgs(), kernel=2, b_trans=1)
+    nn = compile_info(kpm.compileArgs(), kernel=2)
+    assert nt.name.decode() == nn.name.decode() + "_BT1" and nt.reserved[1] == 1 and nn.reserved[1] == 0
+    assert _lib.KernelInfo.from_dict(nt.to_dict()).reserved[1] == 1  # survives the trip between processes
+    for kernel, dt in ((1, E.float32), (2, E.float32), (5, E.bfloat16)):
+        keys = dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=2 if kernel == 5 else 1)
+        if kernel == 1:
+            keys.update(BLOCK_SIZE_M=64, BLOCK_SIZE_N=64, BLOCK_SIZE_K=16, THREAD_SIZE_M=4, THREAD_SIZE_N=4)
+        with pytest.raises(_lib.KCGError) as ei:
+            compile_info(default_config(256, 512, 512, dt, **keys).compileArgs(), kernel=kernel, b_trans=1)
+        assert ei.value.code == _lib.E_BAD_CONFIG and b"b_trans" in _lib.get_lib().kcg_last_error()
+
+
+def test_strided_and_softmax_entries_validate_their_arguments_without_a_gpu():
+    import ctypes
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    lib = _lib.get_lib()
+    info = compile_info(default_config(256, 256, 256, E.bfloat16).compileArgs())
+    rc = lib.kcg_launch_gemm_strided(1, ctypes.byref(info), 0, 0, 256, 256, 256, -8, 0, 0, 1, None)
+    assert rc == _lib.E_BAD_ARG and b"negative" in lib.kcg_last_error()
+    assert lib.kcg_launch_gemm_strided(1, ctypes.byref(info), 0, 0, 256, 256, 256, 0, 0, 0, 0, None) == _lib.E_BAD_ARG
+    assert lib.kcg_softmax_rows(0, 0, 0, 4, 8, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG       # null matrix
+    assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 4, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # ld below the row length
+    assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 0, ctypes.c_float(1.0), 8) == _lib.E_BAD_ARG     # float64
+    assert lib.kcg_softmax_rows(0, 0, 4096, 4, 6, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # 12-byte rows
