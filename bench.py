@@ -13,8 +13,8 @@ tcgen05 kernel.
 Outside the timed region every rank checks its result against the CPU oracle (``oracle_check``): eight random
 128-row blocks of its slab at every N, and every row at N=1; a failed check ends the run with a non-zero exit
 code. At N=1 the line also carries, under ``other_workloads``, the other single-GPU configs - fp32 1024^3 and
-4096^3 (3xTF32 and FFMA SIMT), bf16 8192^3 and the rectangular sweep M in {128, 512, 2048} x N=K in {4096, 11008}
-x {fp32, bf16} - each with its roofline and the same shape through cuBLAS (``torch.matmul`` on the device) timed
+4096^3 (3xTF32 and FFMA SIMT), bf16 8192^3 and the rectangular sweep M in {128, 512, 2048} x N, K in {4096, 11008}
+x {fp32, bf16} (24 points) - each with its roofline and the same shape through cuBLAS (``torch.matmul`` on the device) timed
 the same way.
 
 Prints ONE JSON line on rank 0 (metric: GEMM TFLOP/s, device-timed with CUDA events, max over ranks).
@@ -226,6 +226,36 @@ def time_launches(fn, launches, warmup):
     return [evs[i].elapsed_time(evs[i + 1]) for i in range(launches)]
 
 
+def time_graph(fn, launches, replays=5):
+    """Mean device time per launch (ms) when `launches` launches are replayed from a CUDA graph: no host work
+    between kernels, so it shows what the GPU alone needs - for kernels of a few microseconds the event-timed
+    figure above is bounded by the host's launch rate instead. None when the capture is not possible."""
+    import torch
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()  # the library sets up this stream's status block and workspace outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(launches):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (replays * launches)
+    except Exception:  # an extra figure: never lose the line over it
+        torch.cuda.synchronize()
+        return None
+
+
 def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches: int = 20):
     """Device-timed figures for the remaining single-GPU configs. Per workload: our kernel (the config the
     operator picks) and cuBLAS (``torch.matmul`` on the device, a comparison) timed the same way - median of
@@ -246,10 +276,11 @@ def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches:
                          ("c2 fp32 4096^3 FFMA SIMT", 4096, 4096, 4096, f32, "uniform", simt)]),
         ("square bf16", [("c3 bf16 8192^3", 8192, 8192, 8192, bf16, "normal", None)]),
     ]
-    for nk in (4096, 11008):
-        for (edt, tdt), tag in ((bf16, "bf16"), (f32, "fp32")):
-            groups.append((f"c4 {tag} N=K={nk}",
-                           [(f"c4 {tag} {m}x{nk}x{nk}", m, nk, nk, (edt, tdt), "uniform", None) for m in (128, 512, 2048)]))
+    for n in (4096, 11008):
+        for k in (4096, 11008):
+            for (edt, tdt), tag in ((bf16, "bf16"), (f32, "fp32")):
+                groups.append((f"c4 {tag} N={n} K={k}",
+                               [(f"c4 {tag} {m}x{n}x{k}", m, n, k, (edt, tdt), "uniform", None) for m in (128, 512, 2048)]))
     dev = f"cuda:{device}"
     out, group_clocks = [], []
     torch.backends.cuda.matmul.allow_tf32 = False  # the cuBLAS comparison of fp32 data is a true fp32 GEMM
@@ -279,10 +310,13 @@ def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches:
 
                 ts = sorted(time_launches(ours, launches, 3))
                 kern.checkStatus()
+                g_ours = time_graph(ours, launches)
+                kern.checkStatus()
                 a0, b0, c0 = sets[0]
                 kern.run(a0, b0, c0)
                 mine = c0.clone()
                 tl = sorted(time_launches(cublas, launches, 3))
+                g_lib = time_graph(cublas, launches)
                 torch.matmul(a0, b0, out=c0)
                 scale = c0.float().abs().max().clamp_min(1e-30)
                 diff = float(((mine.float() - c0.float()).abs().max() / scale).item())
@@ -303,6 +337,9 @@ def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches:
                                                  f"{peaks['source']} bf16_tflops") +
                                                 (f", capped by AI x {peaks['source']} hbm_gbs" if bound == "hbm" else "")},
                     "cublas_tflops": round(flops / (lib_med * 1e9), 1), "vs_cublas": round(lib_med / med, 3),
+                    "graph_replay": None if (g_ours is None or g_lib is None) else {
+                        "ms": round(g_ours, 4), "tflops": round(flops / (g_ours * 1e9), 1),
+                        "cublas_ms": round(g_lib, 4), "vs_cublas": round(g_lib / g_ours, 3)},
                     "max_diff_vs_cublas_rel": diff,
                     "tile": f"{kpm.BLOCK_SIZE_M}x{kpm.BLOCK_SIZE_N}x{kpm.BLOCK_SIZE_K}", "split_k": int(kpm.LOCAL_SPLIT_U),
                     "kernel_variant": variant, "launches": launches,

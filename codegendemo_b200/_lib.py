@@ -22,7 +22,7 @@ E_BAD_CONFIG, E_COMPILE, E_NO_DRIVER, E_IO, E_DEVICE_TIMEOUT, E_BAD_ARG, E_TOO_L
 EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
-    "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_strided", "kcg_softmax_rows",
+    "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_strided", "kcg_softmax_rows", "kcg_softmax_rows_ex",
     "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
     "kcg_peer_free", "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
     "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
@@ -51,7 +51,7 @@ class KernelInfo(ctypes.Structure):
 
     _SCALARS = ("smem_bytes", "kernel", "dtype", "bm", "bn", "bk", "stages", "splitk", "group",
                 "atrans", "m", "n", "k")
-    _RESERVED = {"num_sms": 0, "b_trans": 1}  # named slots of `reserved`
+    _RESERVED = {"num_sms": 0, "b_trans": 1, "serpentine": 2, "dtype_c": 3}  # named slots of `reserved`
 
     def to_dict(self) -> dict:
         """Plain, picklable form (compile workers hand it to the process that owns the GPU)."""
@@ -85,7 +85,7 @@ class CompileOpts(ctypes.Structure):
     """``kcg_compile_opts``."""
     _fields_ = [("kernel", ctypes.c_int32), ("num_stages", ctypes.c_int32),
                 ("num_sms", ctypes.c_int32), ("force", ctypes.c_int32), ("b_trans", ctypes.c_int32),
-                ("reserved", ctypes.c_int32 * 3)]
+                ("serpentine", ctypes.c_int32), ("reserved", ctypes.c_int32 * 2)]
 
 
 class Epilogue(ctypes.Structure):
@@ -145,6 +145,9 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_softmax_rows.argtypes = [ctypes.c_int, u64, u64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64,
                                      ctypes.c_float, ctypes.c_int]
     lib.kcg_softmax_rows.restype = ctypes.c_int
+    lib.kcg_softmax_rows_ex.argtypes = [ctypes.c_int, u64, u64, ctypes.c_int, ctypes.c_int64, u64, ctypes.c_int,
+                                        ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_float]
+    lib.kcg_softmax_rows_ex.restype = ctypes.c_int
     lib.kcg_peer_alloc.argtypes = [ctypes.c_int, u64, ctypes.POINTER(u64), ctypes.c_char_p]
     lib.kcg_peer_open.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(u64)]
     lib.kcg_peer_close.argtypes = [ctypes.c_int, u64]

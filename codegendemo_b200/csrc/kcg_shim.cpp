@@ -245,6 +245,8 @@ struct Resolved {
   int stages = 0;
   int num_sms = 148;
   int btrans = 0;
+  int serpentine = 0;
+  int out_f32 = 0;  // DATATYPE_C = float32 with 16-bit A and B
 };
 
 // The reference's KernelArgMatmul.check() (Operators/matmul.py:180-194) for the
@@ -290,8 +292,12 @@ int simt_smem_bytes(const Cfg& c) {
 int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
   const int dt = c[KCG_CFG_DATATYPE_A];
   if (!dtype_str(dt)) return fail(KCG_E_BAD_CONFIG, "unsupported DATATYPE_A %d (2 float16, 4 float32, 62 bfloat16)", dt);
-  if (c[KCG_CFG_DATATYPE_B] != dt || c[KCG_CFG_DATATYPE_C] != dt)
-    return fail(KCG_E_BAD_CONFIG, "DATATYPE_A/B/C must be equal");
+  // A, B and C share one type, with one exception: fp16 / bf16 operands with a float32 C (the fp32
+  // accumulators stored unrounded) on the single-pass tcgen05 kernels.
+  const bool out_f32 = dt != KCG_DTYPE_FLOAT32 && c[KCG_CFG_DATATYPE_C] == KCG_DTYPE_FLOAT32;
+  if (c[KCG_CFG_DATATYPE_B] != dt || (c[KCG_CFG_DATATYPE_C] != dt && !out_f32))
+    return fail(KCG_E_BAD_CONFIG, "DATATYPE_A/B/C must be equal (or C float32 with 16-bit A and B)");
+  r->out_f32 = out_f32 ? 1 : 0;
   const int bm = c[KCG_CFG_BLOCK_SIZE_M], bn = c[KCG_CFG_BLOCK_SIZE_N], bk = c[KCG_CFG_BLOCK_SIZE_K];
   const int M = c[KCG_CFG_M_SIZE], N = c[KCG_CFG_N_SIZE], K = c[KCG_CFG_K_SIZE];
   if (bm <= 0 || bn <= 0 || bk <= 0 || M <= 0 || N <= 0 || K <= 0)
@@ -314,7 +320,15 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     want = (kcg::tc_config_error(dt, bm, bn, bk, st, 1) == 0) ? KCG_KERNEL_TCGEN05 : KCG_KERNEL_SIMT;
   }
   r->kernel = want;
+  if (r->out_f32 && !(want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TCGEN05_PAIR))
+    return fail(KCG_E_BAD_CONFIG, "a float32 C with 16-bit A and B needs a single-pass tcgen05 kernel (KERNEL_VARIANT 2 or 4)");
   r->btrans = (opts && opts->b_trans) ? 1 : 0;
+  r->serpentine = (opts && opts->serpentine) ? 1 : 0;
+  if (r->serpentine && !(want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TF32X1 || want == KCG_KERNEL_TCGEN05_PAIR ||
+                         want == KCG_KERNEL_TCGEN05_CLUSTERK))
+    return fail(KCG_E_BAD_CONFIG, "the serpentine raster belongs to the tcgen05 kernels' tile walk");
+  if (r->serpentine && c[KCG_CFG_BLOCK_MAPPING] < 2)
+    return fail(KCG_E_BAD_CONFIG, "the serpentine raster needs BLOCK_MAPPING >= 2 (rows per group)");
   if (r->btrans) {
     const bool single_pass16 = (want == KCG_KERNEL_TCGEN05 || want == KCG_KERNEL_TCGEN05_PAIR) && dt != KCG_DTYPE_FLOAT32;
     if (!single_pass16)
@@ -360,7 +374,7 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if (!ok(st))
       return fail(KCG_E_BAD_CONFIG,
                   "tile 128x%dx%d / %d stages / LOCAL_SPLIT_U %d not buildable by the cluster split-K kernel (rule %d: "
-                  "fp16 / bf16, split 2, 4 or 8, BLOCK_SIZE_N a multiple of 32 * split, ring >= 512 * BLOCK_SIZE_N bytes)",
+                  "fp16 / bf16, split 2..8 and at most BLOCK_SIZE_N / 32, ring large enough for the received slices)",
                   bn, bk, st, split, kcg::ck_config_error(dt, bn, bk, st, split));
     if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
     r->stages = st;
@@ -401,6 +415,7 @@ std::string kernel_name(const Cfg& c, const Resolved& r) {
   ss << "RC" << c[KCG_CFG_REDUCE_C_CONTINUOUS] << "_";
   ss << "ST" << r.stages << "_V" << r.kernel;
   if (r.btrans) ss << "_BT1";
+  if (r.serpentine) ss << "_SP1";
   return ss.str();
 }
 
@@ -549,6 +564,8 @@ std::vector<std::string> macro_flags(const Cfg& c, const Resolved& r, const std:
   // accumulator drain with the next tile's main loop
   D("REGP", c[KCG_CFG_REG_PREFETCH] ? 1 : 0);
   D("BTRANS", r.btrans);
+  D("SERPENTINE", r.serpentine);
+  D("OUT_F32", r.out_f32);
   return f;
 }
 
@@ -557,6 +574,13 @@ int run_nvcc(const std::string& nvcc, const std::vector<std::string>& flags, con
   std::vector<std::string> args = {nvcc, "-cubin", "-gencode", "arch=compute_100a,code=sm_100a", "-O3",
                                    "-std=c++17", "-lineinfo", "-I" + kernel_src_dir()};
   args.insert(args.end(), flags.begin(), flags.end());
+  // KCG_NVCC_FLAGS: extra flags for experiments (e.g. -DKCG_TIMELINE=1 -Xptxas -v). The cubin cache is
+  // keyed by kernel name and source text only, so point KCG_CACHE_DIR elsewhere when using it.
+  if (const char* extra = getenv("KCG_NVCC_FLAGS")) {
+    std::stringstream es(extra);
+    std::string tok;
+    while (es >> tok) args.push_back(tok);
+  }
   args.push_back("-o");
   args.push_back(out);
   args.push_back(kernel_src_dir() + "/gemm_entry.cu");
@@ -640,6 +664,8 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
   out->k = K;
   out->reserved[0] = r.num_sms;
   out->reserved[1] = r.btrans;
+  out->reserved[2] = r.serpentine;
+  out->reserved[3] = r.out_f32 ? KCG_DTYPE_FLOAT32 : 0;
   return 0;
 }
 
@@ -1034,6 +1060,8 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   // C is M x N. A leading dimension larger than the row length addresses a sub-matrix of a wider
   // array; in a batched launch the batches still follow one another row after row at that pitch.
   const int btrans = info->reserved[1] ? 1 : 0;
+  const int dtype_c = info->reserved[3] ? info->reserved[3] : info->dtype;  // C may be float32 over 16-bit operands
+  const int eb_c = (dtype_c == KCG_DTYPE_FLOAT32) ? 4 : 2;
   const int64_t row_a = info->atrans ? Mb : K, row_b = btrans ? K : N, row_c = N;
   const int64_t lda = ld.lda ? ld.lda : row_a, ldb = ld.ldb ? ld.ldb : row_b, ldc = ld.ldc ? ld.ldc : row_c;
   if (lda < row_a || ldb < row_b || ldc < row_c)
@@ -1041,7 +1069,7 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
                 (long long)lda, (long long)ldb, (long long)ldc, (long long)row_a, (long long)row_b, (long long)row_c);
   if (lda > 0x7fffffff || ldb > 0x7fffffff || ldc > 0x7fffffff)
     return fail(KCG_E_TOO_LARGE, "leading dimensions must fit 31 bits");
-  if ((lda * eb) % 16 || (ldb * eb) % 16 || (ldc * eb) % 16)
+  if ((lda * eb) % 16 || (ldb * eb) % 16 || (ldc * eb_c) % 16)
     return fail(KCG_E_BAD_ARG, "leading dimensions must keep every row 16-byte aligned");
   if ((ld.lda || ld.ldb || ld.ldc) && n_peers > 0)
     return fail(KCG_E_BAD_ARG, "the fused all-gather takes contiguous operands");
@@ -1097,7 +1125,7 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
     // 128B-swizzled staging buffers; the 3xTF32 kernel stores from registers.
     const bool x3 = eb == 4 && info->kernel != KCG_KERNEL_TF32X1;
     if (!x3) {
-      if (int e = encode_map(s, &p.tmC, info->dtype, C, N, M, static_cast<uint64_t>(ldc) * eb, 128 / eb, 32,
+      if (int e = encode_map(s, &p.tmC, dtype_c, C, N, M, static_cast<uint64_t>(ldc) * eb_c, 128 / eb_c, 32,
                              3 /*CU_TENSOR_MAP_SWIZZLE_128B*/))
         return e;
     }
@@ -1202,8 +1230,9 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
   DeviceState* s = nullptr;
   if (int e = ensure_device(device, &s)) return e;
   const size_t eb = (info->dtype == KCG_DTYPE_FLOAT32) ? 4 : 2;
+  const size_t eb_c = (info->reserved[3] == KCG_DTYPE_FLOAT32) ? 4 : eb;
   const size_t bytes[3] = {static_cast<size_t>(info->m) * info->k * eb, static_cast<size_t>(info->k) * info->n * eb,
-                           static_cast<size_t>(info->m) * info->n * eb};
+                           static_cast<size_t>(info->m) * info->n * eb_c};
   {
     std::lock_guard<std::mutex> g(g_dev_mutex);
     for (int i = 0; i < 3; ++i)
@@ -1276,7 +1305,7 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
   size_t row0 = 0;
   for (int i = 0; i < nslabs && rc == 0; ++i) {
     const size_t rows = static_cast<size_t>(base_tiles + (i < extra ? 1 : 0)) * bm;
-    const size_t a_off = row0 * info->k * eb, c_off = row0 * info->n * eb;
+    const size_t a_off = row0 * info->k * eb, c_off = row0 * info->n * eb_c;
     if (!step(d.p_cuMemcpyHtoDAsync(s->hbuf[0] + a_off, static_cast<const char*>(hostA) + a_off, rows * info->k * eb,
                                     s_in), "cuMemcpyHtoDAsync(A)"))
       break;
@@ -1289,7 +1318,7 @@ int kcg_matmul_host(uint64_t function, const kcg_kernel_info* info, int device, 
     if (rc != 0) break;
     if (!step(d.p_cuEventRecord(s->hevents[2 * i + 1], s_exec), "cuEventRecord")) break;
     if (!step(d.p_cuStreamWaitEvent(s_out, s->hevents[2 * i + 1], 0), "cuStreamWaitEvent")) break;
-    if (!step(d.p_cuMemcpyDtoHAsync(static_cast<char*>(hostC) + c_off, s->hbuf[2] + c_off, rows * info->n * eb, s_out),
+    if (!step(d.p_cuMemcpyDtoHAsync(static_cast<char*>(hostC) + c_off, s->hbuf[2] + c_off, rows * info->n * eb_c, s_out),
               "cuMemcpyDtoHAsync(C)"))
       break;
     row0 += rows;

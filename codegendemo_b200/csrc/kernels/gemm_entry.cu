@@ -24,6 +24,10 @@
 #ifndef KCG_BTRANS
 #define KCG_BTRANS 0
 #endif
+// DATATYPE_C = float32 with 16-bit A and B (single-pass tcgen05 kernels): C keeps the fp32 accumulators
+#ifndef KCG_OUT_F32
+#define KCG_OUT_F32 0
+#endif
 
 #if KCG_DTYPE == KCG_DT_F32
 #define KCG_T float
@@ -47,7 +51,7 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 }
 #elif KCG_VARIANT == KCG_VARIANT_TCGEN05 || KCG_VARIANT == KCG_VARIANT_TF32X1
 #include "gemm_tcgen05.cuh"
-using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 0, KCG_ACC_OVERLAP, KCG_BTRANS>;
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 0, KCG_ACC_OVERLAP, KCG_BTRANS, KCG_OUT_F32>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);
@@ -64,7 +68,7 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 }
 #elif KCG_VARIANT == KCG_VARIANT_TCGEN05_PAIR
 #include "gemm_tcgen05.cuh"
-using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 1, KCG_ACC_OVERLAP, KCG_BTRANS>;
+using Gemm = kcg::TcGemm<KCG_DTYPE, KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, 1, KCG_ACC_OVERLAP, KCG_BTRANS, KCG_OUT_F32>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);

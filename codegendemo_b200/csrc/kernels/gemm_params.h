@@ -217,14 +217,14 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
 // (128 x BN x 4 bytes), so the ring must be at least that large; no TMA-store staging.
 constexpr int ck_config_error(int dtype, int BN, int BK, int stages, int split) {
   if (!(dtype == KCG_DT_F16 || dtype == KCG_DT_BF16)) return 1;
-  if (!(split == 2 || split == 4 || split == 8)) return 2;
-  if (BN < 64 || BN > 256 || (BN % 64) != 0 || (BN % (32 * split)) != 0) return 3;
+  if (split < 2 || split > 8) return 2;  // a portable cluster has at most 8 CTAs
+  if (BN < 64 || BN > 256 || (BN % 64) != 0 || BN / 32 < split) return 3;
   const int rowb = BK * 2;
   if (!(rowb == 32 || rowb == 64 || (rowb % 128) == 0) || rowb > 512 || (BK % 16) != 0) return 5;
   if (stages < 2 || stages > 12) return 7;
   const int ring = (128 + BN) * BK * 2 * stages;
   if (ring + 2048 > 227 * 1024) return 8;
-  if (ring < 128 * BN * 4) return 10;
+  if (ring < split * ((BN / 32 + split - 1) / split) * 128 * 128) return 10;  // kSplit slices of whole 32-column blocks
   return 0;
 }
 constexpr int ck_smem_bytes(int BN, int BK, int stages) { return (128 + BN) * BK * 2 * stages + 2048; }

@@ -58,8 +58,11 @@ namespace kcg {
 //
 // kBTrans = 1: B is stored N x K row-major (C = A * Bt^T, the "NT" product: Q * K^T of attention
 // without a transposed copy of K); the B tile is then a K-major operand like a K-major A tile.
+//
+// kOutF32 = 1 (DATATYPE_C = float32 with 16-bit A and B): C is written as fp32, the accumulators
+// unrounded - e.g. attention scores, whose rounding to bf16 would be amplified by the softmax's exp.
 template <int kDType, int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK,
-          int kGroup, int kPair = 0, int kAccOverlap = 1, int kBTrans = 0>
+          int kGroup, int kPair = 0, int kAccOverlap = 1, int kBTrans = 0, int kOutF32 = 0>
 struct TcGemm {
   static constexpr int NCTA = kPair ? 2 : 1;
   static constexpr int R = kBM / NCTA;    // rows of the tile held by one CTA
@@ -86,7 +89,8 @@ struct TcGemm {
   static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS + 32 * NUM_PUSH_WARPS;
   static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, R, BNL, kBK, kStages, 0);
   static constexpr int STG_BYTES = 32 * 128;       // one staging buffer: 32 rows x 128 bytes
-  static constexpr int SCOLS = 128 / (kDType == KCG_DT_F32 ? 4 : 2);  // C columns per staging buffer
+  static constexpr bool kOut32 = (kDType == KCG_DT_F32) || kOutF32;  // C holds fp32
+  static constexpr int SCOLS = 128 / (kOut32 ? 4 : 2);  // C columns per staging buffer
   static_assert(8 * STG_BYTES == tc_staging_bytes(kDType, 0), "staging size out of step with the host");
   static_assert(kBN % SCOLS == 0, "tile width must be a multiple of the staging width");
   static constexpr uint32_t FMT = (kDType == KCG_DT_F32)    ? FMT_TF32
@@ -104,11 +108,19 @@ struct TcGemm {
     volatile uint32_t abort_flag;
     uint32_t last_flag;
     uint32_t push_count;  // epilogue warps that have finished (and completed the stores of) a whole-K tile
+#ifdef KCG_TIMELINE
+    uint64_t tl[16];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
+#endif
   };
+#ifdef KCG_TIMELINE
+#define KCG_TL(i) bars->tl[i] = global_timer_ns()
+#else
+#define KCG_TL(i) ((void)0)
+#endif
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
   using Unit = WorkUnit;
-  using Iter = WorkIter<kBM, kBN, kGroup>;  // units of this CTA (pair), in order: work_iter.cuh
+  using Iter = WorkIter<kBM, kBN, kGroup, KCG_SERPENTINE>;  // units of this CTA (pair), in order: work_iter.cuh
 
   __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
                                                 uint32_t code, uint32_t d0, uint32_t d1) {
@@ -121,13 +133,14 @@ struct TcGemm {
   }
 
   __device__ static void run(const KcgGemmParams& p) {
-    using OutT = typename std::conditional<kTf32, float,
+    using OutT = typename std::conditional<kOut32, float,
                  typename std::conditional<kDType == KCG_DT_BF16, __nv_bfloat16, __half>::type>::type;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Tiles need 1024-byte alignment (128B swizzle repeat); the launch asks for 1 KiB of slack.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
+    if (threadIdx.x == 0) KCG_TL(0);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -137,6 +150,9 @@ struct TcGemm {
     const int first_split = p.split_first_tile;
 
     if (threadIdx.x == 0) {
+      // the first TMA instruction needs its descriptor: start fetching the maps before anything else
+      tma_prefetch_desc(&p.tmA);
+      tma_prefetch_desc(&p.tmB);
       for (int s = 0; s < kStages; ++s) {
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
@@ -151,6 +167,91 @@ struct TcGemm {
       fence_mbar_init();
       fence_proxy_async_smem();
     }
+    const uint32_t rank = kPair ? cluster_cta_rank() : 0u;  // 0 = leader
+    const int unit0 = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int unit_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int row_base = static_cast<int>(rank) * R;     // this CTA's first row inside the tile
+    const int bcol_base = static_cast<int>(rank) * BNL;  // this CTA's first B column inside the tile
+
+    // ---- producer state (thread 0). The loop below is entered twice: once before the set-up barrier
+    // for the first ring of stages (their `empty` waits pass at once on fresh barriers, and a single CTA's
+    // loads signal only its own barriers, which this very thread has just initialised), so that the
+    // first operands are already in flight while TMEM is allocated; and again, to the end, as warp 0's role.
+    Iter p_units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
+    Unit p_w;
+    uint32_t p_it = 0;
+    int p_kb = 0;
+    bool p_have = false, p_ok = true;
+    auto produce = [&](uint32_t it_limit) {
+      while (p_ok && p_have && p_it < it_limit) {
+        if (p_kb >= p_w.kbn) {
+          p_kb = 0;
+          p_have = p_units.next(p_w);
+          continue;
+        }
+        const uint32_t s = p_it % kStages;
+        const uint32_t ph = (p_it / kStages) & 1u;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
+          report(p, bars, KCG_ST_TIMEOUT_PRODUCER, p_it, s);
+          p_ok = false;
+          break;
+        }
+        const Unit& w = p_w;
+        uint8_t* sa = smem + s * STAGE_BYTES;
+        uint8_t* sb = sa + L.a_bytes;
+        const int k0 = (w.kb0 + p_kb) * kBK;
+        // K x M storage: the batch selects K rows and M is counted inside the batch
+        const int am0 = (kATrans ? w.mcol : w.m0) + row_base, bn0 = w.n0 + bcol_base;
+        const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
+        if constexpr (kPair) {
+          // completion bytes of both CTAs land on the leader's barrier
+          const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[s]), 0u);
+          if (rank == 0u) mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(2 * STAGE_HI));
+#pragma unroll
+          for (int j = 0; j < L.a_boxes; ++j) {
+            if constexpr (kATrans) {
+              tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, am0 + j * L.atom, ka);
+            } else {
+              tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, ka + j * L.a_box_inner, am0);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < L.b_boxes; ++j) {
+            if constexpr (kBTrans) {  // N x K storage: the batch selects N rows
+              tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, k0 + j * L.b_box_inner,
+                               bn0 + w.nofs);
+            } else {
+              tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, kb_row);
+            }
+          }
+        } else {
+          mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
+#pragma unroll
+          for (int j = 0; j < L.a_boxes; ++j) {
+            if constexpr (kATrans) {
+              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
+            } else {
+              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < L.b_boxes; ++j) {
+            if constexpr (kBTrans) {
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], k0 + j * L.b_box_inner, bn0 + w.nofs);
+            } else {
+              tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, kb_row);
+            }
+          }
+        }
+        if (p_it == 0) KCG_TL(2);
+        ++p_it;
+        ++p_kb;
+      }
+    };
+    if (threadIdx.x == 0) {
+      p_have = p_units.next(p_w);
+      if constexpr (!kPair) produce(static_cast<uint32_t>(kStages));
+    }
     if (warp == 1) {
       if constexpr (kPair) {
         tmem_alloc_pair(&bars->tmem_base, TMEM_COLS);
@@ -160,84 +261,17 @@ struct TcGemm {
         tmem_relinquish();
       }
     }
+    __syncwarp();  // thread 0 rejoins its warp before the block-wide barrier
     tc_fence_before_sync();
     __syncthreads();
     if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anyone signals them
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
-    const uint32_t rank = kPair ? cluster_cta_rank() : 0u;  // 0 = leader
-    const int unit0 = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-    const int unit_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-    const int row_base = static_cast<int>(rank) * R;     // this CTA's first row inside the tile
-    const int bcol_base = static_cast<int>(rank) * BNL;  // this CTA's first B column inside the tile
+    if (threadIdx.x == 0) KCG_TL(1);
 
     if (warp == 0) {
       // ------------------------------------------------------------ producer
-      if (lane == 0) {
-        tma_prefetch_desc(&p.tmA);
-        tma_prefetch_desc(&p.tmB);
-        uint32_t it = 0;
-        bool ok = true;
-        Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
-        Unit w;
-        while (ok && units.next(w)) {
-          for (int kb = 0; kb < w.kbn; ++kb, ++it) {
-            const uint32_t s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1u;
-            if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
-              report(p, bars, KCG_ST_TIMEOUT_PRODUCER, it, s);
-              ok = false;
-              break;
-            }
-            uint8_t* sa = smem + s * STAGE_BYTES;
-            uint8_t* sb = sa + L.a_bytes;
-            const int k0 = (w.kb0 + kb) * kBK;
-            // K x M storage: the batch selects K rows and M is counted inside the batch
-            const int am0 = (kATrans ? w.mcol : w.m0) + row_base, bn0 = w.n0 + bcol_base;
-            const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
-            if constexpr (kPair) {
-              // completion bytes of both CTAs land on the leader's barrier
-              const uint32_t full_leader = map_to_cta(smem_u32(&bars->full[s]), 0u);
-              if (rank == 0u) mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(2 * STAGE_HI));
-#pragma unroll
-              for (int j = 0; j < L.a_boxes; ++j) {
-                if constexpr (kATrans) {
-                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, am0 + j * L.atom, ka);
-                } else {
-                  tma_load_2d_pair(sa + j * L.a_box_bytes, &p.tmA, full_leader, ka + j * L.a_box_inner, am0);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < L.b_boxes; ++j) {
-                if constexpr (kBTrans) {  // N x K storage: the batch selects N rows
-                  tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, k0 + j * L.b_box_inner,
-                                   bn0 + w.nofs);
-                } else {
-                  tma_load_2d_pair(sb + j * L.b_box_bytes, &p.tmB, full_leader, bn0 + j * L.atom, kb_row);
-                }
-              }
-            } else {
-              mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_HI));
-#pragma unroll
-              for (int j = 0; j < L.a_boxes; ++j) {
-                if constexpr (kATrans) {
-                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
-                } else {
-                  tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < L.b_boxes; ++j) {
-                if constexpr (kBTrans) {
-                  tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], k0 + j * L.b_box_inner, bn0 + w.nofs);
-                } else {
-                  tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], bn0 + j * L.atom, kb_row);
-                }
-              }
-            }
-          }
-        }
-      }
+      if (lane == 0) produce(0xffffffffu);
     } else if (warp == 1) {
       // -------------------------- MMA issuer (in a pair: the leader CTA only)
       if (lane == 0 && rank == 0u) {
@@ -341,9 +375,11 @@ struct TcGemm {
               break;
             }
             tc_fence_after_sync();
+            if (it == 0) KCG_TL(3);
             issue(s, kb, 0, MT, tmem_acc);
             free_stage(s);
           }
+          if (acc_it == 0) KCG_TL(4);
           if (ok) {
             if constexpr (kPair) {
               umma_commit_pair(smem_u32(&bars->tmem_full[ab]));
@@ -435,6 +471,7 @@ struct TcGemm {
           break;
         }
         tc_fence_after_sync();
+        if (warp == 2 && lane == 0 && acc_it == 0) KCG_TL(5);
         const uint32_t tmem_acc = tmem_base + ab * ACC_COLS + (static_cast<uint32_t>(q * 32) << 16);
         // This warp has read all it needs of accumulator buffer (or, in HALF mode, accumulator) `idx`.
         auto release = [&](uint32_t idx) {
@@ -560,6 +597,7 @@ struct TcGemm {
           }
         }
         if constexpr (!HALF) release(ab);
+        if (warp == 2 && lane == 0 && acc_it == 0) KCG_TL(6);
 
         if (w.nsplit > 1) {
           // Publish this split's partial tile; the last split to arrive sums all
@@ -651,11 +689,18 @@ struct TcGemm {
           named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit
         }
       }
-      if (lane == 0) tma_store_wait_all<0>();  // staging is read and C written before the CTA exits
+      // The staging buffers must have been read before the CTA gives its shared memory back; the
+      // writes themselves complete with the kernel (the fused all-gather's push warps are told about
+      // written tiles earlier, tile by tile).
+      if (lane == 0) tma_store_wait_read<0>();
+      if (warp == 2 && lane == 0) KCG_TL(7);
       if (p.n_peers > 0) __threadfence_system();  // peer stores ordered before the kernel's completion
     }
 
     // ------------------------------------------------------------ common exit
+    // The producer and MMA roles run in one lane; the other lanes of those warps come straight here.
+    // Reconverge every warp first: the block-wide barrier below must be executed by whole warps.
+    __syncwarp();
     if (bars->abort_flag != 0u) {
       // Give copies / MMAs still in flight time to land before shared memory
       // and TMEM are released.
@@ -668,6 +713,7 @@ struct TcGemm {
       __syncwarp();
       cluster_sync_all();  // the peer's shared memory and TMEM stay valid until both CTAs are done
     }
+    if (threadIdx.x == 0) KCG_TL(8);
     if (warp == 1) {
       __syncwarp();
       tc_fence_after_sync();
@@ -675,7 +721,13 @@ struct TcGemm {
         tmem_dealloc_pair(tmem_base, TMEM_COLS);
       } else
         tmem_dealloc(tmem_base, TMEM_COLS);
+      if (lane == 0) KCG_TL(9);
     }
+#ifdef KCG_TIMELINE
+    __syncthreads();
+    if (threadIdx.x == 0 && blockIdx.x == 0)
+      for (int i = 0; i < 10; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
+#endif
   }
 };
 

@@ -4,7 +4,8 @@
 // A cluster of kSplit CTAs owns ONE 128 x kBN output tile. CTA r of the cluster multiplies the
 // r-th of kSplit equal K ranges with the usual pipeline (warp 0 TMA producer, warp 1 tcgen05.mma
 // issuer, fp32 accumulator in TMEM), so kSplit times as many SMs stream B as there are tiles.
-// The partial tiles never touch global memory: the tile's columns are cut into kSplit slices,
+// The partial tiles never touch global memory: the tile's columns are cut into kSplit slices
+// (runs of 32-column blocks, lengths differing by at most one, so any kSplit from 2 to 8 works),
 // every CTA sends slice j of its accumulator to CTA j through distributed shared memory
 // (st.shared::cluster), and CTA j adds the kSplit slices it received in rank order (bitwise
 // reproducible) and stores its slice of C. No workspace, no counters, no waits between
@@ -45,10 +46,14 @@ struct TcGemmClusterK {
   static constexpr int KSTEPS = kBK / UMMA_K;
   static constexpr int STAGE_BYTES = L.stage_hi_bytes;
   static constexpr int TMEM_COLS = kc_pow2_ceil(kBN);
-  static constexpr int W = kBN / kSplit;   // columns of the tile this CTA reduces and stores
-  static constexpr int CB = W / 32;        // 32-column blocks per slice
-  static constexpr int BLOCK_BYTES = 128 * 128;          // one 32-column block: 128 rows x 128 bytes
-  static constexpr int SLICE_BYTES = CB * BLOCK_BYTES;   // one source rank's slice
+  // The tile's kBN / 32 column blocks of 32 are dealt to the kSplit CTAs in contiguous runs whose
+  // lengths differ by at most one: block c belongs to CTA c * kSplit / NCH.
+  static constexpr int NCH = kBN / 32;
+  static constexpr int CB = (NCH + kSplit - 1) / kSplit;  // most 32-column blocks one CTA owns
+  static constexpr int BLOCK_BYTES = 128 * 128;           // one 32-column block: 128 rows x 128 bytes
+  static constexpr int SLICE_BYTES = CB * BLOCK_BYTES;    // room for one source rank's slice
+  __host__ __device__ static constexpr int owner_of(int c) { return c * kSplit / NCH; }
+  __host__ __device__ static constexpr int first_block_of(int r) { return (r * NCH + kSplit - 1) / kSplit; }
   static constexpr int NUM_EPI_THREADS = 128;
   static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
   static constexpr int SMEM_BYTES = ck_smem_bytes(kBN, kBK, kStages);
@@ -64,7 +69,15 @@ struct TcGemmClusterK {
     uint64_t recv_full;     // all slices for this CTA have arrived (4 warps of each of kSplit CTAs)
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+#ifdef KCG_TIMELINE
+    uint64_t tl[16];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
+#endif
   };
+#ifdef KCG_TIMELINE
+#define KCG_CTL(i) bars->tl[i] = global_timer_ns()
+#else
+#define KCG_CTL(i) ((void)0)
+#endif
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
   __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars, uint32_t code,
@@ -91,6 +104,10 @@ struct TcGemmClusterK {
     const int num_kb = (p.K + kBK - 1) / kBK;
 
     if (threadIdx.x == 0) {
+      KCG_CTL(0);
+      // the first TMA instruction needs its descriptor: start fetching the maps before anything else
+      tma_prefetch_desc(&p.tmA);
+      tma_prefetch_desc(&p.tmB);
       for (int s = 0; s < kStages; ++s) {
         mbar_init(&bars->full[s], 1);
         mbar_init(&bars->empty[s], 1);
@@ -102,20 +119,10 @@ struct TcGemmClusterK {
       fence_mbar_init();
       fence_proxy_async_smem();
     }
-    if (warp == 1) {
-      tmem_alloc(&bars->tmem_base, TMEM_COLS);
-      tmem_relinquish();
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();  // every CTA's barriers exist before anyone signals them
-    tc_fence_after_sync();
-    const uint32_t tmem_base = bars->tmem_base;
     const uint32_t rank = cluster_cta_rank();
-
     // This cluster's tile and this CTA's K range. The raster (and a batched launch's offsets) come
     // from the iterator the other tcgen05 kernels use.
-    WorkIter<kBM, kBN, kGroup> raster(p, 0, 1, tiles_m, tiles_n, num_kb);
+    WorkIter<kBM, kBN, kGroup, KCG_SERPENTINE> raster(p, 0, 1, tiles_m, tiles_n, num_kb);
     WorkUnit w;
     w.tile = static_cast<int>(blockIdx.x) / kSplit;
     raster.origin(w);
@@ -123,37 +130,56 @@ struct TcGemmClusterK {
     const int kb0 = static_cast<int>(rank) * per;
     const int kbn = (kb0 >= num_kb) ? 0 : ((num_kb - kb0 < per) ? num_kb - kb0 : per);
 
+    // Producer (thread 0), entered twice: before the set-up barriers for the first ring of stages - the
+    // loads signal only this CTA's own barriers, which this very thread has just initialised, so the first
+    // operands are in flight while TMEM is allocated and the cluster synchronises - and again as warp 0's role.
+    int p_kb = 0;
+    auto produce = [&](int kb_limit) {
+      for (; p_kb < kbn && p_kb < kb_limit; ++p_kb) {
+        const int kb = p_kb;
+        const uint32_t s = kb % kStages;
+        const uint32_t ph = (kb / kStages) & 1u;
+        if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
+          report(p, bars, KCG_ST_TIMEOUT_PRODUCER, kb, s);
+          p_kb = kbn;
+          break;
+        }
+        uint8_t* sa = smem + s * STAGE_BYTES;
+        uint8_t* sb = sa + L.a_bytes;
+        const int k0 = (kb0 + kb) * kBK;
+        const int am0 = kATrans ? w.mcol : w.m0;
+        const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
+        mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_BYTES));
+#pragma unroll
+        for (int j = 0; j < L.a_boxes; ++j) {
+          if constexpr (kATrans) {
+            tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
+          } else {
+            tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < L.b_boxes; ++j)
+          tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, kb_row);
+        if (kb == 0) KCG_CTL(2);
+      }
+    };
+    if (threadIdx.x == 0) produce(kStages);
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    __syncwarp();  // thread 0 rejoins its warp before the block-wide barrier
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();  // every CTA's barriers exist before anyone signals them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+    if (threadIdx.x == 0) KCG_CTL(1);
+
     if (warp == 0) {
       // ------------------------------------------------------------ producer
-      if (lane == 0) {
-        tma_prefetch_desc(&p.tmA);
-        tma_prefetch_desc(&p.tmB);
-        for (int kb = 0; kb < kbn; ++kb) {
-          const uint32_t s = kb % kStages;
-          const uint32_t ph = (kb / kStages) & 1u;
-          if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
-            report(p, bars, KCG_ST_TIMEOUT_PRODUCER, kb, s);
-            break;
-          }
-          uint8_t* sa = smem + s * STAGE_BYTES;
-          uint8_t* sb = sa + L.a_bytes;
-          const int k0 = (kb0 + kb) * kBK;
-          const int am0 = kATrans ? w.mcol : w.m0;
-          const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
-          mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_BYTES));
-#pragma unroll
-          for (int j = 0; j < L.a_boxes; ++j) {
-            if constexpr (kATrans) {
-              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
-            } else {
-              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
-            }
-          }
-#pragma unroll
-          for (int j = 0; j < L.b_boxes; ++j)
-            tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, kb_row);
-        }
-      }
+      if (lane == 0) produce(kbn);
     } else if (warp == 1) {
       // ---------------------------------------------------------- MMA issuer
       if (lane == 0) {
@@ -185,6 +211,7 @@ struct TcGemmClusterK {
           }
           umma_commit(&bars->empty[s]);
         }
+        KCG_CTL(3);
         if (ok && kbn > 0) umma_commit(&bars->tmem_full);
       }
     } else {
@@ -199,6 +226,7 @@ struct TcGemmClusterK {
       if (!have_acc && !ok) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 0u, rank);
       if (have_acc) {
         tc_fence_after_sync();
+        if (epi_tid == 0) KCG_CTL(4);
         // This CTA's MMAs have retired (or it had none): its ring is free to receive slices.
         if (epi_tid == 0) {
           for (uint32_t j = 0; j < static_cast<uint32_t>(kSplit); ++j)
@@ -208,8 +236,8 @@ struct TcGemmClusterK {
         const uint32_t my_slot = smem_u32(smem) + rank * SLICE_BYTES + row * 128;
 #pragma unroll 1
         for (int c = 0; c < kBN / 32; ++c) {
-          const uint32_t owner = static_cast<uint32_t>(c / CB);
-          const int cbi = c % CB;
+          const uint32_t owner = static_cast<uint32_t>(owner_of(c));
+          const int cbi = c - first_block_of(static_cast<int>(owner));
           // the owner's ring is idle (its MMAs retired): our slice may overwrite it
           const bool free_ = mbar_wait(&bars->ring_free[owner], 0u, &bars->abort_flag);
           if (!__all_sync(0xffffffffu, free_)) {
@@ -230,6 +258,7 @@ struct TcGemmClusterK {
           for (int j = 0; j < 8; ++j)
             st_cluster_v4(dst + ((j ^ (row & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
+        if (epi_tid == 0) KCG_CTL(5);
         // Publish: every lane's stores are ordered before lane 0's release arrivals.
         fence_acq_rel_cluster();
         __syncwarp();
@@ -240,12 +269,14 @@ struct TcGemmClusterK {
         bool got = ok && mbar_wait_cluster(&bars->recv_full, 0u, &bars->abort_flag);
         const bool all_in = named_bar_all(2, NUM_EPI_THREADS, got);
         if (!all_in && ok && !got) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 2u, rank);
+        if (epi_tid == 0) KCG_CTL(6);
         if (all_in) {
-          // Add the kSplit slices in rank (= K) order and store this CTA's W columns of C.
+          // Add the kSplit slices in rank (= K) order and store this CTA's columns of C.
           OutT* Cout = reinterpret_cast<OutT*>(p.C);
-          constexpr int TOTAL = CB * 128 * 8;  // 16-byte units of one slice
+          const int c_first = first_block_of(static_cast<int>(rank));
+          const int total = (first_block_of(static_cast<int>(rank) + 1) - c_first) * 128 * 8;  // 16-byte units
 #pragma unroll 2
-          for (int idx = epi_tid; idx < TOTAL; idx += NUM_EPI_THREADS) {
+          for (int idx = epi_tid; idx < total; idx += NUM_EPI_THREADS) {
             const int u = idx & 7;
             const int rr = (idx >> 3) & 127;
             const int cbi = idx >> 10;
@@ -260,7 +291,7 @@ struct TcGemmClusterK {
               acc.w += x.w;
             }
             const int grow = w.m0 + rr;
-            const int gcol = w.n0 + static_cast<int>(rank) * W + cbi * 32 + u * 4;
+            const int gcol = w.n0 + (c_first + cbi) * 32 + u * 4;
             if (grow >= p.M || gcol >= p.N) continue;
             float o[4] = {acc.x, acc.y, acc.z, acc.w};
             if (p.epi_flags != 0u) epi_span<OutT, 4>(p, o, grow, gcol);
@@ -279,11 +310,15 @@ struct TcGemmClusterK {
     }
 
     // ------------------------------------------------------------ common exit
+    // The producer and MMA roles run in one lane; the other lanes of those warps come straight here.
+    // Reconverge every warp first: the block-wide barrier below must be executed by whole warps.
+    __syncwarp();
     if (bars->abort_flag != 0u) {
       // Give copies / MMAs still in flight time to land before shared memory and TMEM are released.
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
+    if (threadIdx.x == 64) KCG_CTL(7);
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();  // no CTA leaves while another may still write into its shared memory
@@ -291,7 +326,13 @@ struct TcGemmClusterK {
       __syncwarp();
       tc_fence_after_sync();
       tmem_dealloc(tmem_base, TMEM_COLS);
+      if (lane == 0) KCG_CTL(8);
     }
+#ifdef KCG_TIMELINE
+    __syncthreads();
+    if (threadIdx.x == 0 && blockIdx.x == 0)
+      for (int i = 0; i < 9; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
+#endif
   }
 };
 

@@ -83,7 +83,7 @@ struct TcGemmF32x3 {
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
   using Unit = WorkUnit;
-  using Iter = WorkIter<kBM, kBN, kGroup>;  // units of this CTA (pair), in order: work_iter.cuh
+  using Iter = WorkIter<kBM, kBN, kGroup, KCG_SERPENTINE>;  // units of this CTA (pair), in order: work_iter.cuh
 
   __device__ static __forceinline__ void report(const KcgGemmParams& p, Barriers* bars,
                                                 uint32_t code, uint32_t d0, uint32_t d1) {
@@ -480,6 +480,9 @@ struct TcGemmF32x3 {
     }
 
     // ------------------------------------------------------------ common exit
+    // The producer and MMA roles run in one lane; the other lanes of those warps come straight here.
+    // Reconverge every warp first: the block-wide barrier below must be executed by whole warps.
+    __syncwarp();
     if (bars->abort_flag != 0u) {
       const uint64_t t0 = global_timer_ns();
       while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);

@@ -29,6 +29,11 @@
 #define KCG_HD inline
 #endif
 
+// Raster variant of the translation unit (set by the compile entry; 0 unless asked for).
+#ifndef KCG_SERPENTINE
+#define KCG_SERPENTINE 0
+#endif
+
 namespace kcg {
 
 struct WorkUnit {
@@ -43,7 +48,10 @@ struct WorkUnit {
   int kb0, kbn; // first K block and number of K blocks
 };
 
-template <int kBM, int kBN, int kGroup>
+// kSerpentine = 1: inside a group, odd tile columns walk the group's rows upwards instead of
+// downwards (the reference's serpentine variant, matmul.cpp:1279-1287), so that consecutive
+// tiles of the walk always share a row block of A or a column block of B.
+template <int kBM, int kBN, int kGroup, int kSerpentine = 0>
 struct WorkIter {
   int u, stride, first_split, factor, num_units;
   int tiles_m, tiles_n, num_kb;
@@ -75,8 +83,9 @@ struct WorkIter {
       const int first_m = g * kGroup;
       const int gsz = (tiles_m - first_m < kGroup) ? (tiles_m - first_m) : kGroup;
       const int r = w.tile - g * per_group;
-      mb = first_m + (r % gsz);
       nb = r / gsz;
+      const int down = r % gsz;
+      mb = first_m + ((kSerpentine && (nb & 1)) ? gsz - 1 - down : down);
     } else {
       mb = w.tile / tiles_n;
       nb = w.tile - mb * tiles_n;

@@ -27,7 +27,7 @@ def getTempJsonFileName(startIndex: int, endIndex: int, outDir: str) -> str:
 
 def _tensor_core(cfg: Dict) -> bool:
     v = cfg.get(kw.KEY_KERNEL_VARIANT, 0)
-    if v in (2, 3, 4):
+    if v in (2, 3, 4, 5):
         return True
     if v == 1:
         return False
@@ -102,8 +102,23 @@ def _rules() -> List[Tuple[Tuple[str, ...], Callable[[Dict], bool]]]:
             return TuningSpaceChecker_Matmul.tcgen05_tile_ok(_per_cta(cfg))
         return v not in (2, 3) or TuningSpaceChecker_Matmul.tcgen05_tile_ok(cfg)
 
+    def clusterk(cfg):
+        # KERNEL_VARIANT 5: a cluster of LOCAL_SPLIT_U CTAs per 128-row tile of 16-bit data; every CTA owns whole
+        # 32-column blocks of the tile, and the operand ring (>= 2 stages) must hold the received slices
+        if cfg.get(kw.KEY_KERNEL_VARIANT, 0) != 5:
+            return True
+        dt = int(cfg.get(kw.KEY_DTYPE_A, cfg[kw.KEY_DTYPE_C]))
+        s, bn, bk = cfg[kw.KEY_LOCAL_SPLIT_U], cfg[kw.KEY_BLOCK_SIZE_N], cfg[kw.KEY_BLOCK_SIZE_K]
+        if dt % 30 != 2 or cfg[kw.KEY_BLOCK_SIZE_M] != 128 or not 2 <= s <= 8 or bn % 64 or bn // 32 < s:
+            return False
+        recv = s * -(-(bn // 32) // s) * 128 * 128
+        stage = (128 + bn) * bk * 2
+        stages = max(2, -(-recv // stage))
+        return stage * stages + 2048 <= 227 * 1024
+
     tile = (kw.KEY_BLOCK_SIZE_M, kw.KEY_BLOCK_SIZE_N, kw.KEY_BLOCK_SIZE_K, kw.KEY_DTYPE_C)
     return [
+        (tile + (kw.KEY_LOCAL_SPLIT_U,), clusterk),
         (tile, forced_tile),
         (tile + (kw.KEY_M, kw.KEY_N, kw.KEY_K), divides),
         (tile + (kw.KEY_WARP_LAYOUT_M, kw.KEY_WARP_LAYOUT_N, kw.KEY_WARP_SIZE), warp),
@@ -181,8 +196,78 @@ def iter_cfgs(param_options: Dict, dedupe_tensor_core: bool = True) -> Iterator[
     yield from rec(0)
 
 
+# ----------------------------------------------------------------------------- cost-model pre-filter
+# A B200 has 148 SMs; a persistent tcgen05 launch runs one CTA (or one CTA of a pair) per SM. The model below is
+# the launcher's own view of a config - how many work units it has, how many run at once, how long one takes -
+# reduced to three rates: tensor throughput per SM, operand delivery per SM, operand delivery of the whole L2.
+NUM_SMS = 148
+SM_MFLOP_PER_US = {"16bit": 10.0, "fp32x3": 1.4, "simt": 0.4}  # useful flop per microsecond per SM
+SM_LOAD_KB_PER_US = 90.0      # shared-memory fill rate one SM sustains through TMA from L2
+L2_LOAD_KB_PER_US = 7500.0    # all SMs together
+LAUNCH_US = 6.0               # prologue + first load + epilogue of any launch
+
+
+def estimate_us(cfg: Dict) -> float:
+    """Rough run time of a config from tiles, waves and bytes (no GPU needed). Only the ORDER of configs of
+    one shape matters: the pre-filter keeps those within a factor of the best estimate."""
+    dt = int(cfg.get(kw.KEY_DTYPE_A, cfg[kw.KEY_DTYPE_C]))
+    eb = dt % 30
+    M, N, K = cfg[kw.KEY_M], cfg[kw.KEY_N], cfg[kw.KEY_K]
+    bm, bn, bk = cfg[kw.KEY_BLOCK_SIZE_M], cfg[kw.KEY_BLOCK_SIZE_N], cfg[kw.KEY_BLOCK_SIZE_K]
+    variant = cfg.get(kw.KEY_KERNEL_VARIANT, 0)
+    split = max(1, cfg.get(kw.KEY_LOCAL_SPLIT_U, 1))
+    tiles = (M // bm) * (N // bn)
+    tc = _tensor_core(cfg) or variant == 5
+    if not tc:
+        # SIMT: one CTA per tile, LOCAL_SPLIT_U splits K inside the CTA; several CTAs share an SM
+        per_sm = max(1, min(8, (200 * 1024) // max(1, (bm + bn) * bk * eb * 2)))
+        waves = -(-tiles // (NUM_SMS * per_sm))
+        return LAUNCH_US + waves * per_sm * 2.0 * bm * bn * K / 1e6 / SM_MFLOP_PER_US["simt"]
+    pair = variant == 4
+    rows, cols = (bm // 2, bn // 2) if pair else (bm, bn)   # operand slices one CTA loads
+    rate = SM_MFLOP_PER_US["fp32x3" if eb == 4 else "16bit"]
+    units = tiles * split                                     # a unit keeps one CTA (pair) busy
+    at_once = (NUM_SMS // 2) if pair else NUM_SMS
+    if variant == 5:
+        units, at_once = tiles, NUM_SMS // split              # clusters of `split` CTAs, one tile each
+    kb = K / bk / split
+    unit_kb = (rows + cols) * bk * eb * kb / 1024.0
+    unit_us = max(2.0 * rows * bn * (K / split) / 1e6 / rate, unit_kb / SM_LOAD_KB_PER_US)
+    waves = units / at_once
+    if waves > 1.0 and split == 1:
+        waves = max(1.0, waves)                               # the stream-K tail levels the last wave
+    else:
+        waves = float(-(-units // at_once))
+    ctas = units * (2 if pair else 1) * (split if variant == 5 else 1)
+    l2_us = ctas * unit_kb / L2_LOAD_KB_PER_US
+    reduce_us = 0.0
+    if split > 1:
+        reduce_us = 2.0 if variant == 5 else 5.0 + 0.18 * rows * bn * 4 / 1024.0
+    return LAUNCH_US + max(waves * unit_us, l2_us) + reduce_us
+
+
+def prefilter_by_cost(cfgs: List[Dict], keep_within: float) -> List[Dict]:
+    """Keeps the configs whose estimate is within `keep_within` times the best estimate of their shape and
+    type: tiles that leave most SMs idle, or re-read the operands many times over, are not worth a compile."""
+    best: Dict[Tuple, float] = {}
+    est = []
+    for c in cfgs:
+        key = (c[kw.KEY_M], c[kw.KEY_N], c[kw.KEY_K], int(c.get(kw.KEY_DTYPE_A, c[kw.KEY_DTYPE_C])))
+        e = estimate_us(c)
+        est.append((key, e))
+        best[key] = min(best.get(key, e), e)
+    return [c for c, (key, e) in zip(cfgs, est) if e <= keep_within * best[key]]
+
+
 def get_cfgs(tuning_cfg_file: str) -> List[Dict]:
-    return list(iter_cfgs(read_params(tuning_cfg_file)))
+    """The valid configs of a tuning-space JSON. An optional entry "COST_PREFILTER": [f] (not a tuning key) keeps
+    only the configs whose estimated run time is within f times the best estimate (see estimate_us)."""
+    space = read_params(tuning_cfg_file)
+    keep = space.pop("COST_PREFILTER", None)
+    cfgs = list(iter_cfgs(space))
+    if keep:
+        cfgs = prefilter_by_cost(cfgs, float(keep[0] if isinstance(keep, (list, tuple)) else keep))
+    return cfgs
 
 
 def split_bigjson_to_temp(bigcfgs: Dict, startIndex: int, endIndex: int, outDir: str) -> str:

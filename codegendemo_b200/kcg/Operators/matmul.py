@@ -32,7 +32,7 @@ _ATTR_TO_KEY = {
     "REDUCE_C_CONTINUOUS": ConfigKeywords.KEY_REDUCE_C_CONTINUOUS,
 }
 _OPTIONAL = {"NUM_STAGES": ConfigKeywords.KEY_NUM_STAGES, "KERNEL_VARIANT": ConfigKeywords.KEY_KERNEL_VARIANT,
-             "IS_BTRANS": ConfigKeywords.KEY_IS_B_TRANSPOSE}
+             "IS_BTRANS": ConfigKeywords.KEY_IS_B_TRANSPOSE, "RASTER_SERPENTINE": ConfigKeywords.KEY_RASTER_SERPENTINE}
 
 # Shared memory one CTA may use on sm_100a (the reference asserts 64 KiB for gfx906).
 MAX_SHARED_BYTES = 227 * 1024
@@ -87,6 +87,7 @@ class KernelArgMatmul:
         self.NUM_STAGES = 0       # 0 = derive from SHARED_PREFETCH
         self.KERNEL_VARIANT = 0   # 0 = auto
         self.IS_BTRANS = 0        # 1 = B is stored N x K (tcgen05 16-bit kernels)
+        self.RASTER_SERPENTINE = 0  # 1 = odd tile columns of a BLOCK_MAPPING group walk its rows upwards
 
     def jsonfy(self) -> Dict:
         obj = {key: int(getattr(self, attr)) for attr, key in _ATTR_TO_KEY.items()}
@@ -144,6 +145,11 @@ class KernelArgMatmul:
         """The 31 integers in the compile entry's positional order."""
         j = self.jsonfy()
         return [int(j[k]) for k in ConfigKeywords.COMPILE_ORDER]
+
+    def setOutputDtype(self, typeC) -> None:
+        """DATATYPE_C on its own: float32 C over fp16 / bf16 operands keeps the fp32 accumulators unrounded
+        (single-pass tcgen05 kernels); everywhere else C has the operands' type."""
+        self.__dataType_C = int(typeC)
 
     def dtype(self, index: str) -> EnumKernelDType:
         return {'A': self.__dataType_A, 'B': self.__dataType_B, 'C': self.__dataType_C}.get(index)

@@ -232,6 +232,7 @@ class ConfigKeywords:
     KEY_KERNEL_VARIANT = "KERNEL_VARIANT"  # 0 auto, 1 SIMT FFMA, 2 tcgen05 (fp32: 3xTF32), 3 TF32 x1, 4 CTA pairs,
     #                                        5 cluster split-K (LOCAL_SPLIT_U CTAs per tile, shared-memory reduction)
     KEY_IS_B_TRANSPOSE = "IS_BTRANS"       # 1 = B stored N x K row-major (16-bit tcgen05 kernels)
+    KEY_RASTER_SERPENTINE = "RASTER_SERPENTINE"  # 1 = serpentine walk inside a BLOCK_MAPPING group (tcgen05 kernels)
 
     # Positional order of the compile entry (src/main.cc:64-102 == KCGCompiler.py:14-44).
     COMPILE_ORDER = (

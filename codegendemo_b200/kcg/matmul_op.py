@@ -7,10 +7,11 @@ from codegendemo_b200.kcg.Operators.matmul import KernelArgMatmul
 from codegendemo_b200.kcg.Utils import EnumKernelDType, FromTorchType
 
 
-def default_config(M: int, N: int, K: int, dtype: EnumKernelDType, **keys) -> KernelArgMatmul:
+def default_config(M: int, N: int, K: int, dtype: EnumKernelDType, out_dtype=None, **keys) -> KernelArgMatmul:
     """A tensor-core config for the NN case (A is M x K row-major) with sensible B200 defaults;
-    any tuning key can be overridden by keyword (attribute names of KernelArgMatmul)."""
-    kpm = KernelArgMatmul(M, N, K, dtype, dtype, dtype)
+    any tuning key can be overridden by keyword (attribute names of KernelArgMatmul). ``out_dtype`` =
+    float32 with fp16 / bf16 operands stores the fp32 accumulators unrounded."""
+    kpm = KernelArgMatmul(M, N, K, dtype, dtype, dtype if out_dtype is None else out_dtype)
     eb = int(dtype) % 30
     kpm.BLOCK_SIZE_M = 128
     kpm.BLOCK_SIZE_N = 256 if N % 256 == 0 else 128 if N % 128 == 0 else 64
@@ -150,9 +151,10 @@ def _single_pass_16bit(kpm, M, N, K, dt):
 def attention(q, k, v, scale=None, out=None):
     """``softmax(scale * q @ k^T) @ v`` per head, the attention-shaped chain, as three launches on the current
     stream: a batched product with k taken as stored (keys x head_dim, no transposed copy) whose epilogue applies
-    ``scale``; a row softmax in place (fp32 arithmetic); a batched product with v. ``q`` is (heads, Sq, d), ``k``
-    and ``v`` are (heads, Sk, d), all contiguous fp16 / bf16; ``heads`` may be batch * heads flattened. The
-    Sq x Sk score matrix is materialised in the inputs' dtype; returns (heads, Sq, d)."""
+    ``scale`` and which stores the scores as fp32; a row softmax (fp32 arithmetic) from the scores into
+    probabilities of the inputs' dtype; a batched product with v. ``q`` is (heads, Sq, d), ``k`` and ``v`` are
+    (heads, Sk, d), all contiguous fp16 / bf16; ``heads`` may be batch * heads flattened. The Sq x Sk score and
+    probability matrices are materialised; Sk must be a multiple of 8. Returns (heads, Sq, d)."""
     import ctypes
     import math
     import torch
@@ -170,24 +172,29 @@ def attention(q, k, v, scale=None, out=None):
     key = ("attn", H, Sq, Sk, D, int(dt), dev)
     kerns = _KERNELS.get(key)
     if kerns is None:
-        def tile_for(m, n, kk, btrans):
+        def tile_for(m, n, kk, scores_step):
             kpm = tuned_config(H * m, n, kk, dt)
             if m % kpm.BLOCK_SIZE_M or kpm.KERNEL_VARIANT not in (0, 2, 4):
                 kpm = default_config(m, n, kk, dt)
             kpm.M = m
-            if btrans:
+            if scores_step:
+                # q k^T with k as stored; the scores leave as fp32: rounded to 16 bits first, their error
+                # (up to 2^-9 of a score of several units) would be amplified by the softmax's exp
                 kpm = _single_pass_16bit(kpm, m, n, kk, dt)
                 kpm.IS_BTRANS = 1
+                kpm.setOutputDtype(EnumKernelDType.float32)
             return build_kernel(kpm, dev)[1]
         kerns = (tile_for(Sq, Sk, D, True), tile_for(Sq, D, Sk, False))
         _KERNELS[key] = kerns
-    scores = torch.empty((H, Sq, Sk), dtype=q.dtype, device=q.device)
+    scores = torch.empty((H, Sq, Sk), dtype=torch.float32, device=q.device)
+    probs = torch.empty((H, Sq, Sk), dtype=q.dtype, device=q.device)
     if out is None:
         out = torch.empty((H, Sq, D), dtype=q.dtype, device=q.device)
     kerns[0].run(q, k, scores, alpha=float(scale), batch=H)
-    _lib.check(_lib.get_lib().kcg_softmax_rows(dev, ctypes.c_uint64(DeviceInfo.get_cuda_stream(dev)),
-                                               ctypes.c_uint64(scores.data_ptr()), H * Sq, Sk, 0, 1.0, int(dt)))
-    kerns[1].run(scores, v, out, batch=H)
+    _lib.check(_lib.get_lib().kcg_softmax_rows_ex(dev, ctypes.c_uint64(DeviceInfo.get_cuda_stream(dev)),
+                                                  ctypes.c_uint64(scores.data_ptr()), int(EnumKernelDType.float32), 0,
+                                                  ctypes.c_uint64(probs.data_ptr()), int(dt), 0, H * Sq, Sk, 1.0))
+    kerns[1].run(probs, v, out, batch=H)
     return out
 
 

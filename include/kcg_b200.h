@@ -53,7 +53,7 @@ enum kcg_cfg_index {
 #define KCG_KERNEL_TCGEN05 2  /* TMA + tcgen05/TMEM; fp32 runs as 3xTF32 */
 #define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
 #define KCG_KERNEL_TCGEN05_PAIR 4 /* fp16/bf16 on CTA pairs (tcgen05 cta_group::2), BLOCK_SIZE_M = 256 */
-#define KCG_KERNEL_TCGEN05_CLUSTERK 5 /* fp16/bf16 128-row tiles; LOCAL_SPLIT_U (2, 4, 8) CTAs of a thread-block
+#define KCG_KERNEL_TCGEN05_CLUSTERK 5 /* fp16/bf16 128-row tiles; LOCAL_SPLIT_U (2..8) CTAs of a thread-block
                                          cluster split K and reduce through distributed shared memory */
 #define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
 #define KCG_KERNEL_WAIT_PROBE 101 /* no GEMM: one bounded wait (20 ms) that expires -> KCG_E_DEVICE_TIMEOUT */
@@ -82,7 +82,8 @@ typedef struct kcg_kernel_info {
   int32_t group;      /* BLOCK_MAPPING */
   int32_t atrans;     /* IS_ATRANS */
   int32_t m, n, k;
-  int32_t reserved[8]; /* [0] persistent grid cap (SMs), [1] b_trans */
+  int32_t reserved[8]; /* [0] persistent grid cap (SMs), [1] b_trans, [2] serpentine,
+                          [3] DATATYPE_C when it differs from DATATYPE_A (float32 C over 16-bit operands) */
 } kcg_kernel_info;
 
 typedef struct kcg_compile_opts {
@@ -92,7 +93,9 @@ typedef struct kcg_compile_opts {
   int32_t force;       /* 1 = recompile even when the cubin is cached */
   int32_t b_trans;     /* 1 = B is stored N x K row-major (C = A * Bt^T); fp16 / bf16 with KCG_KERNEL_TCGEN05 / _PAIR.
                           The reference stores B as K x N only (src/lib/Operators/Matmul.cc:93-121). */
-  int32_t reserved[3];
+  int32_t serpentine;  /* 1 = inside a BLOCK_MAPPING group, odd tile columns walk the rows upwards (the reference's
+                          serpentine twin, matmul.cpp:1279-1287); tcgen05 kernels, BLOCK_MAPPING >= 2 */
+  int32_t reserved[2];
 } kcg_compile_opts;
 
 typedef struct kcg_device_props {
@@ -187,6 +190,11 @@ int kcg_launch_gemm_strided(uint64_t function, const kcg_kernel_info* info, int 
  * GEMM among its next operators (doc/结果汇总.md). Rows must start and end on 16-byte boundaries. */
 int kcg_softmax_rows(int device, uint64_t stream, uint64_t X, int64_t rows, int cols, int64_t ld, float scale,
                      int dtype);
+/* The same from X into another matrix Y, each with its own type and pitch: fp32 scores in, fp16 / bf16
+ * probabilities out (a GEMM compiled with DATATYPE_C = float32 over 16-bit operands writes such scores).
+ * cols must be a multiple of 8. Y == X is the in-place call above. */
+int kcg_softmax_rows_ex(int device, uint64_t stream, uint64_t X, int dtype_in, int64_t ldx, uint64_t Y,
+                        int dtype_out, int64_t ldy, int64_t rows, int cols, float scale);
 
 /* ---- M-sharded product with the all-gather of C fused into the kernel ---------------
  * No counterpart in the reference (it has no multi-GPU code). Rank r of G computes rows

@@ -70,6 +70,10 @@ SEEDED = [
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=64, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=2)),
     ("clusterk_bf16_split8_bn256", 128, 512, 4096, E.bfloat16, "normal",
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, LOCAL_SPLIT_U=8)),
+    ("clusterk_bf16_split3_bn256", 256, 768, 1536, E.bfloat16, "normal",   # 8 column blocks dealt 3 + 3 + 2
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, LOCAL_SPLIT_U=3)),
+    ("clusterk_bf16_split5_bn256_bk128", 128, 512, 2560, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=5)),
     ("clusterk_fp16_split4_atrans", 256, 256, 1024, E.float16, "normal",
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4, isATranspose=1)),
     ("clusterk_bf16_uneven_k", 128, 256, 320, E.bfloat16, "uniform",   # 5 K blocks over 4 CTAs: one CTA has none
@@ -85,6 +89,8 @@ SEEDED = [
      dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, NUM_STAGES=4)),
     ("bf16_256x256_half_release_short_k", 8192, 2048, 128, E.bfloat16, "normal",
      dict(BLOCK_SIZE_M=256, NUM_STAGES=3)),
+    ("pair_bf16_serpentine_raster", 2048, 2048, 512, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_MAPPING=4, RASTER_SERPENTINE=1)),
     # B stored N x K (IS_BTRANS): the NT product
     ("bf16_btrans", 256, 512, 512, E.bfloat16, "normal", dict(IS_BTRANS=1)),
     ("fp16_btrans_bk32_atrans", 256, 256, 256, E.float16, "normal", dict(IS_BTRANS=1, BLOCK_SIZE_K=32, isATranspose=1)),
@@ -121,11 +127,13 @@ RECT = [("c4_bf16_128x11008", 128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=
         ("c4_fp32_512x4096", 512, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=128, LOCAL_SPLIT_U=2)),
         ("c4_bf16_2048x4096", 2048, 4096, 4096, E.bfloat16, dict())]
 
-# The rectangular sweep in full, M in {128, 512, 2048} x N = K in {4096, 11008} x {fp32, bf16}, and the row slabs
+# The rectangular sweep in full, M in {128, 512, 2048} x N, K in {4096, 11008} (the N = K points and the two
+# mixed ones: 12 shapes) x {fp32, bf16} = 24 points, and the row slabs
 # of the M-sharded 32768 x 8192 x 8192 bf16 product at 1, 2, 4 and 8 GPUs: each run with the config the operator
 # and the benchmark use for that shape (kernel database entry, else the rule of thumb): (id, M, N, K, dtype, dist)
-TUNED_SHAPES = [(f"c4_{'fp32' if dt == E.float32 else 'bf16'}_{m}x{nk}", m, nk, nk, dt, "uniform")
-                for nk in (4096, 11008) for m in (128, 512, 2048) for dt in (E.float32, E.bfloat16)]
+TUNED_SHAPES = [(f"c4_{'fp32' if dt == E.float32 else 'bf16'}_{m}x{n}x{k}", m, n, k, dt, "uniform")
+                for n in (4096, 11008) for k in (4096, 11008) for m in (128, 512, 2048)
+                for dt in (E.float32, E.bfloat16)]
 TUNED_SHAPES += [(f"c5_bf16_slab_{32768 // g}_rows_g{g}", 32768 // g, 8192, 8192, E.bfloat16, "normal")
                  for g in (1, 2, 4, 8)]
 
@@ -175,6 +183,8 @@ def all_configs():
     for (_, m, n, k, dt, keys) in [BIG_FP32, BIG_BF16] + RECT:
         out.append(default_config(m, n, k, dt, **keys))
     out.append(default_config(BIG_BF16[1] // 8, BIG_BF16[2], BIG_BF16[3], BIG_BF16[4], **BIG_BF16_SLAB))
+    for keys in (dict(), dict(LOCAL_SPLIT_U=2), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256)):
+        out.append(default_config(512, 512, 1024, E.bfloat16, out_dtype=E.float32, **keys))  # float32 C over bf16
     from codegendemo_b200.kcg.matmul_op import tuned_config
     for (_, m, n, k, dt, _) in TUNED_SHAPES:
         out.append(tuned_config(m, n, k, dt))

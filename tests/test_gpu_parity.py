@@ -404,6 +404,23 @@ def test_strided_operands_are_read_and_written_in_place():
     assert ei.value.code == _lib.E_BAD_ARG
 
 
+def test_float32_c_over_bf16_operands_keeps_the_accumulators():
+    """DATATYPE_C = float32 with bf16 A and B: C holds the fp32 accumulators, so it agrees with the fp32-accumulate
+    oracle to fp32 summation-order noise (1e-5 here), far inside the 16-bit bound. Whole-K store path, K-split
+    reducer and the CTA-pair kernel."""
+    M, N, K = 512, 512, 1024
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=15)
+    ref = oracle.host_matmul(A, B)
+    for keys in (dict(), dict(LOCAL_SPLIT_U=2), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256)):
+        kpm = default_config(M, N, K, E.bfloat16, out_dtype=E.float32, **keys)
+        _, kern = build_kernel(kpm, 0)
+        c = torch.full((M, N), float("nan"), dtype=torch.float32, device="cuda:0")
+        kern.run(A.cuda(), B.cuda(), c)
+        kern.checkStatus()
+        err = oracle.rel_errors(c, ref)
+        assert not err["nan"] and err["max_rel"] <= 1e-5, (keys, err)
+
+
 def test_nt_product_takes_b_as_stored():
     from codegendemo_b200.kcg.matmul_op import matmul
     M, N, K = 512, 768, 256
@@ -454,6 +471,17 @@ def test_row_softmax_entry():
         assert (wide[:, :x.shape[1]].float().cpu() - ref).abs().max().item() <= tol
         assert (wide[:, x.shape[1]:] == 0).all().item()
     assert lib.kcg_softmax_rows(0, 0, 16, 4, 7, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG  # 14-byte rows
+    # fp32 scores in, bf16 probabilities out, each matrix with its own pitch
+    x = (torch.randn(64, 512, generator=g) * 4)
+    src = torch.zeros(64, 520, dtype=torch.float32, device="cuda:0")
+    src[:, :512] = x.cuda()
+    dst = torch.full((64, 528), -1.0, dtype=torch.bfloat16, device="cuda:0")
+    rc = lib.kcg_softmax_rows_ex(0, ctypes.c_uint64(DeviceInfo.get_cuda_stream(0)), ctypes.c_uint64(src.data_ptr()), 4,
+                                 520, ctypes.c_uint64(dst.data_ptr()), 62, 528, 64, 512, ctypes.c_float(1.0))
+    assert rc == 0, lib.kcg_last_error()
+    torch.cuda.synchronize()
+    assert (dst[:, :512].float().cpu() - torch.softmax(x, dim=-1)).abs().max().item() <= 4e-3
+    assert (dst[:, 512:] == -1.0).all().item() and torch.equal(src[:, :512].cpu(), x)
 
 
 def test_device_naive_reference_agrees_with_tensor_core_kernel():

@@ -238,6 +238,8 @@ WORK_PLANS = [
     # 3xTF32 kernel: even split of the last wave's 68 tiles by two, not stream-K
     (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4), "even"),
     (256, 512, 1280, E.bfloat16, dict(LOCAL_SPLIT_U=3), "even"),
+    # serpentine raster inside the groups of four tile rows (RASTER_SERPENTINE), with a stream-K tail
+    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128, BLOCK_MAPPING=4, RASTER_SERPENTINE=1), "streamk"),
     # batched: 40 products of 256x512x16384 walked as one tall problem (320 tiles: the tail goes to stream-K)
     (256, 512, 16384, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk", 40),
     (128, 256, 2048, E.bfloat16, dict(LOCAL_SPLIT_U=2), "even", 4),
@@ -255,7 +257,8 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     M, N, K, dt, keys, layer = case[:6]
     batch = case[6] if len(case) > 6 else 1
     kpm = default_config(M, N, K, dt, **keys)
-    info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT)
+    info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT,
+                        serpentine=kpm.RASTER_SERPENTINE)
     out = (ctypes.c_int * 6)()
     lib = _lib.get_lib()
     lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.c_int,
@@ -274,7 +277,7 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     exe = tmp_path / "work_iter_check"
     kdir = os.path.join(ROOT, "codegendemo_b200", "csrc", "kernels")
     subprocess.run(["g++", "-O1", "-std=c++17", "-I/usr/local/cuda/include", "-I" + kdir, f"-DWIC_BM={info.bm}",
-                    f"-DWIC_BN={info.bn}", f"-DWIC_BK={info.bk}", f"-DWIC_GROUP={info.group}", "-o", str(exe),
+                    f"-DWIC_BN={info.bn}", f"-DWIC_BK={info.bk}", f"-DWIC_GROUP={info.group}", f"-DKCG_SERPENTINE={int(info.reserved[2])}", "-o", str(exe),
                     os.path.join(ROOT, "tests", "work_iter_check.cpp")], check=True)
     args = [str(exe), str(M * batch), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots)]
     if batch > 1:
@@ -406,7 +409,10 @@ def test_cluster_split_k_config_rules_and_geometry():
     assert info.grid[0] == 32 * 4 and info.block[0] == 192 and info.splitk == 4
     assert info.smem_bytes == info.stages * (128 + 128) * 64 * 2 + 2048
     assert info.stages * (128 + 128) * 64 * 2 >= 128 * 128 * 4  # ring >= receive buffer
-    for bad in (dict(LOCAL_SPLIT_U=3), dict(LOCAL_SPLIT_U=1), dict(BLOCK_SIZE_M=256), dict(BLOCK_SIZE_N=64, LOCAL_SPLIT_U=4)):
+    odd = compile_info(default_config(128, 11008, 11008, E.bfloat16, KERNEL_VARIANT=5, BLOCK_SIZE_N=256,
+                                      LOCAL_SPLIT_U=3).compileArgs(), kernel=5)
+    assert list(odd.cluster) == [3, 1, 1] and odd.grid[0] == 43 * 3  # 8 column blocks dealt 3 + 3 + 2
+    for bad in (dict(LOCAL_SPLIT_U=9), dict(LOCAL_SPLIT_U=1), dict(BLOCK_SIZE_M=256), dict(BLOCK_SIZE_N=64, LOCAL_SPLIT_U=4)):
         keys = dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)
         keys.update(bad)
         with pytest.raises(_lib.KCGError) as ei:
@@ -448,3 +454,27 @@ def test_strided_and_softmax_entries_validate_their_arguments_without_a_gpu():
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 4, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # ld below the row length
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 0, ctypes.c_float(1.0), 8) == _lib.E_BAD_ARG     # float64
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 6, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # 12-byte rows
+
+
+def test_cost_model_prefilter_drops_configs_that_idle_most_sms(tmp_path):
+    """`COST_PREFILTER` in a tuning-space JSON: configs whose estimated time (tiles, waves, operand bytes per SM
+    and through L2) is more than the given factor above the best estimate of the shape are not enumerated."""
+    space = {kw.KEY_DTYPE_C: [int(E.bfloat16)], kw.KEY_M: [128], kw.KEY_N: [4096], kw.KEY_K: [4096],
+             kw.KEY_KERNEL_VARIANT: [2, 5], kw.KEY_BLOCK_SIZE_M: [128], kw.KEY_BLOCK_SIZE_N: [64, 128, 256],
+             kw.KEY_BLOCK_SIZE_K: [64], kw.KEY_LOCAL_SPLIT_U: [1, 2, 4], kw.KEY_IS_A_TRANSPOSE: [0],
+             kw.KEY_SHARED_PREFETCH: [1]}
+    allc = list(ConfigGenerator.iter_cfgs(space))
+    # the cluster kernel has no one-way split, and needs a 32-column block per CTA of the cluster
+    v5 = [(c[kw.KEY_BLOCK_SIZE_N], c[kw.KEY_LOCAL_SPLIT_U]) for c in allc if c[kw.KEY_KERNEL_VARIANT] == 5]
+    assert sorted(v5) == [(64, 2), (128, 2), (128, 4), (256, 2), (256, 4)]
+    whole = next(c for c in allc if c[kw.KEY_KERNEL_VARIANT] == 2 and c[kw.KEY_BLOCK_SIZE_N] == 256 and c[kw.KEY_LOCAL_SPLIT_U] == 1)
+    split = next(c for c in allc if c[kw.KEY_KERNEL_VARIANT] == 5 and c[kw.KEY_BLOCK_SIZE_N] == 128 and c[kw.KEY_LOCAL_SPLIT_U] == 4)
+    # 16 tiles on 148 SMs against 128 CTAs streaming a quarter of K each
+    assert ConfigGenerator.estimate_us(whole) > 2.2 * ConfigGenerator.estimate_us(split)
+    kept = ConfigGenerator.prefilter_by_cost(allc, 2.0)
+    assert split in kept and whole not in kept and 0 < len(kept) < len(allc)
+    f = tmp_path / "space.json"
+    f.write_text(json.dumps(dict(space, COST_PREFILTER=[2.0])))
+    assert ConfigGenerator.get_cfgs(str(f)) == kept
+    f.write_text(json.dumps(space))
+    assert ConfigGenerator.get_cfgs(str(f)) == allc

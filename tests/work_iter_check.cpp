@@ -3,6 +3,7 @@
 //   * each tile's K blocks are covered exactly once;
 //   * a tile's contributors are numbered 0..nsplit-1 in K order and all agree on nsplit;
 //   * their workspace slots are slot0 + split, distinct from every other tile's, and below `slots`.
+//   * with -DKCG_SERPENTINE=1: consecutive tiles of a raster group share a row block or a column block.
 // usage: work_iter_check M N K first factor sk_per grid slots   (tile and raster group are macros)
 #include <cstdio>
 #include <cstdlib>
@@ -44,7 +45,7 @@ int main(int argc, char** argv) {
   std::map<int, int> slot_owner;
   std::map<long long, int> origin_owner;
   for (int c = 0; c < grid; ++c) {
-    kcg::WorkIter<WIC_BM, WIC_BN, WIC_GROUP> it(p, c, grid, tiles_m, tiles_n, num_kb);
+    kcg::WorkIter<WIC_BM, WIC_BN, WIC_GROUP, KCG_SERPENTINE> it(p, c, grid, tiles_m, tiles_n, num_kb);
     kcg::WorkUnit w;
     while (it.next(w)) {
       if (w.tile < 0 || w.tile >= tiles || w.kb0 < 0 || w.kb0 + w.kbn > num_kb) return printf("FAIL range\n"), 1;
@@ -59,6 +60,21 @@ int main(int argc, char** argv) {
       by_tile[w.tile].push_back({w.split, w.nsplit, w.slot, w.kb0, w.kbn});
     }
   }
+#if KCG_SERPENTINE
+  {
+    // serpentine walk: consecutive tiles of the raster share a row block or a column block
+    kcg::WorkIter<WIC_BM, WIC_BN, WIC_GROUP, 1> walk(p, 0, 1, tiles_m, tiles_n, num_kb);
+    kcg::WorkUnit a, b;
+    for (int t = 0; t + 1 < tiles; ++t) {
+      a.tile = t;
+      b.tile = t + 1;
+      walk.origin(a);
+      walk.origin(b);
+      const bool same_group = (t / (WIC_GROUP * tiles_n)) == ((t + 1) / (WIC_GROUP * tiles_n));
+      if (same_group && a.m0 != b.m0 && a.n0 != b.n0) return printf("FAIL serpentine jump after tile %d\n", t), 1;
+    }
+  }
+#endif
   for (size_t i = 0; i < cover.size(); ++i)
     if (cover[i] != 1) return printf("FAIL tile %zu block %zu covered %d times\n", i / num_kb, i % num_kb, cover[i]), 1;
   if (static_cast<int>(origin_owner.size()) != tiles) return printf("FAIL raster misses tiles\n"), 1;
