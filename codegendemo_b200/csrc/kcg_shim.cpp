@@ -374,7 +374,7 @@ int resolve(const Cfg& c, const kcg_compile_opts* opts, Resolved* r) {
     if (!ok(st))
       return fail(KCG_E_BAD_CONFIG,
                   "tile 128x%dx%d / %d stages / LOCAL_SPLIT_U %d not buildable by the cluster split-K kernel (rule %d: "
-                  "fp16 / bf16, split 2..8 and at most BLOCK_SIZE_N / 32, ring large enough for the received slices)",
+                  "fp16 / bf16, split 2..4 and at most BLOCK_SIZE_N / 32, ring large enough for the exchange buffers)",
                   bn, bk, st, split, kcg::ck_config_error(dt, bn, bk, st, split));
     if (N % 8) return fail(KCG_E_BAD_CONFIG, "N must be a multiple of 8 for TMA row strides");
     r->stages = st;
@@ -724,27 +724,23 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
   } else {
     const char* e = getenv("KCG_TAIL_SPLIT");
     // Default: stream-K for the single-pass kernel, whose partials move as full lines; the 3xTF32
-    // kernel stores its partials straight from registers and measured better with the even split
-    // of the last wave only (512x11008x11008 fp32: 214 vs 199 TFLOP/s, 4096^3: 228 vs 222).
+    // kernel stores its partials straight from registers and does better with the even split of
+    // the last wave only.
     const int mode = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : (e && e[0] == '1') ? 1 : (x3 ? 2 : 1);
     const int rem = T % G;
     if (mode != 0 && rem > 0) {
-      // Worth it only when the time saved exceeds the cost of the split: estimate a tile's
-      // main-loop time from a per-SM rate of ~10 MFLOP/us (16-bit) or ~1.4 MFLOP/us useful (fp32
-      // as 3xTF32).
+      // Worth it only when the time saved exceeds the cost of the split. A tile's main-loop time is
+      // estimated from a per-SM rate in MFLOP per microsecond: 10 for 16-bit data, 1.4 useful for fp32
+      // as 3xTF32, 4.5 for the single TF32 pass.
       const double mflop_per_us = (info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1) ? 1.4
                                   : (info->dtype == KCG_DTYPE_FLOAT32)                                     ? 4.5
                                                                                                            : 10.0;
-      // (HBM-bound 128-row shapes run longer per tile than this says, but splitting them measured
-      // worse anyway: 128x11008x11008 bf16 71 us with a stream-K tail against 64 us without.)
       const double tile_us =
           2.0 * (info->bm / (pair ? 2 : 1)) * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
       // What a split costs a CTA: its fp32 partial goes to the workspace once, the reducing CTA
-      // reads two or three of them back and writes C, and each extra unit refills the pipeline.
-      // Measured on 512x11008x11008 bf16: ~28 us for a 128 KB partial (128 x 256 rows per CTA),
-      // ~51 us for 256 KB (the 3xTF32 kernel's thread-major partials cost about the same: 1024^3
-      // fp32 with 128 KB partials gains 21 us from a four-way split). The saving has to beat that
-      // with a margin.
+      // reads two or three of them back and writes C, and each extra unit refills the pipeline:
+      // 5 us plus 0.18 us per KB of partial tile (fitted to measurements). The saving has to beat
+      // that with a margin.
       const double partial_kb = (info->bm / (pair ? 2 : 1)) * static_cast<double>(info->bn) * 4.0 / 1024.0;
       const double overhead_us = 5.0 + 0.18 * partial_kb;
       const double gate_us = 1.25 * overhead_us;

@@ -180,11 +180,9 @@ constexpr int tc_staging_bytes(int dtype, int x3) {
 }
 
 // 3xTF32 kernel: depth of the ring of lo twins beside `stages` TMA-fed hi stages. The kernel
-// supports a shorter lo ring, but measured on 4096^3 every shorter ring lost: the splitter must
-// run about 2 us (hand-offs + 2 x 32 KB of shared-memory traffic) ahead of the MMAs, i.e. three
-// 32-wide or four 16-wide K blocks, which is what equal rings give (pair 256x256x32: 3 hi + 3 lo
-// 215-229 TFLOP/s, 3 + 2 158, 4 + 3 162, 5 + 2 163; single 128x256x16: 4 + 4 214, 4 + 3 144,
-// 6 + 3 150). So the lo ring is as deep as the hi ring.
+// supports a shorter lo ring, but the splitter has to run several K blocks ahead of the MMAs
+// (hand-offs plus two passes over a stage of shared memory), which only equally deep rings give:
+// every shorter lo ring measured slower. So the lo ring is as deep as the hi ring.
 constexpr int tc_lo_stages(int stages) { return stages; }
 
 // Bytes of the operand rings: single-pass kernel stages * (A + B tile); 3xTF32 adds the lo ring.
@@ -213,18 +211,21 @@ constexpr int tc_config_error(int dtype, int BM, int BN, int BK, int stages, int
 }
 
 // Cluster split-K kernel (gemm_tcgen05_clusterk.cuh): a 128 x BN tile per cluster of `split` CTAs.
-// The operand ring doubles as the buffer that receives the cluster's fp32 partial slices
-// (128 x BN x 4 bytes), so the ring must be at least that large; no TMA-store staging.
+// The operand ring doubles as the exchange buffers of the reduction (a staging copy of the fp32
+// accumulator, 128 x BN x 4 bytes, plus a receive slot per other CTA), so it must be at least that
+// large; no TMA-store staging.
 constexpr int ck_config_error(int dtype, int BN, int BK, int stages, int split) {
   if (!(dtype == KCG_DT_F16 || dtype == KCG_DT_BF16)) return 1;
-  if (split < 2 || split > 8) return 2;  // a portable cluster has at most 8 CTAs
+  if (split < 2 || split > 4) return 2;  // larger clusters do not fit the exchange buffers (nor the GPU: few run at once)
   if (BN < 64 || BN > 256 || (BN % 64) != 0 || BN / 32 < split) return 3;
   const int rowb = BK * 2;
   if (!(rowb == 32 || rowb == 64 || (rowb % 128) == 0) || rowb > 512 || (BK % 16) != 0) return 5;
   if (stages < 2 || stages > 12) return 7;
   const int ring = (128 + BN) * BK * 2 * stages;
   if (ring + 2048 > 227 * 1024) return 8;
-  if (ring < split * ((BN / 32 + split - 1) / split) * 128 * 128) return 10;  // kSplit slices of whole 32-column blocks
+  // the ring doubles as exchange buffers: a receive slot per other CTA plus a staging copy of the accumulator
+  // of the blocks that belong to other CTAs
+  if (ring < ((split - 1) * ((BN / 32 + split - 1) / split) + (BN / 32 - BN / 32 / split)) * 128 * 128) return 10;
   return 0;
 }
 constexpr int ck_smem_bytes(int BN, int BK, int stages) { return (128 + BN) * BK * 2 * stages + 2048; }

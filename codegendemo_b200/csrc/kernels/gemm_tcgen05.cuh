@@ -174,9 +174,10 @@ struct TcGemm {
     const int bcol_base = static_cast<int>(rank) * BNL;  // this CTA's first B column inside the tile
 
     // ---- producer state (thread 0). The loop below is entered twice: once before the set-up barrier
-    // for the first ring of stages (their `empty` waits pass at once on fresh barriers, and a single CTA's
+    // for the FIRST stage only (its `empty` wait passes at once on a fresh barrier, and a single CTA's
     // loads signal only its own barriers, which this very thread has just initialised), so that the
-    // first operands are already in flight while TMEM is allocated; and again, to the end, as warp 0's role.
+    // first operands are in flight while TMEM is allocated - issuing the whole ring there delayed the
+    // barrier by more than it gained -; and again, to the end, as warp 0's role.
     Iter p_units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
     Unit p_w;
     uint32_t p_it = 0;
@@ -250,7 +251,7 @@ struct TcGemm {
     };
     if (threadIdx.x == 0) {
       p_have = p_units.next(p_w);
-      if constexpr (!kPair) produce(static_cast<uint32_t>(kStages));
+      if constexpr (!kPair) produce(1u);
     }
     if (warp == 1) {
       if constexpr (kPair) {

@@ -5,21 +5,26 @@
 // r-th of kSplit equal K ranges with the usual pipeline (warp 0 TMA producer, warp 1 tcgen05.mma
 // issuer, fp32 accumulator in TMEM), so kSplit times as many SMs stream B as there are tiles.
 // The partial tiles never touch global memory: the tile's columns are cut into kSplit slices
-// (runs of 32-column blocks, lengths differing by at most one, so any kSplit from 2 to 8 works),
-// every CTA sends slice j of its accumulator to CTA j through distributed shared memory
-// (st.shared::cluster), and CTA j adds the kSplit slices it received in rank order (bitwise
-// reproducible) and stores its slice of C. No workspace, no counters, no waits between
+// (runs of 32-column blocks, lengths differing by at most one, so kSplit = 3 works as well as 2 and 4),
+// every CTA sends slice j of its accumulator to CTA j through distributed shared memory, and CTA j
+// adds the kSplit slices in rank order (bitwise reproducible) and stores its slice of C. No workspace, no counters, no waits between
 // clusters; the hardware co-schedules the CTAs of a cluster, so the waits inside it cannot starve.
 //
 // This is LOCAL_SPLIT_U of the reference (Optimizer.cc:310-314, 389-411: thread groups of one
 // block split K and reduce their partial tiles through shared memory) lifted from the thread
 // groups of a block to the CTAs of a cluster.
 //
-// Receive buffer = the operand ring. A CTA's ring is idle once its own MMAs have retired; it says
-// so to every CTA of the cluster (ring_free[r]), and only then do the others write their slices
-// into it. Layout of the buffer: [source rank][32-column block][128 rows][128 bytes], the 16-byte
-// units of a row XOR-swizzled by (row & 7) so that the remote stores (one row per lane) and the
-// adding loop (consecutive threads, consecutive units) are both free of bank conflicts.
+// Exchange buffers = the operand ring. A CTA's ring is idle once its own MMAs have retired; it says
+// so to every CTA of the cluster (ring_free[r]), and only then do the others write into it. The
+// ring is then cut in two: a staging area, where the epilogue warps lay down the 32-column blocks
+// of the accumulator that belong to OTHER CTAs (tcgen05.ld, one row per lane, 16-byte units of a
+// row XOR-swizzled by (row & 7) so that the stores are free of bank conflicts), and a receive area
+// [sender][block][128 rows][128 bytes] into which the other CTAs copy theirs. Each warp ships its
+// 32 rows of a block - 4 KB, contiguous - with ONE bulk asynchronous copy (cp.async.bulk
+// shared::cta -> shared::cluster) that completes on the receiver's mbarrier as transaction bytes;
+// plain remote stores, 16 bytes per lane, measured several times slower. The blocks a CTA owns
+// never leave its TMEM: each thread adds, for its own row, the received slices and its own
+// accumulator in rank order and stores 64 bytes of C.
 //
 // One tile per cluster, no persistence: these shapes have fewer tiles than the GPU has SMs.
 // Every wait is bounded (ptx_sm100.cuh); on expiry the role records a status code, raises the
@@ -51,13 +56,16 @@ struct TcGemmClusterK {
   static constexpr int NCH = kBN / 32;
   static constexpr int CB = (NCH + kSplit - 1) / kSplit;  // most 32-column blocks one CTA owns
   static constexpr int BLOCK_BYTES = 128 * 128;           // one 32-column block: 128 rows x 128 bytes
-  static constexpr int SLICE_BYTES = CB * BLOCK_BYTES;    // room for one source rank's slice
+  static constexpr int SLICE_BYTES = CB * BLOCK_BYTES;    // room for one sender's slice
+  static constexpr int RECV_BYTES = (kSplit - 1) * SLICE_BYTES;  // receive area: one slot per other CTA
+  // staging area: the blocks of the other CTAs, in column order (at least NCH / kSplit blocks are this CTA's own)
+  static constexpr int STAGE_OUT_BYTES = (NCH - NCH / kSplit) * BLOCK_BYTES;
   __host__ __device__ static constexpr int owner_of(int c) { return c * kSplit / NCH; }
   __host__ __device__ static constexpr int first_block_of(int r) { return (r * NCH + kSplit - 1) / kSplit; }
   static constexpr int NUM_EPI_THREADS = 128;
   static constexpr int NUM_THREADS = 64 + NUM_EPI_THREADS;
   static constexpr int SMEM_BYTES = ck_smem_bytes(kBN, kBK, kStages);
-  static_assert(kSplit * SLICE_BYTES <= kStages * STAGE_BYTES, "the ring must hold the received slices");
+  static_assert(RECV_BYTES + STAGE_OUT_BYTES <= kStages * STAGE_BYTES, "the ring must hold the exchange buffers");
   static constexpr uint32_t FMT = (kDType == KCG_DT_BF16) ? FMT_BF16 : FMT_F16;
   static constexpr uint32_t IDESC = make_instr_desc(FMT, kATrans ? 1u : 0u, 1u, 128u, kBN);
 
@@ -65,8 +73,8 @@ struct TcGemmClusterK {
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t tmem_full;
-    uint64_t ring_free[8];  // [r]: CTA r of the cluster no longer touches its operand ring
-    uint64_t recv_full;     // all slices for this CTA have arrived (4 warps of each of kSplit CTAs)
+    uint64_t ring_free[4];  // [r]: CTA r of the cluster no longer touches its operand ring
+    uint64_t recv_full;     // all slices for this CTA have arrived (transaction bytes of the bulk copies)
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 #ifdef KCG_TIMELINE
@@ -113,11 +121,16 @@ struct TcGemmClusterK {
         mbar_init(&bars->empty[s], 1);
       }
       mbar_init(&bars->tmem_full, 1);
-      for (int r = 0; r < 8; ++r) mbar_init(&bars->ring_free[r], 1);
-      mbar_init(&bars->recv_full, 4 * kSplit);
+      for (int r = 0; r < 4; ++r) mbar_init(&bars->ring_free[r], 1);
+      mbar_init(&bars->recv_full, 1);
       bars->abort_flag = 0u;
       fence_mbar_init();
       fence_proxy_async_smem();
+      // what the other CTAs will copy in: (kSplit - 1) senders x this CTA's blocks x 16 KB. Posted now;
+      // a copy that lands before this CTA looks is simply counted.
+      const int r_me = static_cast<int>(cluster_cta_rank());
+      const int nb_me = first_block_of(r_me + 1) - first_block_of(r_me);
+      mbar_expect_tx(&bars->recv_full, static_cast<uint32_t>((kSplit - 1) * nb_me * BLOCK_BYTES));
     }
     const uint32_t rank = cluster_cta_rank();
     // This cluster's tile and this CTA's K range. The raster (and a batched launch's offsets) come
@@ -130,9 +143,9 @@ struct TcGemmClusterK {
     const int kb0 = static_cast<int>(rank) * per;
     const int kbn = (kb0 >= num_kb) ? 0 : ((num_kb - kb0 < per) ? num_kb - kb0 : per);
 
-    // Producer (thread 0), entered twice: before the set-up barriers for the first ring of stages - the
-    // loads signal only this CTA's own barriers, which this very thread has just initialised, so the first
-    // operands are in flight while TMEM is allocated and the cluster synchronises - and again as warp 0's role.
+    // Producer (thread 0), entered twice: before the set-up barrier for the first two stages - the loads
+    // signal only this CTA's own barriers, which this very thread has just initialised, so the first
+    // operands are in flight while TMEM is allocated - and again as warp 0's role.
     int p_kb = 0;
     auto produce = [&](int kb_limit) {
       for (; p_kb < kbn && p_kb < kb_limit; ++p_kb) {
@@ -164,7 +177,7 @@ struct TcGemmClusterK {
         if (kb == 0) KCG_CTL(2);
       }
     };
-    if (threadIdx.x == 0) produce(kStages);
+    if (threadIdx.x == 0) produce(2);
     if (warp == 1) {
       tmem_alloc(&bars->tmem_base, TMEM_COLS);
       tmem_relinquish();
@@ -172,7 +185,10 @@ struct TcGemmClusterK {
     __syncwarp();  // thread 0 rejoins its warp before the block-wide barrier
     tc_fence_before_sync();
     __syncthreads();
-    cluster_sync_all();  // every CTA's barriers exist before anyone signals them
+    // Every CTA's barriers must exist before anyone signals them - but nothing crosses CTAs before the
+    // exchange: arrive on the cluster barrier now, wait for it only there (cluster_wait below), and
+    // keep the main loop free of the cluster's start-up skew.
+    cluster_arrive();
     tc_fence_after_sync();
     const uint32_t tmem_base = bars->tmem_base;
     if (threadIdx.x == 0) KCG_CTL(1);
@@ -224,6 +240,7 @@ struct TcGemmClusterK {
       // the four warps take every branch below together (named barrier 2 ANDs their outcomes)
       const bool have_acc = named_bar_all(2, NUM_EPI_THREADS, ok);
       if (!have_acc && !ok) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 0u, rank);
+      cluster_wait();  // the other CTAs' barriers are initialised (all four warps, every lane)
       if (have_acc) {
         tc_fence_after_sync();
         if (epi_tid == 0) KCG_CTL(4);
@@ -233,18 +250,13 @@ struct TcGemmClusterK {
             mbar_arrive_cluster(map_to_cta(smem_u32(&bars->ring_free[rank]), j));
         }
         const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        const uint32_t my_slot = smem_u32(smem) + rank * SLICE_BYTES + row * 128;
+        uint8_t* stage_out = smem + RECV_BYTES;  // staging area behind the receive area
+        const int own_first = first_block_of(static_cast<int>(rank));
+        const int own_count = first_block_of(static_cast<int>(rank) + 1) - own_first;
+        // ---- stage: every block owned by another CTA is laid down in this CTA's (idle) ring first ...
 #pragma unroll 1
-        for (int c = 0; c < kBN / 32; ++c) {
-          const uint32_t owner = static_cast<uint32_t>(owner_of(c));
-          const int cbi = c - first_block_of(static_cast<int>(owner));
-          // the owner's ring is idle (its MMAs retired): our slice may overwrite it
-          const bool free_ = mbar_wait(&bars->ring_free[owner], 0u, &bars->abort_flag);
-          if (!__all_sync(0xffffffffu, free_)) {
-            if (lane == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 1u, owner);
-            ok = false;
-            break;
-          }
+        for (int c = 0; c < NCH; ++c) {
+          if (owner_of(c) == static_cast<int>(rank)) continue;
           uint32_t r[32];
           if (kbn > 0) {
             tmem_ld_32x32b_x32(tmem_acc + c * 32, r);
@@ -253,57 +265,101 @@ struct TcGemmClusterK {
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
-          const uint32_t dst = map_to_cta(my_slot + cbi * BLOCK_BYTES, owner);
+          // this warp's 32 rows of block c, 4 KB (the staging area skips this CTA's own blocks)
+          uint8_t* rowp = stage_out + (c < own_first ? c : c - own_count) * BLOCK_BYTES + q * 32 * 128 + lane * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
-            st_cluster_v4(dst + ((j ^ (row & 7)) << 4), r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
         }
-        if (epi_tid == 0) KCG_CTL(5);
-        // Publish: every lane's stores are ordered before lane 0's release arrivals.
-        fence_acq_rel_cluster();
+        fence_proxy_async_smem();  // generic-proxy writes visible to the bulk copy engine
         __syncwarp();
-        if (ok && lane == 0) {
-          for (uint32_t j = 0; j < static_cast<uint32_t>(kSplit); ++j)
-            mbar_arrive_cluster(map_to_cta(smem_u32(&bars->recv_full), j));
+        // ---- ... push: then one lane ships them, owner by owner (starting with the next rank, so that the
+        // cluster's CTAs do not all write to the same one first), as soon as that owner's ring is idle
+        if (lane == 0) {
+          for (int d = 1; d < kSplit && ok; ++d) {
+            const uint32_t owner = (rank + static_cast<uint32_t>(d)) % static_cast<uint32_t>(kSplit);
+            if (!mbar_wait(&bars->ring_free[owner], 0u, &bars->abort_flag)) {
+              report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 1u, owner);
+              ok = false;
+              break;
+            }
+            const uint32_t slot = rank < owner ? rank : rank - 1u;  // senders in rank order, the owner left out
+            const uint32_t bar = map_to_cta(smem_u32(&bars->recv_full), owner);
+            const int o_first = first_block_of(static_cast<int>(owner));
+            const int o_end = first_block_of(static_cast<int>(owner) + 1);
+            for (int c = o_first; c < o_end; ++c) {
+              const uint32_t src =
+                  smem_u32(stage_out + (c < own_first ? c : c - own_count) * BLOCK_BYTES + q * 32 * 128);
+              const uint32_t dst_local = smem_u32(smem) + slot * SLICE_BYTES + (c - o_first) * BLOCK_BYTES + q * 32 * 128;
+              bulk_copy_to_cta(map_to_cta(dst_local, owner), src, 32 * 128, bar);
+            }
+          }
         }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (epi_tid == 0) KCG_CTL(5);
         bool got = ok && mbar_wait_cluster(&bars->recv_full, 0u, &bars->abort_flag);
         const bool all_in = named_bar_all(2, NUM_EPI_THREADS, got);
         if (!all_in && ok && !got) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 2u, rank);
         if (epi_tid == 0) KCG_CTL(6);
         if (all_in) {
-          // Add the kSplit slices in rank (= K) order and store this CTA's columns of C.
+          // ---- add: for every block this CTA owns, each thread adds - for its own row - the slices in
+          // rank (= K) order, its own from TMEM, and stores 32 values of C
           OutT* Cout = reinterpret_cast<OutT*>(p.C);
           const int c_first = first_block_of(static_cast<int>(rank));
-          const int total = (first_block_of(static_cast<int>(rank) + 1) - c_first) * 128 * 8;  // 16-byte units
-#pragma unroll 2
-          for (int idx = epi_tid; idx < total; idx += NUM_EPI_THREADS) {
-            const int u = idx & 7;
-            const int rr = (idx >> 3) & 127;
-            const int cbi = idx >> 10;
-            const uint8_t* src = smem + cbi * BLOCK_BYTES + rr * 128 + ((u ^ (rr & 7)) << 4);
-            float4 acc = *reinterpret_cast<const float4*>(src);
-#pragma unroll
-            for (int s = 1; s < kSplit; ++s) {
-              const float4 x = *reinterpret_cast<const float4*>(src + s * SLICE_BYTES);
-              acc.x += x.x;
-              acc.y += x.y;
-              acc.z += x.z;
-              acc.w += x.w;
-            }
-            const int grow = w.m0 + rr;
-            const int gcol = w.n0 + (c_first + cbi) * 32 + u * 4;
-            if (grow >= p.M || gcol >= p.N) continue;
-            float o[4] = {acc.x, acc.y, acc.z, acc.w};
-            if (p.epi_flags != 0u) epi_span<OutT, 4>(p, o, grow, gcol);
-            uint2 out;
-            if constexpr (kDType == KCG_DT_BF16) {
-              __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
-              out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+          const int c_end = first_block_of(static_cast<int>(rank) + 1);
+          const int grow = w.m0 + row;
+#pragma unroll 1
+          for (int c = c_first; c < c_end; ++c) {
+            const int cbi = c - c_first;
+            uint32_t own[32];
+            if (kbn > 0) {
+              tmem_ld_32x32b_x32(tmem_acc + c * 32, own);
+              tmem_ld_wait();
             } else {
-              __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
-              out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+#pragma unroll
+              for (int i = 0; i < 32; ++i) own[i] = 0u;
             }
-            *reinterpret_cast<uint2*>(Cout + static_cast<size_t>(grow) * p.ldc + gcol) = out;
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+#pragma unroll
+            for (int sdr = 0; sdr < kSplit; ++sdr) {
+              if (static_cast<uint32_t>(sdr) == rank) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(own[i]);
+              } else {
+                const int slot = sdr < static_cast<int>(rank) ? sdr : sdr - 1;
+                const uint8_t* src = smem + slot * SLICE_BYTES + cbi * BLOCK_BYTES + row * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 x = *reinterpret_cast<const float4*>(src + ((j ^ (row & 7)) << 4));
+                  v[4 * j] += x.x;
+                  v[4 * j + 1] += x.y;
+                  v[4 * j + 2] += x.z;
+                  v[4 * j + 3] += x.w;
+                }
+              }
+            }
+            const int gcol = w.n0 + c * 32;
+            if (grow >= p.M || gcol >= p.N) continue;
+            if (p.epi_flags != 0u) epi_span<OutT, 32>(p, v, grow, gcol);
+            uint4* dst = reinterpret_cast<uint4*>(Cout + static_cast<size_t>(grow) * p.ldc + gcol);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t h[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if constexpr (kDType == KCG_DT_BF16) {
+                  __nv_bfloat162 x = __floats2bfloat162_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+                  h[i] = *reinterpret_cast<uint32_t*>(&x);
+                } else {
+                  __half2 x = __floats2half2_rn(v[8 * j + 2 * i], v[8 * j + 2 * i + 1]);
+                  h[i] = *reinterpret_cast<uint32_t*>(&x);
+                }
+              }
+              dst[j] = make_uint4(h[0], h[1], h[2], h[3]);
+            }
           }
         }
       }
@@ -313,6 +369,7 @@ struct TcGemmClusterK {
     // The producer and MMA roles run in one lane; the other lanes of those warps come straight here.
     // Reconverge every warp first: the block-wide barrier below must be executed by whole warps.
     __syncwarp();
+    if (warp < 2) cluster_wait();  // warps 0 and 1 complete the set-up phase of the cluster barrier here
     if (bars->abort_flag != 0u) {
       // Give copies / MMAs still in flight time to land before shared memory and TMEM are released.
       const uint64_t t0 = global_timer_ns();

@@ -297,6 +297,15 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
+// The two halves of cluster_sync_all, for code that has work to do in between. Every thread of the
+// cluster executes both, whole warps at a time.
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Arrive on an mbarrier that lives in another CTA of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
@@ -310,6 +319,17 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b),
                "r"(c), "r"(d)
                : "memory");
+}
+// Bulk asynchronous copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from this CTA's
+// shared memory into the shared memory of a CTA of the cluster; completion is counted as transaction
+// bytes on an mbarrier of the RECEIVING CTA (`dst_cluster_addr`, `bar_cluster_addr` from map_to_cta).
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          dst_cluster_addr),
+      "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr)
+      : "memory");
 }
 // Orders this thread's earlier accesses (remote shared-memory stores included) before its later
 // ones at cluster scope; paired with the acquire of mbar_wait_cluster on the reading side.

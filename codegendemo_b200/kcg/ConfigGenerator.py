@@ -109,9 +109,10 @@ def _rules() -> List[Tuple[Tuple[str, ...], Callable[[Dict], bool]]]:
             return True
         dt = int(cfg.get(kw.KEY_DTYPE_A, cfg[kw.KEY_DTYPE_C]))
         s, bn, bk = cfg[kw.KEY_LOCAL_SPLIT_U], cfg[kw.KEY_BLOCK_SIZE_N], cfg[kw.KEY_BLOCK_SIZE_K]
-        if dt % 30 != 2 or cfg[kw.KEY_BLOCK_SIZE_M] != 128 or not 2 <= s <= 8 or bn % 64 or bn // 32 < s:
+        if dt % 30 != 2 or cfg[kw.KEY_BLOCK_SIZE_M] != 128 or not 2 <= s <= 4 or bn % 64 or bn // 32 < s:
             return False
-        recv = s * -(-(bn // 32) // s) * 128 * 128
+        nch = bn // 32
+        recv = ((s - 1) * -(-nch // s) + nch - nch // s) * 128 * 128  # receive slots + staging of the other CTAs' blocks
         stage = (128 + bn) * bk * 2
         stages = max(2, -(-recv // stage))
         return stage * stages + 2048 <= 227 * 1024

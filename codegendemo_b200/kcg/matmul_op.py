@@ -54,22 +54,29 @@ def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: i
             return default_config(M, N, K, dtype, BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4,
                                   isATranspose=isATranspose)
         return default_config(M, N, K, dtype, BLOCK_SIZE_N=128 if N % 128 == 0 else 64, isATranspose=isATranspose)
-    if M % 512 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 512) * (N // 256) >= 6 * pairs:
-        return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
-                              NUM_STAGES=4, isATranspose=isATranspose)
     tiles256 = (M // 256) * (N // 256) if M % 256 == 0 and N % 256 == 0 else 0
     if K <= 512 and K % 64 == 0 and N % 256 == 0:
         # short K: the epilogue weighs as much as the main loop, so take the tile whose two TMEM accumulator
-        # buffers overlap them (batched 256 x (256x256x256): 489 vs 405 TFLOP/s with the pair tile)
+        # buffers overlap them
         return default_config(M, N, K, dtype, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, isATranspose=isATranspose)
-    if K % 64 == 0 and pairs <= tiles256 < 6 * pairs:
-        # one to six waves of 256x256 pair tiles: the pair kernel with a stream-K tail measured best on the
-        # rectangular shapes (512 and 2048 rows x 11008^2), with 128-wide K blocks once K is long
+    if K % 128 == 0 and tiles256 >= pairs:
+        # at least one wave of 256x256 pair tiles: CTA pairs with 128-wide K blocks (half as many stage
+        # hand-offs per byte as 64-wide ones, two accumulator buffers); best or within 2 % of the best on
+        # every large shape measured, from 512 x 11008 x 4096 to 32768 x 8192 x 8192
         return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
-                              BLOCK_SIZE_K=128 if (K % 128 == 0 and K >= 8192) else 64, isATranspose=isATranspose)
-    if K % 64 == 0 and tiles256 >= 148:
-        return default_config(M, N, K, dtype, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3,
-                              isATranspose=isATranspose)
+                              BLOCK_SIZE_K=128, isATranspose=isATranspose)
+    if K % 64 == 0 and tiles256 >= pairs:
+        return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
+                              BLOCK_SIZE_K=64, isATranspose=isATranspose)
+    if M == 128 and K >= 2048:
+        # one row of tiles: far fewer tiles than SMs. K is split over the CTAs of a cluster (KERNEL_VARIANT 5,
+        # reduction in shared memory) so that four (three) times as many SMs stream B
+        if N % 128 == 0 and K % 128 == 0 and (N // 128) * 4 <= 148:
+            return default_config(M, N, K, dtype, KERNEL_VARIANT=5, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128,
+                                  LOCAL_SPLIT_U=4, isATranspose=isATranspose)
+        if N % 256 == 0 and K % 64 == 0 and K >= 8192 and (N // 256) * 3 <= 148:
+            return default_config(M, N, K, dtype, KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
+                                  LOCAL_SPLIT_U=3, isATranspose=isATranspose)
     if N % 128 == 0 and K % 128 == 0 and K >= 1024:
         # few tiles: small tiles with long K blocks (best on the 128- and 512-row shapes)
         return default_config(M, N, K, dtype, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, isATranspose=isATranspose)

@@ -53,7 +53,7 @@ enum kcg_cfg_index {
 #define KCG_KERNEL_TCGEN05 2  /* TMA + tcgen05/TMEM; fp32 runs as 3xTF32 */
 #define KCG_KERNEL_TF32X1 3   /* fp32 in one TF32 pass (reduced accuracy, comparison only) */
 #define KCG_KERNEL_TCGEN05_PAIR 4 /* fp16/bf16 on CTA pairs (tcgen05 cta_group::2), BLOCK_SIZE_M = 256 */
-#define KCG_KERNEL_TCGEN05_CLUSTERK 5 /* fp16/bf16 128-row tiles; LOCAL_SPLIT_U (2..8) CTAs of a thread-block
+#define KCG_KERNEL_TCGEN05_CLUSTERK 5 /* fp16/bf16 128-row tiles; LOCAL_SPLIT_U (2..4) CTAs of a thread-block
                                          cluster split K and reduce through distributed shared memory */
 #define KCG_KERNEL_NAIVE 100  /* one thread per C element, on-device reference */
 #define KCG_KERNEL_WAIT_PROBE 101 /* no GEMM: one bounded wait (20 ms) that expires -> KCG_E_DEVICE_TIMEOUT */

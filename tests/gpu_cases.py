@@ -68,12 +68,12 @@ SEEDED = [
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),
     ("clusterk_bf16_split2_bn64_bk128", 128, 256, 1024, E.bfloat16, "normal",
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=64, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=2)),
-    ("clusterk_bf16_split8_bn256", 128, 512, 4096, E.bfloat16, "normal",
-     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, LOCAL_SPLIT_U=8)),
+    ("clusterk_bf16_split4_bn256", 128, 512, 4096, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, LOCAL_SPLIT_U=4)),
     ("clusterk_bf16_split3_bn256", 256, 768, 1536, E.bfloat16, "normal",   # 8 column blocks dealt 3 + 3 + 2
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, LOCAL_SPLIT_U=3)),
-    ("clusterk_bf16_split5_bn256_bk128", 128, 512, 2560, E.bfloat16, "normal",
-     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=5)),
+    ("clusterk_bf16_split4_bn256_bk128", 128, 512, 2560, E.bfloat16, "normal",   # two stages = the exchange buffers
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=4)),
     ("clusterk_fp16_split4_atrans", 256, 256, 1024, E.float16, "normal",
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4, isATranspose=1)),
     ("clusterk_bf16_uneven_k", 128, 256, 320, E.bfloat16, "uniform",   # 5 K blocks over 4 CTAs: one CTA has none

@@ -356,13 +356,19 @@ def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     kpm = tuned_config(4096, 4096, 4096, E.float32, db=db2)
     assert (kpm.BLOCK_SIZE_N, kpm.BLOCK_SIZE_K, kpm.NUM_STAGES) == (256, 16, 4)
     # untuned shapes fall back to the rule of thumb
-    other = tuned_config(8192, 8192, 8192, E.bfloat16, db=db2)
-    assert other.KERNEL_VARIANT == 4 and other.BLOCK_SIZE_M == 512
-    small = tuned_config(4096, 8192, 8192, E.bfloat16, db=db2)
-    assert small.KERNEL_VARIANT == 0 and small.BLOCK_SIZE_M == 256
-    # one to six waves of 256x256 pair tiles: pair kernel, long K blocks once K is long
-    mid = tuned_config(2048, 8192, 8192, E.bfloat16, db=db2)
+    # at least one wave of 256x256 pair tiles: CTA pairs with 128-wide K blocks, from the largest shapes ...
+    for m in (32768, 8192, 4096, 2048):
+        big = tuned_config(m, 8192, 8192, E.bfloat16, db=db2)
+        assert (big.KERNEL_VARIANT, big.BLOCK_SIZE_M, big.BLOCK_SIZE_N, big.BLOCK_SIZE_K) == (4, 256, 256, 128)
+    mid = tuned_config(512, 11008, 4096, E.bfloat16, db=db2)  # ... down to 86 pair tiles
     assert (mid.KERNEL_VARIANT, mid.BLOCK_SIZE_M, mid.BLOCK_SIZE_N, mid.BLOCK_SIZE_K) == (4, 256, 256, 128)
+    # a single row of tiles: K split over the CTAs of a cluster, four CTAs per 128x128 tile or three per 128x256
+    sk = tuned_config(128, 4096, 11008, E.bfloat16, db=db2)
+    assert (sk.KERNEL_VARIANT, sk.BLOCK_SIZE_N, sk.BLOCK_SIZE_K, sk.LOCAL_SPLIT_U) == (5, 128, 128, 4)
+    sk3 = tuned_config(128, 11008, 11008, E.bfloat16, db=db2)
+    assert (sk3.KERNEL_VARIANT, sk3.BLOCK_SIZE_N, sk3.LOCAL_SPLIT_U) == (5, 256, 3)
+    for kpm in (sk, sk3):
+        kpm.check()
     # short K: the tile with two TMEM accumulator buffers; few tiles: 128x128 with 128-wide K blocks
     short = tuned_config(4096, 4096, 256, E.bfloat16, db=db2)
     assert (short.KERNEL_VARIANT, short.BLOCK_SIZE_M, short.BLOCK_SIZE_N) == (0, 128, 256)
@@ -408,11 +414,11 @@ def test_cluster_split_k_config_rules_and_geometry():
     assert info.kernel == _lib.KERNEL_TCGEN05_CLUSTERK and list(info.cluster) == [4, 1, 1]
     assert info.grid[0] == 32 * 4 and info.block[0] == 192 and info.splitk == 4
     assert info.smem_bytes == info.stages * (128 + 128) * 64 * 2 + 2048
-    assert info.stages * (128 + 128) * 64 * 2 >= 128 * 128 * 4  # ring >= receive buffer
+    assert info.stages * (128 + 128) * 64 * 2 >= (3 + 3) * 128 * 128  # ring >= three receive slots + three staged blocks
     odd = compile_info(default_config(128, 11008, 11008, E.bfloat16, KERNEL_VARIANT=5, BLOCK_SIZE_N=256,
                                       LOCAL_SPLIT_U=3).compileArgs(), kernel=5)
     assert list(odd.cluster) == [3, 1, 1] and odd.grid[0] == 43 * 3  # 8 column blocks dealt 3 + 3 + 2
-    for bad in (dict(LOCAL_SPLIT_U=9), dict(LOCAL_SPLIT_U=1), dict(BLOCK_SIZE_M=256), dict(BLOCK_SIZE_N=64, LOCAL_SPLIT_U=4)):
+    for bad in (dict(LOCAL_SPLIT_U=5), dict(LOCAL_SPLIT_U=1), dict(BLOCK_SIZE_M=256), dict(BLOCK_SIZE_N=64, LOCAL_SPLIT_U=4)):
         keys = dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)
         keys.update(bad)
         with pytest.raises(_lib.KCGError) as ei:
