@@ -537,10 +537,16 @@ def main():
     # against the sustained cuBLAS figure, shorter ones against the burst figure
     peak_kind = "bf16_tflops_sustained" if timed_s > 0.1 else "bf16_tflops"
     peak = peaks[peak_kind]
-    # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum, one-pass ncu captures):
-    # 4.29 GB for the full 32768-row launch of the pair kernel, 227.4 MB for a 2048-row launch of the
-    # single-CTA kernel; other slab heights are scaled by their rows (the traffic grows in proportion).
-    traffic = 4.29e9 * rows / 32768.0 if inc.kernelInfo["kernel"] == 4 else 227.4e6 * rows / 2048.0
+    # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum, one-pass ncu captures, see
+    # profiles/): 4.29 GB for the full 32768-row launch of the 512x256 pair tile; 275.0 MB for a 2048-row launch
+    # of the 256x256x128 pair tile (the tile of the 4096-row slabs); 227.4 MB for a 2048-row launch of the
+    # single-CTA kernel. Other slab heights are scaled by their rows (the traffic grows in proportion).
+    if inc.kernelInfo["kernel"] == 4 and kpm.BLOCK_SIZE_M == 512:
+        traffic = 4.29e9 * rows / 32768.0
+    elif inc.kernelInfo["kernel"] == 4:
+        traffic = 275.0e6 * rows / 2048.0
+    else:
+        traffic = 227.4e6 * rows / 2048.0
     roofline = {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "unit": "TFLOP/s",
                 "frac": round(achieved / peak, 4), "traffic": traffic,
                 "peak_source": f"{peaks['source']} {peak_kind} (cuBLAS bf16 8192^3)",

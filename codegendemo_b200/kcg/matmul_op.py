@@ -59,10 +59,16 @@ def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: i
         # short K: the epilogue weighs as much as the main loop, so take the tile whose two TMEM accumulator
         # buffers overlap them
         return default_config(M, N, K, dtype, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, isATranspose=isATranspose)
+    if M % 512 == 0 and N % 256 == 0 and K % 64 == 0 and (M // 512) * (N // 256) >= 6 * pairs:
+        # six waves and more of 512x256 pair tiles: the largest tile (fewest operand bytes per flop through
+        # L2), its accumulator released in halves. Measured in short bursts at full clock (how the benchmark
+        # runs) it leads; under a sustained power cap the 256x256x128 tile below overtakes it by a few percent.
+        return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
+                              NUM_STAGES=4, isATranspose=isATranspose)
     if K % 128 == 0 and tiles256 >= pairs:
-        # at least one wave of 256x256 pair tiles: CTA pairs with 128-wide K blocks (half as many stage
-        # hand-offs per byte as 64-wide ones, two accumulator buffers); best or within 2 % of the best on
-        # every large shape measured, from 512 x 11008 x 4096 to 32768 x 8192 x 8192
+        # one to twelve waves of 256x256 pair tiles: CTA pairs with 128-wide K blocks (half as many stage
+        # hand-offs per byte as 64-wide ones, two accumulator buffers, stream-K tail); best or within 2 % of
+        # the best on every such shape measured, from 512 x 11008 x 4096 to 4096 x 8192 x 8192
         return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
                               BLOCK_SIZE_K=128, isATranspose=isATranspose)
     if K % 64 == 0 and tiles256 >= pairs:

@@ -11,7 +11,7 @@ import argparse
 import math
 import sys
 
-from codegendemo_b200.kcg.matmul_op import build_kernel, default_config
+from codegendemo_b200.kcg.matmul_op import build_kernel, default_config, tuned_config
 from codegendemo_b200.kcg.Utils import EnumKernelDType
 
 
@@ -28,6 +28,11 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--tuned", action="store_true",
+                    help="start from the kernel database / rule of thumb for this shape instead of the default config")
+    ap.add_argument("--cublas", action="store_true",
+                    help="also launch torch.matmul (cuBLAS) on the same operands the same number of times: "
+                         "a comparison line, and a second kernel in a profiler's launch list")
     a = ap.parse_args(argv)
     edt = {"bf16": EnumKernelDType.bfloat16, "fp16": EnumKernelDType.float16, "fp32": EnumKernelDType.float32}[a.dtype]
     tdt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
@@ -35,7 +40,12 @@ def main(argv=None) -> int:
     for kv in a.set:
         k, v = kv.split("=", 1)
         keys[k] = int(v)
-    kpm = default_config(a.m, a.n, a.k, edt, **keys)
+    if a.tuned:
+        kpm = tuned_config(a.m, a.n, a.k, edt)
+        for k, v in keys.items():
+            setattr(kpm, k, v)
+    else:
+        kpm = default_config(a.m, a.n, a.k, edt, **keys)
     torch.cuda.set_device(a.device)
     dev = f"cuda:{a.device}"
     inConfig, kern = build_kernel(kpm, a.device)
@@ -61,6 +71,20 @@ def main(argv=None) -> int:
     print(f"kernel {inConfig.kernelFuncName}")
     print(f"grid {inConfig.gridDims()} block {inConfig.blockDims()} smem {inConfig.sharedMem()} B")
     print(f"median {med:.4f} ms  {2.0 * a.m * a.n * a.k / (med * 1e9):.1f} TFLOP/s over {a.launches} launches")
+    if a.cublas:
+        ref_out = torch.empty_like(C)
+        lib_times = []
+        for i in range(a.warmup + a.launches):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            torch.matmul(A, B, out=ref_out)
+            e.record()
+            torch.cuda.synchronize()
+            if i >= a.warmup:
+                lib_times.append(s.elapsed_time(e))
+        lib_times.sort()
+        lib = lib_times[len(lib_times) // 2]
+        print(f"torch.matmul (cuBLAS) median {lib:.4f} ms  {2.0 * a.m * a.n * a.k / (lib * 1e9):.1f} TFLOP/s")
     if not a.no_check:
         rows = min(a.m, 512)
         ref = (A[:rows].double() @ B.double()) if tdt == torch.float32 else (A[:rows].float() @ B.float())

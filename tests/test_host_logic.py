@@ -356,11 +356,15 @@ def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     kpm = tuned_config(4096, 4096, 4096, E.float32, db=db2)
     assert (kpm.BLOCK_SIZE_N, kpm.BLOCK_SIZE_K, kpm.NUM_STAGES) == (256, 16, 4)
     # untuned shapes fall back to the rule of thumb
-    # at least one wave of 256x256 pair tiles: CTA pairs with 128-wide K blocks, from the largest shapes ...
-    for m in (32768, 8192, 4096, 2048):
+    # six waves and more of 512x256 pair tiles: the largest tile
+    for m in (32768, 16384, 8192):
         big = tuned_config(m, 8192, 8192, E.bfloat16, db=db2)
-        assert (big.KERNEL_VARIANT, big.BLOCK_SIZE_M, big.BLOCK_SIZE_N, big.BLOCK_SIZE_K) == (4, 256, 256, 128)
-    mid = tuned_config(512, 11008, 4096, E.bfloat16, db=db2)  # ... down to 86 pair tiles
+        assert (big.KERNEL_VARIANT, big.BLOCK_SIZE_M, big.BLOCK_SIZE_N, big.BLOCK_SIZE_K) == (4, 512, 256, 64)
+    # below that, down to one wave of 256x256 pair tiles: CTA pairs with 128-wide K blocks
+    for m in (4096, 2048):
+        slab = tuned_config(m, 8192, 8192, E.bfloat16, db=db2)
+        assert (slab.KERNEL_VARIANT, slab.BLOCK_SIZE_M, slab.BLOCK_SIZE_N, slab.BLOCK_SIZE_K) == (4, 256, 256, 128)
+    mid = tuned_config(512, 11008, 4096, E.bfloat16, db=db2)  # 86 pair tiles
     assert (mid.KERNEL_VARIANT, mid.BLOCK_SIZE_M, mid.BLOCK_SIZE_N, mid.BLOCK_SIZE_K) == (4, 256, 256, 128)
     # a single row of tiles: K split over the CTAs of a cluster, four CTAs per 128x128 tile or three per 128x256
     sk = tuned_config(128, 4096, 11008, E.bfloat16, db=db2)
