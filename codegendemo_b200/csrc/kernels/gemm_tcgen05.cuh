@@ -114,8 +114,12 @@ struct TcGemm {
   };
 #ifdef KCG_TIMELINE
 #define KCG_TL(i) bars->tl[i] = global_timer_ns()
+#define KCG_TLC(var) const long long var = clock64()
+#define KCG_TLC_ADD(i, var) bars->tl[i] += static_cast<uint64_t>(clock64() - var)
 #else
 #define KCG_TL(i) ((void)0)
+#define KCG_TLC(var) ((void)0)
+#define KCG_TLC_ADD(i, var) ((void)0)
 #endif
   static_assert(sizeof(Barriers) <= 1024, "barrier block exceeds its shared-memory slot");
 
@@ -140,6 +144,12 @@ struct TcGemm {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
+#ifdef KCG_TIMELINE
+    if (threadIdx.x == 0) {
+      for (int i = 10; i < 16; ++i) bars->tl[i] = 0;
+    }
+    __syncthreads();
+#endif
     if (threadIdx.x == 0) KCG_TL(0);
 
     const int warp = threadIdx.x >> 5;
@@ -192,11 +202,14 @@ struct TcGemm {
         }
         const uint32_t s = p_it % kStages;
         const uint32_t ph = (p_it / kStages) & 1u;
+        KCG_TLC(c_wait);
         if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
           report(p, bars, KCG_ST_TIMEOUT_PRODUCER, p_it, s);
           p_ok = false;
           break;
         }
+        KCG_TLC_ADD(10, c_wait);
+        KCG_TLC(c_issue);
         const Unit& w = p_w;
         uint8_t* sa = smem + s * STAGE_BYTES;
         uint8_t* sb = sa + L.a_bytes;
@@ -244,6 +257,7 @@ struct TcGemm {
             }
           }
         }
+        KCG_TLC_ADD(11, c_issue);
         if (p_it == 0) KCG_TL(2);
         ++p_it;
         ++p_kb;
@@ -310,11 +324,13 @@ struct TcGemm {
               const uint64_t adesc =
                   make_smem_desc(sa + a_t + a_off, L.a_lbo, L.a_sbo, L.a_desc_swizzle);
               const uint32_t d = tmem_acc + t * kBN;
+#ifndef KCG_PROBE_NO_MMA  // measurement builds only: loads and barriers run, the products do not
               if constexpr (kPair) {
                 umma_ss_pair<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
               } else {
                 umma_ss<kTf32>(d, adesc, bdesc, IDESC, acc_flag);
               }
+#endif
             }
           }
         };
@@ -370,15 +386,19 @@ struct TcGemm {
           for (; kb < w.kbn; ++kb, ++it) {
             const uint32_t s = it % kStages;
             const uint32_t ph = (it / kStages) & 1u;
+            KCG_TLC(c_wait);
             if (!mbar_wait(&bars->full[s], ph, &bars->abort_flag)) {
               report(p, bars, KCG_ST_TIMEOUT_MMA, it, s);
               ok = false;
               break;
             }
+            KCG_TLC_ADD(12, c_wait);
             tc_fence_after_sync();
             if (it == 0) KCG_TL(3);
+            KCG_TLC(c_issue);
             issue(s, kb, 0, MT, tmem_acc);
             free_stage(s);
+            KCG_TLC_ADD(13, c_issue);
           }
           if (acc_it == 0) KCG_TL(4);
           if (ok) {
@@ -727,7 +747,7 @@ struct TcGemm {
 #ifdef KCG_TIMELINE
     __syncthreads();
     if (threadIdx.x == 0 && blockIdx.x == 0)
-      for (int i = 0; i < 10; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
+      for (int i = 0; i < 16; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
 #endif
   }
 };

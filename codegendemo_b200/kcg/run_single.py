@@ -15,6 +15,25 @@ from codegendemo_b200.kcg.matmul_op import build_kernel, default_config, tuned_c
 from codegendemo_b200.kcg.Utils import EnumKernelDType
 
 
+_PHASES = ["entry", "set-up barrier passed", "first TMA issued", "first stage landed", "MMAs of unit 0 issued",
+           "accumulator of unit 0 seen full", "last C store of unit 0 issued", "C stores read out",
+           "exit barrier passed", "TMEM released"]
+_PHASES_CLUSTERK = ["entry", "set-up barrier passed", "first TMA issued", "MMAs issued", "accumulator seen full",
+                    "partials pushed", "peers' partials received", "C stored", "TMEM released"]
+
+
+def print_timeline(C, variant: int) -> None:
+    """Decodes the %globaltimer stamps a KCG_TIMELINE build of the tcgen05 kernels leaves in C[0, :]."""
+    import torch
+    t = C.view(torch.uint8).flatten()[:128].view(torch.int64).cpu().tolist()
+    names = _PHASES_CLUSTERK if variant == 5 else _PHASES
+    print(f"in-kernel time of CTA 0: {(t[len(names) - 1] - t[0]) / 1e3:.2f} us")
+    print("  " + "  ".join(f"{names[i]} +{(t[i] - t[0]) / 1e3:.2f}" for i in range(1, len(names))))
+    if variant != 5:
+        print(f"  cycles over the K loop: producer waiting {t[10]}, producer issuing {t[11]}, "
+              f"MMA thread waiting {t[12]}, MMA thread issuing {t[13]}")
+
+
 def main(argv=None) -> int:
     import torch
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -33,6 +52,11 @@ def main(argv=None) -> int:
     ap.add_argument("--cublas", action="store_true",
                     help="also launch torch.matmul (cuBLAS) on the same operands the same number of times: "
                          "a comparison line, and a second kernel in a profiler's launch list")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the in-kernel phase stamps of CTA 0. Needs kernels compiled with "
+                         "KCG_NVCC_FLAGS=-DKCG_TIMELINE=1 (add -DKCG_PROBE_NO_MMA=1 to time the operand loads "
+                         "alone) into a private KCG_CACHE_DIR; such kernels overwrite the first words of C, "
+                         "so the result check is skipped")
     a = ap.parse_args(argv)
     edt = {"bf16": EnumKernelDType.bfloat16, "fp16": EnumKernelDType.float16, "fp32": EnumKernelDType.float32}[a.dtype]
     tdt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[a.dtype]
@@ -71,6 +95,9 @@ def main(argv=None) -> int:
     print(f"kernel {inConfig.kernelFuncName}")
     print(f"grid {inConfig.gridDims()} block {inConfig.blockDims()} smem {inConfig.sharedMem()} B")
     print(f"median {med:.4f} ms  {2.0 * a.m * a.n * a.k / (med * 1e9):.1f} TFLOP/s over {a.launches} launches")
+    if a.timeline:
+        print_timeline(C, kpm.KERNEL_VARIANT)
+        return 0
     if a.cublas:
         ref_out = torch.empty_like(C)
         lib_times = []
