@@ -75,6 +75,7 @@ struct TcGemmClusterK {
     uint64_t tmem_full;
     uint64_t ring_free[4];  // [r]: CTA r of the cluster no longer touches its operand ring
     uint64_t recv_full;     // all slices for this CTA have arrived (transaction bytes of the bulk copies)
+    uint64_t staged[8];     // [f]: the four epilogue warps have laid down the f-th block that leaves this CTA
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
 #ifdef KCG_TIMELINE
@@ -112,6 +113,9 @@ struct TcGemmClusterK {
     const int num_kb = (p.K + kBK - 1) / kBK;
 
     if (threadIdx.x == 0) {
+#ifdef KCG_TIMELINE
+      for (int i = 0; i < 16; ++i) bars->tl[i] = 0;
+#endif
       KCG_CTL(0);
       // the first TMA instruction needs its descriptor: start fetching the maps before anything else
       tma_prefetch_desc(&p.tmA);
@@ -123,6 +127,7 @@ struct TcGemmClusterK {
       mbar_init(&bars->tmem_full, 1);
       for (int r = 0; r < 4; ++r) mbar_init(&bars->ring_free[r], 1);
       mbar_init(&bars->recv_full, 1);
+      for (int f = 0; f < 8; ++f) mbar_init(&bars->staged[f], 4);  // one arrival per epilogue warp
       bars->abort_flag = 0u;
       fence_mbar_init();
       fence_proxy_async_smem();
@@ -142,60 +147,103 @@ struct TcGemmClusterK {
     const int per = (num_kb + kSplit - 1) / kSplit;
     const int kb0 = static_cast<int>(rank) * per;
     const int kbn = (kb0 >= num_kb) ? 0 : ((num_kb - kb0 < per) ? num_kb - kb0 : per);
-
-    // Producer (thread 0), entered twice: before the set-up barrier for the first two stages - the loads
-    // signal only this CTA's own barriers, which this very thread has just initialised, so the first
-    // operands are in flight while TMEM is allocated - and again as warp 0's role.
-    int p_kb = 0;
-    auto produce = [&](int kb_limit) {
-      for (; p_kb < kbn && p_kb < kb_limit; ++p_kb) {
-        const int kb = p_kb;
-        const uint32_t s = kb % kStages;
-        const uint32_t ph = (kb / kStages) & 1u;
-        if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
-          report(p, bars, KCG_ST_TIMEOUT_PRODUCER, kb, s);
-          p_kb = kbn;
-          break;
+    // The blocks this CTA owns, and the order in which the others leave it: owner by owner, starting with
+    // the next rank (so that the cluster's CTAs do not all write to the same one first). As the owners'
+    // runs of blocks are contiguous, the f-th block to leave is simply block (own_end + f) mod NCH.
+    const int own_first = first_block_of(static_cast<int>(rank));
+    const int own_end = first_block_of(static_cast<int>(rank) + 1);
+    const int own_count = own_end - own_first;
+    const int foreign = NCH - own_count;
+    uint8_t* const stage_out = smem + RECV_BYTES;  // staging area behind the receive area
+    auto block_of = [&](int f) { return (own_end + f) % NCH; };
+    auto staged_at = [&](int c) {  // where block c waits to leave (the staging area skips the own blocks)
+      return stage_out + (c < own_first ? c : c - own_count) * BLOCK_BYTES;
+    };
+    // Shipping: warps 0 and 1 are idle once the loads and the MMAs are issued; their first lanes send the
+    // staged blocks (warp 0 the even ones, warp 1 the odd ones) - 16 KB, contiguous, one bulk copy each -
+    // as soon as the four epilogue warps have laid a block down and its owner's ring is idle. Issuing a
+    // copy takes the lane about 0.2 us, which the staging warps would otherwise spend between blocks.
+    auto ship = [&](int first_f) {
+      for (int f = first_f; f < foreign; f += 2) {
+        const int c = block_of(f);
+        const uint32_t owner = static_cast<uint32_t>(owner_of(c));
+        if (!mbar_wait(&bars->staged[f], 0u, &bars->abort_flag)) {
+          if (bars->abort_flag == 0u) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 3u, static_cast<uint32_t>(f));
+          return;
         }
-        uint8_t* sa = smem + s * STAGE_BYTES;
-        uint8_t* sb = sa + L.a_bytes;
-        const int k0 = (kb0 + kb) * kBK;
-        const int am0 = kATrans ? w.mcol : w.m0;
-        const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
-        mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_BYTES));
-#pragma unroll
-        for (int j = 0; j < L.a_boxes; ++j) {
-          if constexpr (kATrans) {
-            tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
-          } else {
-            tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
-          }
+        if (!mbar_wait(&bars->ring_free[owner], 0u, &bars->abort_flag)) {
+          if (bars->abort_flag == 0u) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 1u, owner);
+          return;
         }
-#pragma unroll
-        for (int j = 0; j < L.b_boxes; ++j)
-          tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, kb_row);
-        if (kb == 0) KCG_CTL(2);
+        const uint32_t slot = rank < owner ? rank : rank - 1u;  // senders in rank order, the owner left out
+        const int o_first = first_block_of(static_cast<int>(owner));
+        const uint32_t dst_local = smem_u32(smem) + slot * SLICE_BYTES + (c - o_first) * BLOCK_BYTES;
+        bulk_copy_to_cta(map_to_cta(dst_local, owner), smem_u32(staged_at(c)), BLOCK_BYTES,
+                         map_to_cta(smem_u32(&bars->recv_full), owner));
       }
     };
-    if (threadIdx.x == 0) produce(2);
+
     if (warp == 1) {
       tmem_alloc(&bars->tmem_base, TMEM_COLS);
       tmem_relinquish();
     }
-    __syncwarp();  // thread 0 rejoins its warp before the block-wide barrier
-    tc_fence_before_sync();
-    __syncthreads();
-    // Every CTA's barriers must exist before anyone signals them - but nothing crosses CTAs before the
-    // exchange: arrive on the cluster barrier now, wait for it only there (cluster_wait below), and
-    // keep the main loop free of the cluster's start-up skew.
-    cluster_arrive();
-    tc_fence_after_sync();
-    const uint32_t tmem_base = bars->tmem_base;
-    if (threadIdx.x == 0) KCG_CTL(1);
+    // Set-up meeting on named barrier 3. Warp 0 needs nothing from the others (thread 0 initialised the
+    // barriers itself, and its loads signal only those), so it merely arrives and starts loading at
+    // once; the MMA and epilogue warps wait for the barriers and the TMEM address.
+    if (warp == 0) {
+      __syncwarp();
+      named_bar_arrive(3, NUM_THREADS);
+    } else {
+      tc_fence_before_sync();
+      named_bar_sync(3, NUM_THREADS);
+      tc_fence_after_sync();
+    }
+    // Every CTA's barriers must exist before another CTA signals them - but nothing crosses CTAs before
+    // the exchange: arrive on the cluster barrier now (thread 0's fence.mbarrier_init has published the
+    // fresh barriers, so the arrival itself needs no ordering), wait for it only there (cluster_wait
+    // below), and keep the main loop free of the cluster's start-up skew.
+    cluster_arrive_relaxed();
+    const uint32_t tmem_base = (warp == 0) ? 0u : bars->tmem_base;
+    if (threadIdx.x == 32) KCG_CTL(1);
 
     if (warp == 0) {
       // ------------------------------------------------------------ producer
-      if (lane == 0) produce(kbn);
+      if (lane == 0) {
+        for (int kb = 0; kb < kbn; ++kb) {
+          const uint32_t s = kb % kStages;
+          const uint32_t ph = (kb / kStages) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u, &bars->abort_flag)) {
+            report(p, bars, KCG_ST_TIMEOUT_PRODUCER, kb, s);
+            break;
+          }
+          uint8_t* sa = smem + s * STAGE_BYTES;
+          uint8_t* sb = sa + L.a_bytes;
+          const int k0 = (kb0 + kb) * kBK;
+          const int am0 = kATrans ? w.mcol : w.m0;
+          const int ka = kATrans ? k0 + w.kofs : k0, kb_row = k0 + w.kofs;
+          mbar_expect_tx(&bars->full[s], static_cast<uint32_t>(STAGE_BYTES));
+#pragma unroll
+          for (int j = 0; j < L.a_boxes; ++j) {
+            if constexpr (kATrans) {
+              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], am0 + j * L.atom, ka);
+            } else {
+              tma_load_2d(sa + j * L.a_box_bytes, &p.tmA, &bars->full[s], ka + j * L.a_box_inner, am0);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < L.b_boxes; ++j)
+            tma_load_2d(sb + j * L.b_box_bytes, &p.tmB, &bars->full[s], w.n0 + j * L.atom, kb_row);
+          if (kb == 0) KCG_CTL(2);
+        }
+      }
+      __syncwarp();
+      cluster_wait();  // set-up phase of the cluster barrier: the other CTAs' barriers exist
+      if (lane == 0) {
+        ship(0);
+        KCG_CTL(5);
+      }
+      __syncwarp();
+      cluster_arrive_relaxed();  // second phase (see the epilogue warps)
     } else if (warp == 1) {
       // ---------------------------------------------------------- MMA issuer
       if (lane == 0) {
@@ -230,6 +278,14 @@ struct TcGemmClusterK {
         KCG_CTL(3);
         if (ok && kbn > 0) umma_commit(&bars->tmem_full);
       }
+      __syncwarp();
+      cluster_wait();
+      if (lane == 0) {
+        ship(1);
+        KCG_CTL(12);
+      }
+      __syncwarp();
+      cluster_arrive_relaxed();
     } else {
       // ------------------------------------------ epilogue: exchange, add, store
       const int q = warp & 3;  // TMEM lane quarter this warp may read
@@ -241,68 +297,65 @@ struct TcGemmClusterK {
       const bool have_acc = named_bar_all(2, NUM_EPI_THREADS, ok);
       if (!have_acc && !ok) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 0u, rank);
       cluster_wait();  // the other CTAs' barriers are initialised (all four warps, every lane)
+      bool all_in = false;
       if (have_acc) {
         tc_fence_after_sync();
         if (epi_tid == 0) KCG_CTL(4);
-        // This CTA's MMAs have retired (or it had none): its ring is free to receive slices.
-        if (epi_tid == 0) {
-          for (uint32_t j = 0; j < static_cast<uint32_t>(kSplit); ++j)
-            mbar_arrive_cluster(map_to_cta(smem_u32(&bars->ring_free[rank]), j));
-        }
+        // This CTA's MMAs have retired (or it had none): its ring is free to receive slices. One lane per
+        // CTA of the cluster tells it so.
+        if (epi_tid < kSplit)
+          mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(&bars->ring_free[rank]), static_cast<uint32_t>(epi_tid)));
+        if (epi_tid == 0) KCG_CTL(9);
         const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        uint8_t* stage_out = smem + RECV_BYTES;  // staging area behind the receive area
-        const int own_first = first_block_of(static_cast<int>(rank));
-        const int own_count = first_block_of(static_cast<int>(rank) + 1) - own_first;
-        // ---- stage: every block owned by another CTA is laid down in this CTA's (idle) ring first ...
-#pragma unroll 1
-        for (int c = 0; c < NCH; ++c) {
-          if (owner_of(c) == static_cast<int>(rank)) continue;
-          uint32_t r[32];
+        // ---- stage: the blocks that belong to other CTAs are laid down in this CTA's (idle) ring in the
+        // order in which they leave; the TMEM read of the next block is in flight while a block is stored.
+        auto load_block = [&](int f, uint32_t (&r)[32]) {
           if (kbn > 0) {
-            tmem_ld_32x32b_x32(tmem_acc + c * 32, r);
-            tmem_ld_wait();
+            tmem_ld_32x32b_x32(tmem_acc + block_of(f) * 32, r);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
-          // this warp's 32 rows of block c, 4 KB (the staging area skips this CTA's own blocks)
-          uint8_t* rowp = stage_out + (c < own_first ? c : c - own_count) * BLOCK_BYTES + q * 32 * 128 + lane * 128;
+        };
+        auto stage_block = [&](int f, const uint32_t (&r)[32]) {
+          uint8_t* rowp = staged_at(block_of(f)) + row * 128;
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) =
                 make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-        }
-        fence_proxy_async_smem();  // generic-proxy writes visible to the bulk copy engine
-        __syncwarp();
-        // ---- ... push: then one lane ships them, owner by owner (starting with the next rank, so that the
-        // cluster's CTAs do not all write to the same one first), as soon as that owner's ring is idle
-        if (lane == 0) {
-          for (int d = 1; d < kSplit && ok; ++d) {
-            const uint32_t owner = (rank + static_cast<uint32_t>(d)) % static_cast<uint32_t>(kSplit);
-            if (!mbar_wait(&bars->ring_free[owner], 0u, &bars->abort_flag)) {
-              report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 1u, owner);
-              ok = false;
-              break;
-            }
-            const uint32_t slot = rank < owner ? rank : rank - 1u;  // senders in rank order, the owner left out
-            const uint32_t bar = map_to_cta(smem_u32(&bars->recv_full), owner);
-            const int o_first = first_block_of(static_cast<int>(owner));
-            const int o_end = first_block_of(static_cast<int>(owner) + 1);
-            for (int c = o_first; c < o_end; ++c) {
-              const uint32_t src =
-                  smem_u32(stage_out + (c < own_first ? c : c - own_count) * BLOCK_BYTES + q * 32 * 128);
-              const uint32_t dst_local = smem_u32(smem) + slot * SLICE_BYTES + (c - o_first) * BLOCK_BYTES + q * 32 * 128;
-              bulk_copy_to_cta(map_to_cta(dst_local, owner), src, 32 * 128, bar);
+          fence_proxy_async_smem();  // generic-proxy writes visible to the bulk copy engine
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->staged[f]);
+        };
+        {
+          uint32_t ra[32], rb[32];
+          if (foreign > 0) load_block(0, ra);
+#pragma unroll 1
+          for (int f = 0; f < foreign; f += 2) {
+            tmem_ld_wait();
+            if (f + 1 < foreign) load_block(f + 1, rb);
+            stage_block(f, ra);
+            if (f + 1 < foreign) {
+              tmem_ld_wait();
+              if (f + 2 < foreign) load_block(f + 2, ra);
+              stage_block(f + 1, rb);
             }
           }
         }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (epi_tid == 0) KCG_CTL(5);
+        if (epi_tid == 0) KCG_CTL(10);
         bool got = ok && mbar_wait_cluster(&bars->recv_full, 0u, &bars->abort_flag);
-        const bool all_in = named_bar_all(2, NUM_EPI_THREADS, got);
+        all_in = named_bar_all(2, NUM_EPI_THREADS, got);
         if (!all_in && ok && !got) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 2u, rank);
         if (epi_tid == 0) KCG_CTL(6);
-        if (all_in) {
+      }
+      // Second phase of the cluster barrier, which guards the CTAs' lifetimes: this CTA has received
+      // everything (or has given up), so no copy into it is in flight any more. Once every CTA of the
+      // cluster has said so, all copies have landed and each may leave; the wait is at the common exit,
+      // behind the adding and storing below.
+      cluster_arrive_relaxed();
+      if (all_in) {
+        const uint32_t tmem_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        {
           // ---- add: for every block this CTA owns, each thread adds - for its own row - the slices in
           // rank (= K) order, its own from TMEM, and stores 32 values of C
           OutT* Cout = reinterpret_cast<OutT*>(p.C);
@@ -316,6 +369,7 @@ struct TcGemmClusterK {
             if (kbn > 0) {
               tmem_ld_32x32b_x32(tmem_acc + c * 32, own);
               tmem_ld_wait();
+              if (epi_tid == 0 && c == c_first) KCG_CTL(15);
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) own[i] = 0u;
@@ -341,6 +395,7 @@ struct TcGemmClusterK {
                 }
               }
             }
+            if (epi_tid == 0 && c == c_first) KCG_CTL(11);
             const int gcol = w.n0 + c * 32;
             if (grow >= p.M || gcol >= p.N) continue;
             if (p.epi_flags != 0u) epi_span<OutT, 32>(p, v, grow, gcol);
@@ -360,6 +415,7 @@ struct TcGemmClusterK {
               }
               dst[j] = make_uint4(h[0], h[1], h[2], h[3]);
             }
+            if (epi_tid == 0 && c == c_first) KCG_CTL(13);
           }
         }
       }
@@ -369,7 +425,6 @@ struct TcGemmClusterK {
     // The producer and MMA roles run in one lane; the other lanes of those warps come straight here.
     // Reconverge every warp first: the block-wide barrier below must be executed by whole warps.
     __syncwarp();
-    if (warp < 2) cluster_wait();  // warps 0 and 1 complete the set-up phase of the cluster barrier here
     if (bars->abort_flag != 0u) {
       // Give copies / MMAs still in flight time to land before shared memory and TMEM are released.
       const uint64_t t0 = global_timer_ns();
@@ -378,7 +433,7 @@ struct TcGemmClusterK {
     if (threadIdx.x == 64) KCG_CTL(7);
     tc_fence_before_sync();
     __syncthreads();
-    cluster_sync_all();  // no CTA leaves while another may still write into its shared memory
+    cluster_wait();  // no CTA leaves while another may still write into its shared memory or read from it
     if (warp == 1) {
       __syncwarp();
       tc_fence_after_sync();
@@ -388,7 +443,7 @@ struct TcGemmClusterK {
 #ifdef KCG_TIMELINE
     __syncthreads();
     if (threadIdx.x == 0 && blockIdx.x == 0)
-      for (int i = 0; i < 9; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
+      for (int i = 0; i < 16; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
 #endif
   }
 };

@@ -305,7 +305,23 @@ __device__ __forceinline__ void cluster_arrive() {
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Arrival without memory ordering: for phases that only order execution (what must be visible across
+// CTAs is published by other means: fence.mbarrier_init for fresh barriers, mbarrier completion for data).
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+// Non-blocking arrival of a whole warp on a named barrier on which other warps wait with bar.sync;
+// `nthreads` counts arriving and waiting threads together.
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 
+// The same without memory ordering: for a signal that only says "I have stopped reading" (nothing the
+// signalling thread wrote has to become visible with it).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
 // Arrive on an mbarrier that lives in another CTA of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)

@@ -74,19 +74,39 @@ def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: i
     if K % 64 == 0 and tiles256 >= pairs:
         return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
                               BLOCK_SIZE_K=64, isATranspose=isATranspose)
-    if M == 128 and K >= 2048:
-        # one row of tiles: far fewer tiles than SMs. K is split over the CTAs of a cluster (KERNEL_VARIANT 5,
-        # reduction in shared memory) so that four (three) times as many SMs stream B
-        if N % 128 == 0 and K % 128 == 0 and (N // 128) * 4 <= 148:
-            return default_config(M, N, K, dtype, KERNEL_VARIANT=5, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128,
-                                  LOCAL_SPLIT_U=4, isATranspose=isATranspose)
-        if N % 256 == 0 and K % 64 == 0 and K >= 8192 and (N // 256) * 3 <= 148:
-            return default_config(M, N, K, dtype, KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64,
-                                  LOCAL_SPLIT_U=3, isATranspose=isATranspose)
+    pick = clusterk_choice(M, N, K)
+    if pick is not None:
+        # fewer 128-row tiles than SMs: K is split over the CTAs of a cluster (KERNEL_VARIANT 5, reduction in
+        # shared memory) so that two to four times as many SMs stream the operands
+        bn, bk, split = pick
+        return default_config(M, N, K, dtype, KERNEL_VARIANT=5, BLOCK_SIZE_N=bn, BLOCK_SIZE_K=bk,
+                              LOCAL_SPLIT_U=split, isATranspose=isATranspose)
     if N % 128 == 0 and K % 128 == 0 and K >= 1024:
         # few tiles: small tiles with long K blocks (best on the 128- and 512-row shapes)
         return default_config(M, N, K, dtype, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, isATranspose=isATranspose)
     return default_config(M, N, K, dtype, isATranspose=isATranspose)
+
+
+def clusterk_choice(M: int, N: int, K: int, sms: int = 148):
+    """(BLOCK_SIZE_N, BLOCK_SIZE_K, LOCAL_SPLIT_U) of the cluster split-K kernel for a 16-bit problem with fewer
+    128-row tiles than SMs, or None when it does not apply. Of the tile widths 128 and 256, each with the largest
+    split of 2..4 whose CTAs still fit one wave, the one that occupies more SMs wins; at equal count the wider
+    tile (fewer operand bytes through each SM, less to exchange). Measured: 128 x 4096 x 4096 -> 128 wide, split 4;
+    128 x 11008 x K -> 256 wide, split 3; 512 x 4096 x K -> 256 wide, split 2, each ahead of the whole-K kernels."""
+    if M % 128 != 0 or M > 512 or K < 2048:
+        return None
+    best = None
+    for bn, bk in ((128, 128), (256, 64)):
+        if N % bn != 0 or K % bk != 0:
+            continue
+        tiles = (M // 128) * (N // bn)
+        split = min(4, sms // tiles) if tiles > 0 else 0
+        if split < 2 or (K // bk) < 4 * split:
+            continue
+        ctas = tiles * split
+        if best is None or ctas >= best[0]:
+            best = (ctas, bn, bk, split)
+    return None if best is None else best[1:]
 
 
 def build_kernel(kpm: KernelArgMatmul, deviceId: int = 0):

@@ -19,7 +19,7 @@ _PHASES = ["entry", "set-up barrier passed", "first TMA issued", "first stage la
            "accumulator of unit 0 seen full", "last C store of unit 0 issued", "C stores read out",
            "exit barrier passed", "TMEM released"]
 _PHASES_CLUSTERK = ["entry", "set-up barrier passed", "first TMA issued", "MMAs issued", "accumulator seen full",
-                    "partials pushed", "peers' partials received", "C stored", "TMEM released"]
+                    "warp 0's copies issued", "peers' partials received", "C stored", "TMEM released"]
 
 
 def print_timeline(C, variant: int) -> None:
@@ -29,6 +29,10 @@ def print_timeline(C, variant: int) -> None:
     names = _PHASES_CLUSTERK if variant == 5 else _PHASES
     print(f"in-kernel time of CTA 0: {(t[len(names) - 1] - t[0]) / 1e3:.2f} us")
     print("  " + "  ".join(f"{names[i]} +{(t[i] - t[0]) / 1e3:.2f}" for i in range(1, len(names))))
+    if variant == 5:
+        extra = {9: "ring-idle signals sent", 10: "blocks staged", 12: "warp 1's copies issued", 15: "own block read",
+                 11: "first block summed", 13: "first block stored"}
+        print("  " + "  ".join(f"{name} +{(t[i] - t[0]) / 1e3:.2f}" for i, name in extra.items() if t[i] > t[0]))
     if variant != 5:
         print(f"  cycles over the K loop: producer waiting {t[10]}, producer issuing {t[11]}, "
               f"MMA thread waiting {t[12]}, MMA thread issuing {t[13]}")

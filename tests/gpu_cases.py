@@ -80,6 +80,10 @@ SEEDED = [
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),
     ("clusterk_bf16_skinny_4096", 128, 4096, 4096, E.bfloat16, "normal",
      dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=4)),
+    ("clusterk_bf16_four_tile_rows_split2", 512, 2048, 2048, E.bfloat16, "normal",   # 32 tiles, 64 CTAs
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, LOCAL_SPLIT_U=2)),
+    ("clusterk_fp16_split3_bn128", 128, 384, 1536, E.float16, "uniform",   # 4 column blocks dealt 2 + 1 + 1
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, LOCAL_SPLIT_U=3)),
     # REG_PREFETCH = 0: one accumulator buffer, no overlap of the drain with the next tile
     ("bf16_no_acc_overlap", 512, 1024, 512, E.bfloat16, "normal", dict(REG_PREFETCH=0)),
     ("pair_bf16_512_no_acc_overlap", 2048, 1024, 512, E.bfloat16, "normal",

@@ -371,6 +371,16 @@ def test_kernel_db_keeps_fastest_correct_result_per_shape(tmp_path):
     assert (sk.KERNEL_VARIANT, sk.BLOCK_SIZE_N, sk.BLOCK_SIZE_K, sk.LOCAL_SPLIT_U) == (5, 128, 128, 4)
     sk3 = tuned_config(128, 11008, 11008, E.bfloat16, db=db2)
     assert (sk3.KERNEL_VARIANT, sk3.BLOCK_SIZE_N, sk3.LOCAL_SPLIT_U) == (5, 256, 3)
+    # the same rule covers up to four rows of tiles while the clusters still fit one wave
+    for shape, want in (((128, 11008, 4096), (5, 256, 64, 3)), ((512, 4096, 4096), (5, 256, 64, 2)),
+                        ((512, 4096, 11008), (5, 256, 64, 2)), ((256, 4096, 4096), (5, 256, 64, 4)),
+                        ((128, 4096, 4096), (5, 128, 128, 4))):
+        ck = tuned_config(*shape, E.bfloat16, db=db2)
+        assert (ck.KERNEL_VARIANT, ck.BLOCK_SIZE_N, ck.BLOCK_SIZE_K, ck.LOCAL_SPLIT_U) == want, shape
+        ck.check()
+    from codegendemo_b200.kcg.matmul_op import clusterk_choice
+    assert clusterk_choice(512, 11008, 11008) is None and clusterk_choice(2048, 4096, 4096) is None
+    assert clusterk_choice(128, 4096, 1024) is None and clusterk_choice(100, 4096, 4096) is None
     for kpm in (sk, sk3):
         kpm.check()
     # short K: the tile with two TMEM accumulator buffers; few tiles: 128x128 with 128-wide K blocks
