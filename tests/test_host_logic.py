@@ -498,3 +498,24 @@ def test_cost_model_prefilter_drops_configs_that_idle_most_sms(tmp_path):
     assert ConfigGenerator.get_cfgs(str(f)) == kept
     f.write_text(json.dumps(space))
     assert ConfigGenerator.get_cfgs(str(f)) == allc
+
+
+@pytest.mark.parametrize("space", ["128x4096", "128x11008", "512x4096", "512x11008"])
+def test_cost_prefilter_of_the_shipped_spaces_keeps_the_measured_winner(space):
+    """The rectangular bf16 tuning spaces carry COST_PREFILTER = 2.0: the filter must shrink them and must not
+    drop the config the operator picks for the shape (the measured winner)."""
+    import os
+    from codegendemo_b200.kcg.matmul_op import tuned_config
+    path = os.path.join(os.path.dirname(ConfigGenerator.__file__), "..", "TuningConfigs",
+                        f"GEMM_configs_{space}_bf16_b200.json")
+    options = ConfigGenerator.read_params(path)
+    assert options.get("COST_PREFILTER") == [2.0]
+    kept = ConfigGenerator.get_cfgs(path)
+    unfiltered = list(ConfigGenerator.iter_cfgs({k: v for k, v in options.items() if k != "COST_PREFILTER"}))
+    assert 0 < len(kept) < len(unfiltered)
+    M, N, K = kept[0][kw.KEY_M], kept[0][kw.KEY_N], kept[0][kw.KEY_K]
+    t = tuned_config(M, N, K, E.bfloat16)
+    want = (t.KERNEL_VARIANT, t.BLOCK_SIZE_M, t.BLOCK_SIZE_N, t.BLOCK_SIZE_K, t.LOCAL_SPLIT_U)
+    have = {(c.get(kw.KEY_KERNEL_VARIANT), c[kw.KEY_BLOCK_SIZE_M], c[kw.KEY_BLOCK_SIZE_N], c[kw.KEY_BLOCK_SIZE_K],
+             c.get(kw.KEY_LOCAL_SPLIT_U, 1)) for c in kept}
+    assert want in have
