@@ -353,6 +353,78 @@ def other_workloads(device: int, peaks: dict, sampler: "ClockSampler", launches:
     return out, group_clocks
 
 
+def chain_workloads(device: int, sampler: "ClockSampler", launches: int = 20):
+    """The operators around the plain product (batched, strided, attention-shaped chain), each timed like the
+    workloads above beside the PyTorch library call for the same thing and checked against the host composition
+    at fp32 (the oracle's ``torch.matmul`` plus ``torch.softmax``): a sample of the result, outside the timing."""
+    import torch
+    from oracle import oracle
+    from codegendemo_b200.kcg import matmul_op
+    dev = f"cuda:{device}"
+    out = []
+    t_g0 = time.time()
+    g = torch.Generator().manual_seed(0)
+
+    def entry(tag, flops, ours, lib, lib_name, max_rel, note):
+        ts = sorted(time_launches(ours, launches, 3))
+        tl = sorted(time_launches(lib, launches, 3))
+        g_ours, g_lib = time_graph(ours, launches), time_graph(lib, launches)
+        med, lib_med = ts[len(ts) // 2], tl[len(tl) // 2]
+        out.append({"workload": tag, "dtype": "bf16", "ms": round(med, 4), "ms_best": round(ts[0], 4),
+                    "tflops": round(flops / (med * 1e9), 1), "library": lib_name,
+                    "library_tflops": round(flops / (lib_med * 1e9), 1), "vs_library": round(lib_med / med, 3),
+                    "graph_replay": None if (g_ours is None or g_lib is None) else {
+                        "ms": round(g_ours, 4), "library_ms": round(g_lib, 4), "vs_library": round(g_lib / g_ours, 3)},
+                    "oracle_check": {"max_rel": max_rel, "tol": TOL_16BIT, "ok": bool(max_rel <= TOL_16BIT),
+                                     "against": note}, "launches": launches, "group": "operators around the product"})
+
+    def rel(got, ref):
+        ref = ref.float()
+        return float(((got.float().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-30)).item())
+
+    try:  # batched product: 16 x (1024 x 1024 x 1024)
+        a = (torch.randn(16, 1024, 1024, generator=g) / 32).bfloat16().to(dev)
+        b = (torch.randn(16, 1024, 1024, generator=g) / 32).bfloat16().to(dev)
+        c = torch.empty(16, 1024, 1024, dtype=torch.bfloat16, device=dev)
+        matmul_op.bmm(a, b, c)
+        err = max(rel(c[i], oracle.host_matmul(a[i], b[i])) for i in (0, 15))
+        entry("bmm bf16 16 x 1024^3", 2.0 * 16 * 1024 ** 3, lambda: matmul_op.bmm(a, b, c),
+              lambda: torch.bmm(a, b, out=c), "torch.bmm (cuBLAS)", err, "host torch.matmul fp32 of batches 0 and 15")
+        del a, b, c
+    except Exception as e:
+        out.append({"workload": "bmm bf16 16 x 1024^3", "error": str(e)[:300]})
+    try:  # operands with a row pitch: column blocks of wider tensors, nothing copied
+        wide_a = (torch.randn(2048, 8192, generator=g) / 64).bfloat16().to(dev)
+        wide_b = (torch.randn(4096, 8192, generator=g) / 64).bfloat16().to(dev)
+        wide_c = torch.zeros(2048, 8192, dtype=torch.bfloat16, device=dev)
+        av, bv, cv = wide_a[:, 4096:], wide_b[:, :4096], wide_c[:, 2048:6144]
+        matmul_op.matmul(av, bv, c=cv)
+        rows = slice(512, 640)
+        err = rel(cv[rows], oracle.host_matmul(av[rows], bv))
+        untouched = bool((wide_c[:, :2048] == 0).all().item() and (wide_c[:, 6144:] == 0).all().item())
+        entry("strided bf16 2048x4096x4096 (column blocks of 8192-wide tensors)", 2.0 * 2048 * 4096 * 4096,
+              lambda: matmul_op.matmul(av, bv, c=cv), lambda: torch.matmul(av, bv, out=cv), "torch.matmul on the views",
+              err if untouched else float("inf"), "host torch.matmul fp32 of rows 512..639; C outside the block stays zero")
+        del wide_a, wide_b, wide_c
+    except Exception as e:
+        out.append({"workload": "strided bf16 2048x4096x4096", "error": str(e)[:300]})
+    try:  # attention-shaped chain: 16 heads x 2048 x 128
+        H, S, D = 16, 2048, 128
+        q, k, v = ((torch.randn(H, S, D, generator=g)).bfloat16().to(dev) for _ in range(3))
+        o = matmul_op.attention(q, k, v)
+        ref = torch.softmax(oracle.host_matmul(q[3], k[3].t().contiguous()) / math.sqrt(D), dim=-1) @ v[3].float().cpu()
+        err = rel(o[3], ref)
+        entry(f"attention chain bf16 {H} heads x {S} x {D}", 4.0 * H * S * S * D, lambda: matmul_op.attention(q, k, v, out=o),
+              lambda: torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None]),
+              "torch scaled_dot_product_attention (fused library kernel, scores never materialised)", err,
+              "host softmax(q k^T / sqrt(d)) v at fp32, head 3")
+        del q, k, v, o
+    except Exception as e:
+        out.append({"workload": "attention chain bf16 16 heads x 2048 x 128", "error": str(e)[:300]})
+    torch.cuda.empty_cache()
+    return out, dict(sampler.window(t_g0, time.time(), "operators around the product"), group="operators around the product")
+
+
 # ------------------------------------------------------------------------------------ CPU legs
 class CpuGemm:
     """The reference's CPU path for this workload: ``torch.matmul`` on host tensors, bf16 operands up-cast to
@@ -432,6 +504,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-extras", action="store_true", help="skip other_workloads and cpu_baseline")
+    ap.add_argument("--extras-only-operators", action="store_true",
+                    help="of other_workloads run only the operators around the product (batched, strided, attention)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
@@ -672,7 +746,10 @@ def main():
     extras, group_clocks, cpu_base = None, None, None
     if rank == 0 and n_gpus == 1 and not args.no_extras:
         del hA, hB, hC
-        extras, group_clocks = other_workloads(local_rank, peaks, sampler)
+        extras, group_clocks = ([], []) if args.extras_only_operators else other_workloads(local_rank, peaks, sampler)
+        chain, chain_clocks = chain_workloads(local_rank, sampler)
+        extras += chain
+        group_clocks.append(chain_clocks)
         threads = os.cpu_count() or 1
         cpu = CpuGemm(A_full, B_host, threads, budget_s=20.0, passes=4)
         secs = [cpu.timed_pass() for _ in range(4)]

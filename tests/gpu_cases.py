@@ -167,6 +167,8 @@ BATCHED = [
     ("bf16_batch5_atrans", 5, 128, 256, 384, E.bfloat16, "normal", dict(isATranspose=1)),
     ("bf16_batch4_splitk", 4, 128, 256, 2048, E.bfloat16, "normal", dict(LOCAL_SPLIT_U=2)),
     ("fp16_batch2", 2, 256, 256, 256, E.float16, "normal", dict(BLOCK_SIZE_N=128)),
+    ("bf16_batch3_clusterk", 3, 128, 256, 2048, E.bfloat16, "normal",   # what bmm picks for a few skinny batches
+     dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=4)),
     ("fp32_batch4_3xtf32", 4, 256, 256, 512, E.float32, "uniform", dict(BLOCK_SIZE_N=128)),
     ("fp32_batch3_3xtf32_atrans_pair", 3, 256, 512, 256, E.float32, "uniform",
      dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, NUM_STAGES=3, isATranspose=1)),
