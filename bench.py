@@ -418,9 +418,28 @@ def chain_workloads(device: int, sampler: "ClockSampler", launches: int = 20):
               lambda: torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None]),
               "torch scaled_dot_product_attention (fused library kernel, scores never materialised)", err,
               "host softmax(q k^T / sqrt(d)) v at fp32, head 3")
-        del q, k, v, o
+        o2 = matmul_op.attention_fused(q, k, v)
+        matmul_op.attention_status(device)
+        entry(f"attention fused kernel bf16 {H} heads x {S} x {D}", 4.0 * H * S * S * D,
+              lambda: matmul_op.attention_fused(q, k, v, out=o2),
+              lambda: torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None]),
+              "torch scaled_dot_product_attention (fused library kernel)", rel(o2[3], ref),
+              "host softmax(q k^T / sqrt(d)) v at fp32, head 3")
+        matmul_op.attention_status(device)
+        del q, k, v, o, o2
+        H, S, D = 32, 8192, 128  # a longer sequence, fused kernel only (the chain would materialise 8 GB of scores)
+        q, k, v = ((torch.randn(H, S, D, generator=g)).bfloat16().to(dev) for _ in range(3))
+        o2 = matmul_op.attention_fused(q, k, v)
+        ref = torch.softmax(oracle.host_matmul(q[7, :256], k[7].t().contiguous()) / math.sqrt(D), dim=-1) @ v[7].float().cpu()
+        entry(f"attention fused kernel bf16 {H} heads x {S} x {D}", 4.0 * H * S * S * D,
+              lambda: matmul_op.attention_fused(q, k, v, out=o2),
+              lambda: torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None]),
+              "torch scaled_dot_product_attention (fused library kernel)", rel(o2[7, :256], ref),
+              "host softmax(q k^T / sqrt(d)) v at fp32, head 7, rows 0..255")
+        matmul_op.attention_status(device)
+        del q, k, v, o2
     except Exception as e:
-        out.append({"workload": "attention chain bf16 16 heads x 2048 x 128", "error": str(e)[:300]})
+        out.append({"workload": "attention bf16", "error": str(e)[:300]})
     torch.cuda.empty_cache()
     return out, dict(sampler.window(t_g0, time.time(), "operators around the product"), group="operators around the product")
 

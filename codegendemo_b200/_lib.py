@@ -23,6 +23,7 @@ EXPORTED_SYMBOLS = (
     "kcg_compile_matmul", "kcg_compile_matmul_ex", "kcg_kernel_name", "kcg_cache_dir",
     "kcg_load_binary", "kcg_unload", "kcg_device_properties", "kcg_launch_gemm",
     "kcg_launch_gemm_ex", "kcg_launch_gemm_batched", "kcg_launch_gemm_strided", "kcg_softmax_rows", "kcg_softmax_rows_ex",
+    "kcg_attention_fwd", "kcg_attention_status",
     "kcg_launch_gemm_allgather", "kcg_peer_alloc", "kcg_peer_open", "kcg_peer_close",
     "kcg_peer_free", "kcg_check_status", "kcg_matmul_host", "kcg_launch_count", "kcg_shutdown",
     "kcg_last_error", "kcg_version", "kcg_gemm_bf16_splitk_noalloc",
@@ -148,6 +149,11 @@ def get_lib() -> ctypes.CDLL:
     lib.kcg_softmax_rows_ex.argtypes = [ctypes.c_int, u64, u64, ctypes.c_int, ctypes.c_int64, u64, ctypes.c_int,
                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_float]
     lib.kcg_softmax_rows_ex.restype = ctypes.c_int
+    lib.kcg_attention_fwd.argtypes = [ctypes.c_int, u64, u64, u64, u64, u64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_int, ctypes.c_int, ctypes.c_float]
+    lib.kcg_attention_fwd.restype = ctypes.c_int
+    lib.kcg_attention_status.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_uint32)]
+    lib.kcg_attention_status.restype = ctypes.c_int
     lib.kcg_peer_alloc.argtypes = [ctypes.c_int, u64, ctypes.POINTER(u64), ctypes.c_char_p]
     lib.kcg_peer_open.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(u64)]
     lib.kcg_peer_close.argtypes = [ctypes.c_int, u64]

@@ -30,7 +30,7 @@ def build_library(force: bool = False) -> str:
     deps = srcs + [os.path.join(kdir, f) for f in sorted(os.listdir(kdir))] + [
         os.path.join(os.path.dirname(HERE), "include", "kcg_b200.h")]
     # device code linked into the library itself: the allocation-free split-K entry and the row softmax
-    extra = [os.path.join(HERE, "csrc", f) for f in ("kcg_noalloc.cu", "kcg_softmax.cu")]
+    extra = [os.path.join(HERE, "csrc", f) for f in ("kcg_noalloc.cu", "kcg_softmax.cu", "kcg_attention.cu")]
     deps += extra
     if not force and _newer(out, deps):
         return out

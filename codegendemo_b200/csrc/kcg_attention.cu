@@ -1,0 +1,506 @@
+// Fused attention forward, O = softmax(scale * Q K^T) V per head, for fp16 / bf16 with head dimension 64 or 128:
+// the attention-shaped chain (two products around a row softmax, which the reference lists after batched GEMM
+// among its next operators, doc/结果汇总.md) as ONE kernel in which scores and probabilities never leave the SM.
+// The three-launch form (matmul_op.attention: batched Q K^T with fp32 scores, row softmax, batched P V) stays as
+// the path whose parity is pinned to the composition; this kernel is checked against the same composition.
+//
+// One CTA per (head, 128 query rows), 192 threads:
+//   warp 0    TMA producer: the Q tile once, then K and V tiles of 128 keys through two-stage rings
+//   warp 1    tcgen05.mma issuer and TMEM owner: S_j = Q K_j^T (both K-major) into one of two TMEM buffers,
+//             O += P_j V_j (P from shared memory, V as the MN-major operand) into a third
+//   warps 2-5 one query row per thread: read S_j from TMEM, running maximum and sum in the exp2 domain,
+//             P_j (16-bit) into shared memory in the K-major operand layout, O rescaled in TMEM by
+//             exp2(m_old - m_new) once the previous P V has retired; at the end O / sum to global memory
+// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax warps work on
+// the current ones. Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word
+// the host can read (kcg_attention_status), raises the CTA's abort flag and all roles fall through to the exit.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <mutex>
+#include <string>
+
+#include "../../include/kcg_b200.h"
+#include "kernels/ptx_sm100.cuh"
+
+extern "C" int kcg_internal_fail(int code, const char* msg);
+extern "C" void kcg_internal_count_launch(void);
+
+namespace {
+
+using namespace kcg;
+
+__device__ unsigned int g_attn_status[4];  // {code, block, detail, detail}; 0 = no wait ran out
+
+// 3-D tiled load: {column, row, head}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tm, uint64_t* bar, int32_t c0,
+                                            int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+// registers -> TMEM: each thread of the warp writes 32 consecutive fp32 columns of its own lane (row)
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+        "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+        "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+struct AttnParams {
+  CUtensorMap tmQ, tmK, tmV;  // {d, rows, heads}, boxes of {64, 128, 1}, 128-byte swizzle
+  void* O;                    // heads x sq x d, contiguous
+  int sq, sk;
+  float scale_log2;           // scale * log2(e): the softmax runs on exp2
+};
+
+enum : uint32_t { ATTN_TIMEOUT_PRODUCER = 1, ATTN_TIMEOUT_MMA = 2, ATTN_TIMEOUT_SOFTMAX = 3 };
+
+template <int kD, bool kBf16>
+struct AttnFwd {
+  static constexpr int BR = 128;  // query rows per CTA (= TMEM lanes)
+  static constexpr int BC = 128;  // keys per step
+  static constexpr int STAGES = 2;
+  static constexpr int NUM_THREADS = 192;
+  static constexpr int BOXES = kD / 64;          // 64 values = 128 bytes per box row
+  static constexpr int BOX_BYTES = 128 * 128;    // 128 rows x 128 bytes
+  static constexpr int Q_BYTES = BR * kD * 2, KV_BYTES = BC * kD * 2, P_BYTES = BR * BC * 2;
+  static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + STAGES * KV_BYTES, OFF_P = OFF_V + STAGES * KV_BYTES;
+  static constexpr int RING_BYTES = OFF_P + P_BYTES;
+  static constexpr int SMEM_BYTES = RING_BYTES + 2048;  // 1 KB alignment slack + barriers
+  static constexpr uint32_t TMEM_COLS = 512;            // S0 [0,128), S1 [128,256), O [256, 256 + kD)
+  static constexpr uint32_t COL_O = 256;
+  static constexpr uint32_t FMT = kBf16 ? FMT_BF16 : FMT_F16;
+  // S = Q K^T: both operands K-major (rows x d); O += P V: P K-major (rows x keys), V MN-major (keys x d)
+  static constexpr uint32_t IDESC_S = make_instr_desc(FMT, 0u, 0u, 128u, BC);
+  static constexpr uint32_t IDESC_O = make_instr_desc(FMT, 0u, 1u, 128u, kD);
+  using T = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
+
+  struct Barriers {
+    uint64_t q_full;
+    uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint64_t s_full[2], s_empty[2];
+    uint64_t p_full;    // P_j is in shared memory and O is rescaled (4 warps arrive)
+    uint64_t pv_done;   // P_j V_j has retired: P may be overwritten, O may be read
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+  };
+
+  __device__ static __forceinline__ void report(Barriers* bars, uint32_t code, uint32_t d0, uint32_t d1) {
+    bars->abort_flag = 1u;
+    if (atomicCAS(&g_attn_status[0], 0u, code) == 0u) {
+      g_attn_status[1] = blockIdx.x;
+      g_attn_status[2] = d0;
+      g_attn_status[3] = d1;
+    }
+  }
+
+  __device__ static void run(const AttnParams& p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + RING_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_tiles = (p.sq + BR - 1) / BR;
+    const int head = static_cast<int>(blockIdx.x) / q_tiles;
+    const int q0 = (static_cast<int>(blockIdx.x) % q_tiles) * BR;
+    const int nkv = (p.sk + BC - 1) / BC;
+
+    if (threadIdx.x == 0) {
+      tma_prefetch_desc(&p.tmQ);
+      tma_prefetch_desc(&p.tmK);
+      tma_prefetch_desc(&p.tmV);
+      mbar_init(&bars->q_full, 1);
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&bars->k_full[s], 1);
+        mbar_init(&bars->k_empty[s], 1);
+        mbar_init(&bars->v_full[s], 1);
+        mbar_init(&bars->v_empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(&bars->s_full[b], 1);
+        mbar_init(&bars->s_empty[b], 4);  // one arrival per softmax warp
+      }
+      mbar_init(&bars->p_full, 4);
+      mbar_init(&bars->pv_done, 1);
+      bars->abort_flag = 0u;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------------ producer
+      if (lane == 0) {
+        mbar_expect_tx(&bars->q_full, Q_BYTES);
+#pragma unroll
+        for (int b = 0; b < BOXES; ++b) tma_load_3d(smem + b * BOX_BYTES, &p.tmQ, &bars->q_full, b * 64, q0, head);
+        for (int j = 0; j < nkv; ++j) {
+          const int s = j % STAGES;
+          const uint32_t ph = (j / STAGES) & 1u;
+          if (!mbar_wait(&bars->k_empty[s], ph ^ 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_PRODUCER, j, 0u);
+            break;
+          }
+          mbar_expect_tx(&bars->k_full[s], KV_BYTES);
+#pragma unroll
+          for (int b = 0; b < BOXES; ++b)
+            tma_load_3d(smem + OFF_K + s * KV_BYTES + b * BOX_BYTES, &p.tmK, &bars->k_full[s], b * 64, j * BC, head);
+          if (!mbar_wait(&bars->v_empty[s], ph ^ 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_PRODUCER, j, 1u);
+            break;
+          }
+          mbar_expect_tx(&bars->v_full[s], KV_BYTES);
+#pragma unroll
+          for (int b = 0; b < BOXES; ++b)
+            tma_load_3d(smem + OFF_V + s * KV_BYTES + b * BOX_BYTES, &p.tmV, &bars->v_full[s], b * 64, j * BC, head);
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        bool ok = mbar_wait(&bars->q_full, 0u, &bars->abort_flag);
+        if (!ok) report(bars, ATTN_TIMEOUT_MMA, 0u, 0u);
+        tc_fence_after_sync();
+        const uint32_t sq_addr = smem_u32(smem);
+        // S_i = Q K_i^T into S buffer i % 2
+        auto issue_s = [&](int i) -> bool {
+          const int s = i % STAGES, b = i & 1;
+          if (!mbar_wait(&bars->k_full[s], (i / STAGES) & 1u, &bars->abort_flag) ||
+              !mbar_wait(&bars->s_empty[b], ((i >> 1) & 1u) ^ 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_MMA, 1u, static_cast<uint32_t>(i));
+            return false;
+          }
+          tc_fence_after_sync();
+          const uint32_t sk_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint32_t off = ((ks * 32) / 128) * BOX_BYTES + ((ks * 32) % 128);
+            const uint64_t adesc = make_smem_desc(sq_addr + off, 16, 1024, SWZ_128B);
+            const uint64_t bdesc = make_smem_desc(sk_addr + off, 16, 1024, SWZ_128B);
+            umma_ss<false>(tmem_base + b * BC, adesc, bdesc, IDESC_S, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(&bars->k_empty[s]);
+          umma_commit(&bars->s_full[b]);
+          return true;
+        };
+        if (ok) ok = issue_s(0);
+        for (int j = 0; j < nkv && ok; ++j) {
+          if (j + 1 < nkv) ok = issue_s(j + 1);
+          if (!ok) break;
+          const int s = j % STAGES;
+          if (!mbar_wait(&bars->p_full, j & 1u, &bars->abort_flag) ||
+              !mbar_wait(&bars->v_full[s], (j / STAGES) & 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_MMA, 2u, static_cast<uint32_t>(j));
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sp_addr = smem_u32(smem + OFF_P);
+          const uint32_t sv_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < BC / 16; ++ks) {
+            // P: K-major, 128 rows x 128 keys = two boxes of 64 keys; V: keys x d, 64-value column chunks kD/64
+            // boxes of 128 key rows each (leading-dimension offset = one box), a K step = 16 key rows
+            const uint32_t a_off = ((ks * 32) / 128) * BOX_BYTES + ((ks * 32) % 128);
+            const uint64_t adesc = make_smem_desc(sp_addr + a_off, 16, 1024, SWZ_128B);
+            const uint64_t bdesc = make_smem_desc(sv_addr + ks * 16 * 128, BOX_BYTES, 1024, SWZ_128B);
+            umma_ss<false>(tmem_base + COL_O, adesc, bdesc, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(&bars->v_empty[s]);
+          umma_commit(&bars->pv_done);
+        }
+      }
+    } else {
+      // ------------------------------------------------- softmax, correction, epilogue
+      const int q = warp & 3;                // TMEM lane quarter this warp may access
+      const int row = q * 32 + lane;         // query row of this thread inside the tile
+      const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+      float m = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < nkv; ++j) {
+        const int b = j & 1;
+        bool got = mbar_wait(&bars->s_full[b], (j >> 1) & 1u, &bars->abort_flag);
+        if (!named_bar_all(2, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 0u, static_cast<uint32_t>(j));
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        float s[BC];
+#pragma unroll
+        for (int c = 0; c < BC / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BC + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->s_empty[b]);  // the MMA warp may overwrite this S buffer
+        const int valid = p.sk - j * BC;                // keys of this step that exist
+        float mx = m;
+#pragma unroll
+        for (int i = 0; i < BC; ++i) {
+          if (i >= valid) s[i] = -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
+        const float alpha = exp2f(m - mx);  // 0 on the first step (m = -inf)
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < BC; ++i) {
+          s[i] = exp2f(s[i] - mx);
+          sum += s[i];
+        }
+        l = l * alpha + sum;
+        m = mx;
+        // P_{j-1} V_{j-1} must have retired before P is overwritten and O is touched
+        got = mbar_wait(&bars->pv_done, (j & 1u) ^ 1u, &bars->abort_flag);
+        if (!named_bar_all(2, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 1u, static_cast<uint32_t>(j));
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        // this row of P: 256 bytes = two boxes x eight 16-byte units, XOR-swizzled by the row
+        uint8_t* prow = smem + OFF_P + row * 128;
+#pragma unroll
+        for (int u = 0; u < BC / 8; ++u) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if constexpr (kBf16) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
+              w[e] = *reinterpret_cast<uint32_t*>(&v2);
+            } else {
+              __half2 v2 = __floats2half2_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
+              w[e] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+          }
+          *reinterpret_cast<uint4*>(prow + (u / 8) * BOX_BYTES + (((u % 8) ^ (row & 7)) << 4)) =
+              make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        fence_proxy_async_smem();  // P visible to the tensor core's operand reads
+        if (j > 0) {
+          // O <- alpha * O for this row
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full);
+      }
+      if (ok) {
+        bool got = mbar_wait(&bars->pv_done, (nkv - 1) & 1u, &bars->abort_flag);
+        if (!named_bar_all(2, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 2u, 0u);
+          ok = false;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = 1.f / l;
+        const int grow = q0 + row;
+        T* out = reinterpret_cast<T*>(p.O) + (static_cast<size_t>(head) * p.sq + grow) * kD;
+#pragma unroll
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+          tmem_ld_wait();
+          if (grow < p.sq) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a = __uint_as_float(r[u * 8 + 2 * e]) * inv, bb = __uint_as_float(r[u * 8 + 2 * e + 1]) * inv;
+                if constexpr (kBf16) {
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(a, bb);
+                  w[e] = *reinterpret_cast<uint32_t*>(&v2);
+                } else {
+                  __half2 v2 = __floats2half2_rn(a, bb);
+                  w[e] = *reinterpret_cast<uint32_t*>(&v2);
+                }
+              }
+              *reinterpret_cast<uint4*>(out + c * 32 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    if (bars->abort_flag != 0u) {
+      // give loads / MMAs still in flight time to land before shared memory and TMEM are released
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+  }
+};
+
+template <int kD, bool kBf16>
+__global__ void __launch_bounds__(192, 1) kcg_attention_kernel(const __grid_constant__ AttnParams p) {
+  AttnFwd<kD, kBf16>::run(p);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn g_encode = nullptr;
+bool g_ready[16][4];  // [device][kernel instance]: dynamic shared memory opted in
+std::mutex g_mutex;
+
+int fail(int code, const std::string& msg) { return kcg_internal_fail(code, msg.c_str()); }
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(static_cast<int>(e), std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t enter(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return e;
+    if (prev == device) return cudaSuccess;
+    e = cudaSetDevice(device);
+    switched = (e == cudaSuccess);
+    return e;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+// {d, rows, heads} view of a contiguous heads x rows x d tensor; boxes of 64 values x 128 rows of one head.
+// Rows past the end of a head read as zero.
+int encode3(CUtensorMap* tm, bool bf16, uint64_t ptr, int d, int rows, int heads) {
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads)};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(d) * 2 * static_cast<cuuint64_t>(rows)};
+  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = g_encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                              reinterpret_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(static_cast<int>(r), "cuTensorMapEncodeTiled failed");
+  return 0;
+}
+
+template <int kD, bool kBf16>
+int launch(int device, int slot, cudaStream_t st, const AttnParams& p, int grid) {
+  using K = AttnFwd<kD, kBf16>;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_ready[device][slot]) {
+      const cudaError_t e = cudaFuncSetAttribute(kcg_attention_kernel<kD, kBf16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, K::SMEM_BYTES);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+      g_ready[device][slot] = true;
+    }
+  }
+  kcg_attention_kernel<kD, kBf16><<<grid, K::NUM_THREADS, K::SMEM_BYTES, st>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attention launch");
+  kcg_internal_count_launch();
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64_t K, uint64_t V, uint64_t O, int dtype,
+                                 int heads, int sq, int sk, int d, float scale) {
+  if (!Q || !K || !V || !O) return fail(KCG_E_BAD_ARG, "null device pointer");
+  if (heads <= 0 || sq <= 0 || sk <= 0) return fail(KCG_E_BAD_ARG, "empty shape");
+  if (!(dtype == KCG_DTYPE_BFLOAT16 || dtype == KCG_DTYPE_FLOAT16))
+    return fail(KCG_E_BAD_ARG, "the fused attention kernel takes float16 or bfloat16 data");
+  if (!(d == 64 || d == 128)) return fail(KCG_E_BAD_CONFIG, "head dimension must be 64 or 128");
+  if (device < 0 || device >= 16) return fail(KCG_E_BAD_ARG, "device index out of range");
+  if (Q % 16 || K % 16 || V % 16 || O % 16) return fail(KCG_E_BAD_ARG, "operands must start on 16-byte boundaries");
+  const long long tiles = static_cast<long long>(heads) * ((sq + 127) / 128);
+  if (tiles > 0x7fffffffLL) return fail(KCG_E_TOO_LARGE, "too many query tiles for one launch");
+  DeviceGuard guard;
+  cudaError_t e = guard.enter(device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+      if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn)
+        return fail(KCG_E_NO_DRIVER, "cuTensorMapEncodeTiled not available from the driver");
+      g_encode = reinterpret_cast<EncodeFn>(fn);
+    }
+  }
+  const bool bf16 = dtype == KCG_DTYPE_BFLOAT16;
+  AttnParams p{};
+  if (int r = encode3(&p.tmQ, bf16, Q, d, sq, heads)) return r;
+  if (int r = encode3(&p.tmK, bf16, K, d, sk, heads)) return r;
+  if (int r = encode3(&p.tmV, bf16, V, d, sk, heads)) return r;
+  p.O = reinterpret_cast<void*>(O);
+  p.sq = sq;
+  p.sk = sk;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(tiles);
+  if (d == 128) return bf16 ? launch<128, true>(device, 0, st, p, grid) : launch<128, false>(device, 1, st, p, grid);
+  return bf16 ? launch<64, true>(device, 2, st, p, grid) : launch<64, false>(device, 3, st, p, grid);
+}
+
+// Reads (and clears) the status word of the fused attention kernels on `device`: out = {code, block, detail,
+// detail}; code 0 = no bounded wait has run out since the last call. Synchronises the device.
+extern "C" int kcg_attention_status(int device, uint32_t out[4]) {
+  if (!out) return fail(KCG_E_BAD_ARG, "null argument");
+  DeviceGuard guard;
+  cudaError_t e = guard.enter(device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceSynchronize");
+  e = cudaMemcpyFromSymbol(out, g_attn_status, sizeof(uint32_t) * 4);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyFromSymbol");
+  if (out[0] != 0u) {
+    const uint32_t zero[4] = {0u, 0u, 0u, 0u};
+    e = cudaMemcpyToSymbol(g_attn_status, zero, sizeof(zero));
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpyToSymbol");
+    return fail(KCG_E_DEVICE_TIMEOUT, "a bounded wait of the attention kernel ran out");
+  }
+  return 0;
+}

@@ -231,6 +231,42 @@ def attention(q, k, v, scale=None, out=None):
     return out
 
 
+def attention_fused(q, k, v, scale=None, out=None):
+    """``softmax(scale * q @ k^T) @ v`` per head as ONE kernel (``kcg_attention_fwd``): scores and probabilities
+    stay in tensor memory and shared memory. ``q`` is (heads, Sq, d), ``k`` and ``v`` are (heads, Sk, d), all
+    contiguous fp16 / bf16 with d = 64 or 128; any Sq and Sk. Returns (heads, Sq, d). ``attention`` above is the
+    three-launch form of the same chain."""
+    import ctypes
+    import math
+    import torch
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.Utils import DeviceInfo
+    H, Sq, D = q.shape
+    H2, Sk, D2 = k.shape
+    assert H == H2 and D == D2 and tuple(v.shape) == (H, Sk, D)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous()
+    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    if out is None:
+        out = torch.empty((H, Sq, D), dtype=q.dtype, device=q.device)
+    assert out.is_contiguous() and tuple(out.shape) == (H, Sq, D) and out.dtype == q.dtype
+    dev = q.device.index or 0
+    u64 = ctypes.c_uint64
+    _lib.check(_lib.get_lib().kcg_attention_fwd(dev, u64(DeviceInfo.get_cuda_stream(dev)), u64(q.data_ptr()),
+                                                u64(k.data_ptr()), u64(v.data_ptr()), u64(out.data_ptr()),
+                                                int(FromTorchType(q.dtype)), H, Sq, Sk, D, float(scale)))
+    return out
+
+
+def attention_status(device: int = 0) -> None:
+    """Synchronises the device and raises if a bounded wait of the fused attention kernel ran out."""
+    import ctypes
+    from codegendemo_b200 import _lib
+    out = (ctypes.c_uint32 * 4)()
+    _lib.check(_lib.get_lib().kcg_attention_status(int(device), out))
+
+
 def bmm(a, b, c=None, alpha=1.0, beta=0.0, bias=None, relu=False, **keys):
     """``c[i] = a[i] @ b[i]`` (``torch.bmm`` layout: a is batch x M x K, b is batch x K x N, both
     contiguous) as ONE launch of the kernel compiled for a single batch's M, N, K: the persistent grid

@@ -196,6 +196,18 @@ int kcg_softmax_rows(int device, uint64_t stream, uint64_t X, int64_t rows, int 
 int kcg_softmax_rows_ex(int device, uint64_t stream, uint64_t X, int dtype_in, int64_t ldx, uint64_t Y,
                         int dtype_out, int64_t ldy, int64_t rows, int cols, float scale);
 
+/* ---- the same chain as ONE kernel ------------------------------------------------------
+ * O[h] = softmax(scale * Q[h] K[h]^T) V[h] for h in [0, heads): Q and O are heads x sq x d, K and V
+ * heads x sk x d, all contiguous, float16 or bfloat16 (`dtype`), d = 64 or 128. Scores and
+ * probabilities stay in tensor memory and shared memory (tcgen05.mma for both products, running
+ * maximum and sum per query row); nothing of size sq x sk is written. Asynchronous on `stream`. No
+ * counterpart in the reference (see the note on kcg_softmax_rows). */
+int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64_t K, uint64_t V, uint64_t O, int dtype,
+                      int heads, int sq, int sk, int d, float scale);
+/* Synchronises `device` and reads (and clears) the status word of the kernel above: out = {code, block,
+ * detail, detail}. Returns KCG_E_DEVICE_TIMEOUT when a bounded wait ran out since the last call, else 0. */
+int kcg_attention_status(int device, uint32_t out[4]);
+
 /* ---- M-sharded product with the all-gather of C fused into the kernel ---------------
  * No counterpart in the reference (it has no multi-GPU code). Rank r of G computes rows
  * [r*M/G, (r+1)*M/G) of C with the same cubin as kcg_launch_gemm; `C` is the address of that slab

@@ -455,6 +455,47 @@ def test_attention_chain_matches_host_composition(shape):
         assert not err["nan"] and err["max_rel"] <= oracle.TOL_16BIT, (h, err)
 
 
+@pytest.mark.parametrize("shape", [(4, 256, 256, 64, "bf16"), (16, 2048, 2048, 128, "bf16"), (3, 128, 384, 128, "fp16"),
+                                   (2, 200, 328, 64, "fp16"), (5, 77, 1000, 128, "bf16"), (1, 128, 128, 128, "bf16")],
+                         ids=["4x256x256x64", "16x2048x2048x128", "3x128x384x128-fp16", "ragged-2x200x328x64-fp16",
+                              "ragged-5x77x1000x128", "one-step"])
+def test_fused_attention_kernel_matches_host_composition(shape):
+    """The same chain as one kernel (scores and probabilities stay on the SM): checked against the same host
+    composition, every head, with ragged row and key counts (tiles clipped at the end of a head, keys masked), a
+    scale that is not the default, NaN-poisoned output, and the kernel's status word afterwards."""
+    from codegendemo_b200.kcg.matmul_op import attention_fused, attention_status
+    H, Sq, Sk, D, dt = shape
+    tdt = torch.bfloat16 if dt == "bf16" else torch.float16
+    g = torch.Generator().manual_seed(23)
+    q = torch.randn(H, Sq, D, generator=g).to(tdt)
+    k = torch.randn(H, Sk, D, generator=g).to(tdt)
+    v = torch.randn(H, Sk, D, generator=g).to(tdt)
+    scale = 0.11
+    out = torch.full((H, Sq, D), float("nan"), dtype=tdt, device="cuda:0")
+    attention_fused(q.cuda(), k.cuda(), v.cuda(), scale=scale, out=out)
+    attention_status(0)
+    heads = range(H) if H <= 5 else (0, H // 2, H - 1)
+    for h in heads:
+        s = torch.matmul(q[h].float(), k[h].float().t()) * scale
+        ref = torch.matmul(torch.softmax(s, dim=-1), v[h].float())
+        err = oracle.rel_errors(out[h], ref)
+        assert not err["nan"] and err["max_rel"] <= oracle.TOL_16BIT, (h, err)
+    # twice the same launch gives the same bits
+    again = torch.empty_like(out)
+    attention_fused(q.cuda(), k.cuda(), v.cuda(), scale=scale, out=again)
+    attention_status(0)
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16))
+
+
+def test_fused_attention_argument_checks():
+    lib = _lib.get_lib()
+    x = torch.zeros(2, 128, 128, dtype=torch.bfloat16, device="cuda:0")
+    p = ctypes.c_uint64(x.data_ptr())
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 62, 2, 128, 128, 96, ctypes.c_float(1.0)) == _lib.E_BAD_CONFIG
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 4, 2, 128, 128, 128, ctypes.c_float(1.0)) == _lib.E_BAD_ARG
+    assert lib.kcg_attention_fwd(0, 0, 0, p, p, p, 62, 2, 128, 128, 128, ctypes.c_float(1.0)) == _lib.E_BAD_ARG
+
+
 def test_row_softmax_entry():
     lib = _lib.get_lib()
     from codegendemo_b200.kcg.Utils import DeviceInfo
