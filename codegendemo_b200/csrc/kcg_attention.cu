@@ -62,6 +62,12 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnParams {
   CUtensorMap tmQ, tmK, tmV;  // {d, rows, heads}, boxes of {64, 128, 1}, 128-byte swizzle
   void* O;                    // heads x sq x d, contiguous
@@ -256,26 +262,38 @@ struct AttnFwd {
           tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BC + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]) * p.scale_log2;
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
         }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->s_empty[b]);  // the MMA warp may overwrite this S buffer
         const int valid = p.sk - j * BC;                // keys of this step that exist
-        float mx = m;
+        if (valid < BC) {
 #pragma unroll
-        for (int i = 0; i < BC; ++i) {
-          if (i >= valid) s[i] = -INFINITY;
-          mx = fmaxf(mx, s[i]);
+          for (int i = 0; i < BC; ++i)
+            if (i >= valid) s[i] = -INFINITY;
         }
-        const float alpha = exp2f(m - mx);  // 0 on the first step (m = -inf)
-        float sum = 0.f;
+        // running maximum of the raw scores (the scale is positive: checked by the host), four chains
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < BC; ++i) {
-          s[i] = exp2f(s[i] - mx);
-          sum += s[i];
+        for (int i = 0; i < BC; i += 4) {
+          mx4[0] = fmaxf(mx4[0], s[i]);
+          mx4[1] = fmaxf(mx4[1], s[i + 1]);
+          mx4[2] = fmaxf(mx4[2], s[i + 2]);
+          mx4[3] = fmaxf(mx4[3], s[i + 3]);
         }
-        l = l * alpha + sum;
+        const float mx = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2);
+        const float alpha = ex2(m - mx);  // 0 on the first step (m = -inf)
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < BC; i += 4) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            s[i + e] = ex2(fmaf(s[i + e], p.scale_log2, -mx));
+            sum4[e] += s[i + e];
+          }
+        }
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m = mx;
         // P_{j-1} V_{j-1} must have retired before P is overwritten and O is touched
         got = mbar_wait(&bars->pv_done, (j & 1u) ^ 1u, &bars->abort_flag);
@@ -304,8 +322,8 @@ struct AttnFwd {
               make_uint4(w[0], w[1], w[2], w[3]);
         }
         fence_proxy_async_smem();  // P visible to the tensor core's operand reads
-        if (j > 0) {
-          // O <- alpha * O for this row
+        // O <- alpha * O for this row; skipped by a warp none of whose rows saw a new maximum (alpha = 1)
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
           for (int c = 0; c < kD / 32; ++c) {
             uint32_t r[32];
@@ -452,6 +470,7 @@ extern "C" int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64
   if (!(dtype == KCG_DTYPE_BFLOAT16 || dtype == KCG_DTYPE_FLOAT16))
     return fail(KCG_E_BAD_ARG, "the fused attention kernel takes float16 or bfloat16 data");
   if (!(d == 64 || d == 128)) return fail(KCG_E_BAD_CONFIG, "head dimension must be 64 or 128");
+  if (!(scale > 0.f) || !std::isfinite(scale)) return fail(KCG_E_BAD_ARG, "scale must be positive and finite");
   if (device < 0 || device >= 16) return fail(KCG_E_BAD_ARG, "device index out of range");
   if (Q % 16 || K % 16 || V % 16 || O % 16) return fail(KCG_E_BAD_ARG, "operands must start on 16-byte boundaries");
   const long long tiles = static_cast<long long>(heads) * ((sq + 127) / 128);
