@@ -4,13 +4,14 @@
 // The three-launch form (matmul_op.attention: batched Q K^T with fp32 scores, row softmax, batched P V) stays as
 // the path whose parity is pinned to the composition; this kernel is checked against the same composition.
 //
-// One CTA per (head, 128 query rows), 192 threads:
+// One CTA per (head, 128 query rows), 320 threads:
 //   warp 0    TMA producer: the Q tile once, then K and V tiles of 128 keys through two-stage rings
 //   warp 1    tcgen05.mma issuer and TMEM owner: S_j = Q K_j^T (both K-major) into one of two TMEM buffers,
 //             O += P_j V_j (P from shared memory, V as the MN-major operand) into a third
-//   warps 2-5 one query row per thread: read S_j from TMEM, running maximum and sum in the exp2 domain,
-//             P_j (16-bit) into shared memory in the K-major operand layout, O rescaled in TMEM by
-//             exp2(m_old - m_new) once the previous P V has retired; at the end O / sum to global memory
+//   warps 2-9 two threads per query row (64 keys of a step each): read S_j from TMEM, running maximum and sum
+//             in the exp2 domain, P_j (16-bit) into shared memory in the K-major operand layout, O rescaled in
+//             TMEM by exp2(m_old - m_new) once the previous P V has retired (only by warps that saw a new
+//             maximum); at the end O / sum to global memory
 // S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax warps work on
 // the current ones. Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word
 // the host can read (kcg_attention_status), raises the CTA's abort flag and all roles fall through to the exit.
@@ -21,6 +22,7 @@
 
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -77,35 +79,45 @@ struct AttnParams {
 
 enum : uint32_t { ATTN_TIMEOUT_PRODUCER = 1, ATTN_TIMEOUT_MMA = 2, ATTN_TIMEOUT_SOFTMAX = 3 };
 
-template <int kD, bool kBf16>
+// kBC = keys per step (64 or 128); kSplit = threads per query row (1 or 2). With 64 keys per step and one
+// thread per row a CTA needs 96 KB of shared memory (d = 128), 256 TMEM columns and 192 threads, so TWO CTAs
+// share an SM and one's products fill the tensor pipe while the other is in its softmax.
+template <int kD, bool kBf16, int kBC, int kSplit>
 struct AttnFwd {
   static constexpr int BR = 128;  // query rows per CTA (= TMEM lanes)
-  static constexpr int BC = 128;  // keys per step
-  static constexpr int STAGES = 2;
-  static constexpr int NUM_THREADS = 192;
-  static constexpr int BOXES = kD / 64;          // 64 values = 128 bytes per box row
-  static constexpr int BOX_BYTES = 128 * 128;    // 128 rows x 128 bytes
+  static constexpr int BC = kBC;  // keys per step
+  static constexpr int K_STAGES = 2;
+  static constexpr int V_STAGES = (kBC == 64) ? 1 : 2;  // V_j is needed a whole softmax later than K_j
+  static constexpr int NUM_SOFTMAX_THREADS = 128 * kSplit;
+  static constexpr int NUM_THREADS = 64 + NUM_SOFTMAX_THREADS;  // producer, MMA issuer, softmax warps
+  static constexpr int BOXES = kD / 64;             // 64 values = 128 bytes per box row
+  static constexpr int QBOX_BYTES = BR * 128;       // Q: boxes of 128 rows x 128 bytes
+  static constexpr int KVBOX_BYTES = BC * 128;      // K, V: boxes of BC rows x 128 bytes
+  static constexpr int PBOX_BYTES = BR * 128;       // P: boxes of 128 rows x 64 keys
   static constexpr int Q_BYTES = BR * kD * 2, KV_BYTES = BC * kD * 2, P_BYTES = BR * BC * 2;
-  static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + STAGES * KV_BYTES, OFF_P = OFF_V + STAGES * KV_BYTES;
+  static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES, OFF_P = OFF_V + V_STAGES * KV_BYTES;
   static constexpr int RING_BYTES = OFF_P + P_BYTES;
-  static constexpr int SMEM_BYTES = RING_BYTES + 2048;  // 1 KB alignment slack + barriers
-  static constexpr uint32_t TMEM_COLS = 512;            // S0 [0,128), S1 [128,256), O [256, 256 + kD)
-  static constexpr uint32_t COL_O = 256;
+  static constexpr int SMEM_BYTES = RING_BYTES + 3072;  // 1 KB alignment slack + 2 KB barriers and exchange slots
+  static constexpr uint32_t COL_O = 2 * BC;             // S0 [0, BC), S1 [BC, 2 BC), O [2 BC, 2 BC + kD)
+  static constexpr uint32_t TMEM_COLS = (2 * BC + kD <= 256) ? 256 : 512;
   static constexpr uint32_t FMT = kBf16 ? FMT_BF16 : FMT_F16;
   // S = Q K^T: both operands K-major (rows x d); O += P V: P K-major (rows x keys), V MN-major (keys x d)
   static constexpr uint32_t IDESC_S = make_instr_desc(FMT, 0u, 0u, 128u, BC);
   static constexpr uint32_t IDESC_O = make_instr_desc(FMT, 0u, 1u, 128u, kD);
+  static_assert((kBC == 64 || kBC == 128) && (kSplit == 1 || kSplit == 2) && (kBC / kSplit) % 32 == 0, "shape");
   using T = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
 
   struct Barriers {
     uint64_t q_full;
-    uint64_t k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
     uint64_t s_full[2], s_empty[2];
-    uint64_t p_full;    // P_j is in shared memory and O is rescaled (4 warps arrive)
+    uint64_t p_full;    // P_j is in shared memory and O is rescaled (every softmax warp arrives)
     uint64_t pv_done;   // P_j V_j has retired: P may be overwritten, O may be read
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
+    float exchange[2][128];  // row maxima (and, at the end, row sums) passed between the two threads of a row
   };
+  static_assert(sizeof(Barriers) <= 2048, "barrier block exceeds its shared-memory slot");
 
   __device__ static __forceinline__ void report(Barriers* bars, uint32_t code, uint32_t d0, uint32_t d1) {
     bars->abort_flag = 1u;
@@ -132,17 +144,19 @@ struct AttnFwd {
       tma_prefetch_desc(&p.tmK);
       tma_prefetch_desc(&p.tmV);
       mbar_init(&bars->q_full, 1);
-      for (int s = 0; s < STAGES; ++s) {
+      for (int s = 0; s < K_STAGES; ++s) {
         mbar_init(&bars->k_full[s], 1);
         mbar_init(&bars->k_empty[s], 1);
+      }
+      for (int s = 0; s < V_STAGES; ++s) {
         mbar_init(&bars->v_full[s], 1);
         mbar_init(&bars->v_empty[s], 1);
       }
       for (int b = 0; b < 2; ++b) {
         mbar_init(&bars->s_full[b], 1);
-        mbar_init(&bars->s_empty[b], 4);  // one arrival per softmax warp
+        mbar_init(&bars->s_empty[b], 4 * kSplit);  // one arrival per softmax warp
       }
-      mbar_init(&bars->p_full, 4);
+      mbar_init(&bars->p_full, 4 * kSplit);
       mbar_init(&bars->pv_done, 1);
       bars->abort_flag = 0u;
       fence_mbar_init();
@@ -162,26 +176,25 @@ struct AttnFwd {
       if (lane == 0) {
         mbar_expect_tx(&bars->q_full, Q_BYTES);
 #pragma unroll
-        for (int b = 0; b < BOXES; ++b) tma_load_3d(smem + b * BOX_BYTES, &p.tmQ, &bars->q_full, b * 64, q0, head);
+        for (int b = 0; b < BOXES; ++b) tma_load_3d(smem + b * QBOX_BYTES, &p.tmQ, &bars->q_full, b * 64, q0, head);
         for (int j = 0; j < nkv; ++j) {
-          const int s = j % STAGES;
-          const uint32_t ph = (j / STAGES) & 1u;
-          if (!mbar_wait(&bars->k_empty[s], ph ^ 1u, &bars->abort_flag)) {
+          const int ks = j % K_STAGES, vs = j % V_STAGES;
+          if (!mbar_wait(&bars->k_empty[ks], ((j / K_STAGES) & 1u) ^ 1u, &bars->abort_flag)) {
             report(bars, ATTN_TIMEOUT_PRODUCER, j, 0u);
             break;
           }
-          mbar_expect_tx(&bars->k_full[s], KV_BYTES);
+          mbar_expect_tx(&bars->k_full[ks], KV_BYTES);
 #pragma unroll
           for (int b = 0; b < BOXES; ++b)
-            tma_load_3d(smem + OFF_K + s * KV_BYTES + b * BOX_BYTES, &p.tmK, &bars->k_full[s], b * 64, j * BC, head);
-          if (!mbar_wait(&bars->v_empty[s], ph ^ 1u, &bars->abort_flag)) {
+            tma_load_3d(smem + OFF_K + ks * KV_BYTES + b * KVBOX_BYTES, &p.tmK, &bars->k_full[ks], b * 64, j * BC, head);
+          if (!mbar_wait(&bars->v_empty[vs], ((j / V_STAGES) & 1u) ^ 1u, &bars->abort_flag)) {
             report(bars, ATTN_TIMEOUT_PRODUCER, j, 1u);
             break;
           }
-          mbar_expect_tx(&bars->v_full[s], KV_BYTES);
+          mbar_expect_tx(&bars->v_full[vs], KV_BYTES);
 #pragma unroll
           for (int b = 0; b < BOXES; ++b)
-            tma_load_3d(smem + OFF_V + s * KV_BYTES + b * BOX_BYTES, &p.tmV, &bars->v_full[s], b * 64, j * BC, head);
+            tma_load_3d(smem + OFF_V + vs * KV_BYTES + b * KVBOX_BYTES, &p.tmV, &bars->v_full[vs], b * 64, j * BC, head);
         }
       }
     } else if (warp == 1) {
@@ -193,8 +206,8 @@ struct AttnFwd {
         const uint32_t sq_addr = smem_u32(smem);
         // S_i = Q K_i^T into S buffer i % 2
         auto issue_s = [&](int i) -> bool {
-          const int s = i % STAGES, b = i & 1;
-          if (!mbar_wait(&bars->k_full[s], (i / STAGES) & 1u, &bars->abort_flag) ||
+          const int s = i % K_STAGES, b = i & 1;
+          if (!mbar_wait(&bars->k_full[s], (i / K_STAGES) & 1u, &bars->abort_flag) ||
               !mbar_wait(&bars->s_empty[b], ((i >> 1) & 1u) ^ 1u, &bars->abort_flag)) {
             report(bars, ATTN_TIMEOUT_MMA, 1u, static_cast<uint32_t>(i));
             return false;
@@ -203,9 +216,10 @@ struct AttnFwd {
           const uint32_t sk_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
 #pragma unroll
           for (int ks = 0; ks < kD / 16; ++ks) {
-            const uint32_t off = ((ks * 32) / 128) * BOX_BYTES + ((ks * 32) % 128);
-            const uint64_t adesc = make_smem_desc(sq_addr + off, 16, 1024, SWZ_128B);
-            const uint64_t bdesc = make_smem_desc(sk_addr + off, 16, 1024, SWZ_128B);
+            // 16 values of d = 32 bytes of a 128-byte box row; the boxes of 64 values follow one another
+            const uint32_t in_row = (ks * 32) % 128, box = (ks * 32) / 128;
+            const uint64_t adesc = make_smem_desc(sq_addr + box * QBOX_BYTES + in_row, 16, 1024, SWZ_128B);
+            const uint64_t bdesc = make_smem_desc(sk_addr + box * KVBOX_BYTES + in_row, 16, 1024, SWZ_128B);
             umma_ss<false>(tmem_base + b * BC, adesc, bdesc, IDESC_S, ks > 0 ? 1u : 0u);
           }
           umma_commit(&bars->k_empty[s]);
@@ -216,9 +230,9 @@ struct AttnFwd {
         for (int j = 0; j < nkv && ok; ++j) {
           if (j + 1 < nkv) ok = issue_s(j + 1);
           if (!ok) break;
-          const int s = j % STAGES;
+          const int s = j % V_STAGES;
           if (!mbar_wait(&bars->p_full, j & 1u, &bars->abort_flag) ||
-              !mbar_wait(&bars->v_full[s], (j / STAGES) & 1u, &bars->abort_flag)) {
+              !mbar_wait(&bars->v_full[s], (j / V_STAGES) & 1u, &bars->abort_flag)) {
             report(bars, ATTN_TIMEOUT_MMA, 2u, static_cast<uint32_t>(j));
             ok = false;
             break;
@@ -228,11 +242,11 @@ struct AttnFwd {
           const uint32_t sv_addr = smem_u32(smem + OFF_V + s * KV_BYTES);
 #pragma unroll
           for (int ks = 0; ks < BC / 16; ++ks) {
-            // P: K-major, 128 rows x 128 keys = two boxes of 64 keys; V: keys x d, 64-value column chunks kD/64
-            // boxes of 128 key rows each (leading-dimension offset = one box), a K step = 16 key rows
-            const uint32_t a_off = ((ks * 32) / 128) * BOX_BYTES + ((ks * 32) % 128);
+            // P: K-major, 128 rows x BC keys in boxes of 64 keys; V: BC keys x d, its 64-value column chunks
+            // are boxes of BC key rows (leading-dimension offset = one box), a K step = 16 key rows
+            const uint32_t a_off = ((ks * 32) / 128) * PBOX_BYTES + ((ks * 32) % 128);
             const uint64_t adesc = make_smem_desc(sp_addr + a_off, 16, 1024, SWZ_128B);
-            const uint64_t bdesc = make_smem_desc(sv_addr + ks * 16 * 128, BOX_BYTES, 1024, SWZ_128B);
+            const uint64_t bdesc = make_smem_desc(sv_addr + ks * 16 * 128, KVBOX_BYTES, 1024, SWZ_128B);
             umma_ss<false>(tmem_base + COL_O, adesc, bdesc, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(&bars->v_empty[s]);
@@ -241,25 +255,31 @@ struct AttnFwd {
       }
     } else {
       // ------------------------------------------------- softmax, correction, epilogue
+      // kSplit threads per query row. With two, warps 2-5 take the first half of a step's keys and of O's
+      // columns, warps 6-9 the second; the two warps that share a TMEM lane quarter meet on a named barrier
+      // of their own to combine their row maxima (the sums stay separate until the end).
       const int q = warp & 3;                // TMEM lane quarter this warp may access
+      const int h = (warp - 2) >> 2;         // which part of the keys / of O's columns (0 when kSplit = 1)
       const int row = q * 32 + lane;         // query row of this thread inside the tile
       const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+      constexpr int HC = BC / kSplit;        // keys per thread and step
+      constexpr int OC = kD / kSplit;        // O columns per thread
       float m = -INFINITY, l = 0.f;
       bool ok = true;
       for (int j = 0; j < nkv; ++j) {
         const int b = j & 1;
         bool got = mbar_wait(&bars->s_full[b], (j >> 1) & 1u, &bars->abort_flag);
-        if (!named_bar_all(2, 128, got)) {
+        if (!named_bar_all(2, NUM_SOFTMAX_THREADS, got)) {
           if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 0u, static_cast<uint32_t>(j));
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        float s[BC];
+        float s[HC];
 #pragma unroll
-        for (int c = 0; c < BC / 32; ++c) {
+        for (int c = 0; c < HC / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BC + c * 32, r);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + b * BC + h * HC + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
@@ -267,26 +287,34 @@ struct AttnFwd {
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->s_empty[b]);  // the MMA warp may overwrite this S buffer
-        const int valid = p.sk - j * BC;                // keys of this step that exist
-        if (valid < BC) {
+        const int valid = p.sk - j * BC - h * HC;       // keys of this thread's half that exist
+        if (valid < HC) {
 #pragma unroll
-          for (int i = 0; i < BC; ++i)
+          for (int i = 0; i < HC; ++i)
             if (i >= valid) s[i] = -INFINITY;
         }
         // running maximum of the raw scores (the scale is positive: checked by the host), four chains
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < BC; i += 4) {
+        for (int i = 0; i < HC; i += 4) {
           mx4[0] = fmaxf(mx4[0], s[i]);
           mx4[1] = fmaxf(mx4[1], s[i + 1]);
           mx4[2] = fmaxf(mx4[2], s[i + 2]);
           mx4[3] = fmaxf(mx4[3], s[i + 3]);
         }
-        const float mx = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2);
+        float rowmax = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if constexpr (kSplit == 2) {
+          bars->exchange[h][row] = rowmax;
+          named_bar_sync(3 + q, 64);  // the two warps of this lane quarter
+          rowmax = fmaxf(rowmax, bars->exchange[h ^ 1][row]);
+          // (the slot is written again a step later, behind the vote of all softmax warps below: the partner
+          // has read it by then)
+        }
+        const float mx = fmaxf(m, rowmax * p.scale_log2);
         const float alpha = ex2(m - mx);  // 0 on the first step (m = -inf)
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < BC; i += 4) {
+        for (int i = 0; i < HC; i += 4) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             s[i + e] = ex2(fmaf(s[i + e], p.scale_log2, -mx));
@@ -297,16 +325,17 @@ struct AttnFwd {
         m = mx;
         // P_{j-1} V_{j-1} must have retired before P is overwritten and O is touched
         got = mbar_wait(&bars->pv_done, (j & 1u) ^ 1u, &bars->abort_flag);
-        if (!named_bar_all(2, 128, got)) {
+        if (!named_bar_all(2, NUM_SOFTMAX_THREADS, got)) {
           if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 1u, static_cast<uint32_t>(j));
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        // this row of P: 256 bytes = two boxes x eight 16-byte units, XOR-swizzled by the row
+        // this thread's keys of its row of P: boxes of 64 keys, 16-byte units XOR-swizzled by the row
         uint8_t* prow = smem + OFF_P + row * 128;
 #pragma unroll
-        for (int u = 0; u < BC / 8; ++u) {
+        for (int u = 0; u < HC / 8; ++u) {
+          const int unit = (h * HC) / 8 + u;  // 16-byte unit inside the row of BC keys
           uint32_t w[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -318,20 +347,20 @@ struct AttnFwd {
               w[e] = *reinterpret_cast<uint32_t*>(&v2);
             }
           }
-          *reinterpret_cast<uint4*>(prow + (u / 8) * BOX_BYTES + (((u % 8) ^ (row & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(prow + (unit / 8) * PBOX_BYTES + (((unit % 8) ^ (row & 7)) << 4)) =
               make_uint4(w[0], w[1], w[2], w[3]);
         }
         fence_proxy_async_smem();  // P visible to the tensor core's operand reads
-        // O <- alpha * O for this row; skipped by a warp none of whose rows saw a new maximum (alpha = 1)
+        // O <- alpha * O for this thread's columns; skipped by a warp none of whose rows saw a new maximum
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < kD / 32; ++c) {
+          for (int c = 0; c < OC / 32; ++c) {
             uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+            tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + h * OC + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+            tmem_st_32x32b_x32(tmem_base + lane_addr + COL_O + h * OC + c * 32, r);
           }
           tmem_st_wait();
         }
@@ -341,20 +370,25 @@ struct AttnFwd {
       }
       if (ok) {
         bool got = mbar_wait(&bars->pv_done, (nkv - 1) & 1u, &bars->abort_flag);
-        if (!named_bar_all(2, 128, got)) {
+        if (!named_bar_all(2, NUM_SOFTMAX_THREADS, got)) {
           if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 2u, 0u);
           ok = false;
         }
       }
       if (ok) {
         tc_fence_after_sync();
+        if constexpr (kSplit == 2) {
+          bars->exchange[h][row] = l;  // the row's sum = the two halves' sums (both relative to the same maximum)
+          named_bar_sync(3 + q, 64);
+          l += bars->exchange[h ^ 1][row];
+        }
         const float inv = 1.f / l;
         const int grow = q0 + row;
-        T* out = reinterpret_cast<T*>(p.O) + (static_cast<size_t>(head) * p.sq + grow) * kD;
+        T* out = reinterpret_cast<T*>(p.O) + (static_cast<size_t>(head) * p.sq + grow) * kD + h * OC;
 #pragma unroll
-        for (int c = 0; c < kD / 32; ++c) {
+        for (int c = 0; c < OC / 32; ++c) {
           uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + c * 32, r);
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + COL_O + h * OC + c * 32, r);
           tmem_ld_wait();
           if (grow < p.sq) {
 #pragma unroll
@@ -394,16 +428,17 @@ struct AttnFwd {
   }
 };
 
-template <int kD, bool kBf16>
-__global__ void __launch_bounds__(192, 1) kcg_attention_kernel(const __grid_constant__ AttnParams p) {
-  AttnFwd<kD, kBf16>::run(p);
+template <int kD, bool kBf16, int kBC, int kSplit>
+__global__ void __launch_bounds__(64 + 128 * kSplit, (kBC == 64 && kSplit == 1) ? 2 : 1)
+kcg_attention_kernel(const __grid_constant__ AttnParams p) {
+  AttnFwd<kD, kBf16, kBC, kSplit>::run(p);
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
-bool g_ready[16][4];  // [device][kernel instance]: dynamic shared memory opted in
+bool g_ready[16][8];  // [device][kernel instance]: dynamic shared memory opted in
 std::mutex g_mutex;
 
 int fail(int code, const std::string& msg) { return kcg_internal_fail(code, msg.c_str()); }
@@ -427,12 +462,12 @@ struct DeviceGuard {
   }
 };
 
-// {d, rows, heads} view of a contiguous heads x rows x d tensor; boxes of 64 values x 128 rows of one head.
-// Rows past the end of a head read as zero.
-int encode3(CUtensorMap* tm, bool bf16, uint64_t ptr, int d, int rows, int heads) {
+// {d, rows, heads} view of a contiguous heads x rows x d tensor; boxes of 64 values x `box_rows` rows of one
+// head. Rows past the end of a head read as zero.
+int encode3(CUtensorMap* tm, bool bf16, uint64_t ptr, int d, int rows, int heads, int box_rows) {
   cuuint64_t gdim[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(heads)};
   cuuint64_t gstride[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(d) * 2 * static_cast<cuuint64_t>(rows)};
-  cuuint32_t box[3] = {64, 128, 1};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = g_encode(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                               reinterpret_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -442,23 +477,48 @@ int encode3(CUtensorMap* tm, bool bf16, uint64_t ptr, int d, int rows, int heads
   return 0;
 }
 
-template <int kD, bool kBf16>
-int launch(int device, int slot, cudaStream_t st, const AttnParams& p, int grid) {
-  using K = AttnFwd<kD, kBf16>;
+struct Problem {
+  uint64_t Q, K, V, O;
+  int heads, sq, sk, d;
+  float scale;
+  bool bf16;
+};
+
+template <int kD, bool kBf16, int kBC, int kSplit>
+int launch(int device, int slot, cudaStream_t st, const Problem& pb) {
+  using Kern = AttnFwd<kD, kBf16, kBC, kSplit>;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!g_ready[device][slot]) {
-      const cudaError_t e = cudaFuncSetAttribute(kcg_attention_kernel<kD, kBf16>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, K::SMEM_BYTES);
+      const cudaError_t e = cudaFuncSetAttribute(kcg_attention_kernel<kD, kBf16, kBC, kSplit>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Kern::SMEM_BYTES);
       if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
       g_ready[device][slot] = true;
     }
   }
-  kcg_attention_kernel<kD, kBf16><<<grid, K::NUM_THREADS, K::SMEM_BYTES, st>>>(p);
+  AttnParams p{};
+  if (int r = encode3(&p.tmQ, kBf16, pb.Q, kD, pb.sq, pb.heads, 128)) return r;
+  if (int r = encode3(&p.tmK, kBf16, pb.K, kD, pb.sk, pb.heads, kBC)) return r;
+  if (int r = encode3(&p.tmV, kBf16, pb.V, kD, pb.sk, pb.heads, kBC)) return r;
+  p.O = reinterpret_cast<void*>(pb.O);
+  p.sq = pb.sq;
+  p.sk = pb.sk;
+  p.scale_log2 = pb.scale * 1.4426950408889634f;
+  const int grid = pb.heads * ((pb.sq + 127) / 128);
+  kcg_attention_kernel<kD, kBf16, kBC, kSplit><<<grid, Kern::NUM_THREADS, Kern::SMEM_BYTES, st>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention launch");
   kcg_internal_count_launch();
   return 0;
+}
+
+template <int kBC, int kSplit>
+int launch_shape(int device, int base_slot, cudaStream_t st, const Problem& pb) {
+  if (pb.d == 128)
+    return pb.bf16 ? launch<128, true, kBC, kSplit>(device, base_slot, st, pb)
+                   : launch<128, false, kBC, kSplit>(device, base_slot + 1, st, pb);
+  return pb.bf16 ? launch<64, true, kBC, kSplit>(device, base_slot + 2, st, pb)
+                 : launch<64, false, kBC, kSplit>(device, base_slot + 3, st, pb);
 }
 
 }  // namespace
@@ -489,19 +549,15 @@ extern "C" int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64
       g_encode = reinterpret_cast<EncodeFn>(fn);
     }
   }
-  const bool bf16 = dtype == KCG_DTYPE_BFLOAT16;
-  AttnParams p{};
-  if (int r = encode3(&p.tmQ, bf16, Q, d, sq, heads)) return r;
-  if (int r = encode3(&p.tmK, bf16, K, d, sk, heads)) return r;
-  if (int r = encode3(&p.tmV, bf16, V, d, sk, heads)) return r;
-  p.O = reinterpret_cast<void*>(O);
-  p.sq = sq;
-  p.sk = sk;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  Problem pb{Q, K, V, O, heads, sq, sk, d, scale, dtype == KCG_DTYPE_BFLOAT16};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = static_cast<int>(tiles);
-  if (d == 128) return bf16 ? launch<128, true>(device, 0, st, p, grid) : launch<128, false>(device, 1, st, p, grid);
-  return bf16 ? launch<64, true>(device, 2, st, p, grid) : launch<64, false>(device, 3, st, p, grid);
+  // Two CTAs of 64-key steps per SM by default; KCG_ATTN_WIDE=1 selects one CTA of 128-key steps with two
+  // threads per row (a comparison form).
+  static const bool wide = [] {
+    const char* v = getenv("KCG_ATTN_WIDE");
+    return v && v[0] == '1';
+  }();
+  return wide ? launch_shape<128, 2>(device, 4, st, pb) : launch_shape<64, 1>(device, 0, st, pb);
 }
 
 // Reads (and clears) the status word of the fused attention kernels on `device`: out = {code, block, detail,
