@@ -64,6 +64,21 @@ __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// D[tmem] (+)= A[tmem] * B[smem], 16-bit operands: A is read from tensor memory (lane = row, one 32-bit column =
+// two consecutive K values), B through a shared-memory descriptor. Issued by ONE thread.
+__device__ __forceinline__ void umma_ts_f16(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -82,7 +97,10 @@ enum : uint32_t { ATTN_TIMEOUT_PRODUCER = 1, ATTN_TIMEOUT_MMA = 2, ATTN_TIMEOUT_
 // kBC = keys per step (64 or 128); kSplit = threads per query row (1 or 2). With 64 keys per step and one
 // thread per row a CTA needs 96 KB of shared memory (d = 128), 256 TMEM columns and 192 threads, so TWO CTAs
 // share an SM and one's products fill the tensor pipe while the other is in its softmax.
-template <int kD, bool kBf16, int kBC, int kSplit>
+// kPTmem = 1 keeps P in tensor memory: the softmax threads write it (packed pairs) over the columns of the S buffer
+// they have just read, and P V takes its A operand from there, so P never crosses the shared-memory port (which
+// carries every operand byte of both products and is what bounds this kernel).
+template <int kD, bool kBf16, int kBC, int kSplit, int kPTmem>
 struct AttnFwd {
   static constexpr int BR = 128;  // query rows per CTA (= TMEM lanes)
   static constexpr int BC = kBC;  // keys per step
@@ -93,8 +111,7 @@ struct AttnFwd {
   static constexpr int BOXES = kD / 64;             // 64 values = 128 bytes per box row
   static constexpr int QBOX_BYTES = BR * 128;       // Q: boxes of 128 rows x 128 bytes
   static constexpr int KVBOX_BYTES = BC * 128;      // K, V: boxes of BC rows x 128 bytes
-  static constexpr int PBOX_BYTES = BR * 128;       // P: boxes of 128 rows x 64 keys
-  static constexpr int Q_BYTES = BR * kD * 2, KV_BYTES = BC * kD * 2, P_BYTES = BR * BC * 2;
+  static constexpr int Q_BYTES = BR * kD * 2, KV_BYTES = BC * kD * 2, P_BYTES = kPTmem ? 0 : BR * BC * 2;
   static constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES, OFF_P = OFF_V + V_STAGES * KV_BYTES;
   static constexpr int RING_BYTES = OFF_P + P_BYTES;
   static constexpr int SMEM_BYTES = RING_BYTES + 3072;  // 1 KB alignment slack + 2 KB barriers and exchange slots
@@ -244,10 +261,16 @@ struct AttnFwd {
           for (int ks = 0; ks < BC / 16; ++ks) {
             // P: K-major, 128 rows x BC keys in boxes of 64 keys; V: BC keys x d, its 64-value column chunks
             // are boxes of BC key rows (leading-dimension offset = one box), a K step = 16 key rows
-            const uint32_t a_off = ((ks * 32) / 128) * PBOX_BYTES + ((ks * 32) % 128);
-            const uint64_t adesc = make_smem_desc(sp_addr + a_off, 16, 1024, SWZ_128B);
             const uint64_t bdesc = make_smem_desc(sv_addr + ks * 16 * 128, KVBOX_BYTES, 1024, SWZ_128B);
-            umma_ss<false>(tmem_base + COL_O, adesc, bdesc, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+            if constexpr (kPTmem) {
+              // 16 keys = 8 columns of packed pairs in the S buffer of this step
+              umma_ts_f16(tmem_base + COL_O, tmem_base + (j & 1) * BC + ks * 8, bdesc, IDESC_O,
+                          (j > 0 || ks > 0) ? 1u : 0u);
+            } else {
+              const uint32_t a_off = ((ks * 32) / 128) * (BR * 128) + ((ks * 32) % 128);  // boxes of 64 keys
+              const uint64_t adesc = make_smem_desc(sp_addr + a_off, 16, 1024, SWZ_128B);
+              umma_ss<false>(tmem_base + COL_O, adesc, bdesc, IDESC_O, (j > 0 || ks > 0) ? 1u : 0u);
+            }
           }
           umma_commit(&bars->v_empty[s]);
           umma_commit(&bars->pv_done);
@@ -323,36 +346,60 @@ struct AttnFwd {
         }
         l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m = mx;
-        // P_{j-1} V_{j-1} must have retired before P is overwritten and O is touched
-        got = mbar_wait(&bars->pv_done, (j & 1u) ^ 1u, &bars->abort_flag);
+        // Does any row of this warp have a new maximum? Only then is O rescaled (alpha = 1 otherwise).
+        const bool rescale = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+        if constexpr (kPTmem) {
+          // P_j goes over the S columns this thread has read: no other step uses them, so it need not wait
+          // for the previous product. Two keys per 32-bit column.
+          static_assert(HC == 64, "one 32-column store per thread and step");
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if constexpr (kBf16) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(s[2 * i], s[2 * i + 1]);
+              w[i] = *reinterpret_cast<uint32_t*>(&v2);
+            } else {
+              __half2 v2 = __floats2half2_rn(s[2 * i], s[2 * i + 1]);
+              w[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+          }
+          tmem_st_32x32b_x32(tmem_base + lane_addr + b * BC + h * (HC / 2), w);
+        }
+        // P_{j-1} V_{j-1} must have retired before O is touched - and, when P goes through shared memory, before
+        // its one buffer is overwritten. (S_j is complete, so every product before P_{j-1} V_{j-1} has retired:
+        // the barrier is at most one phase behind and the parity test is unambiguous even after skipped waits.)
+        got = (kPTmem && !rescale) ? true : mbar_wait(&bars->pv_done, (j & 1u) ^ 1u, &bars->abort_flag);
         if (!named_bar_all(2, NUM_SOFTMAX_THREADS, got)) {
           if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 1u, static_cast<uint32_t>(j));
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        // this thread's keys of its row of P: boxes of 64 keys, 16-byte units XOR-swizzled by the row
-        uint8_t* prow = smem + OFF_P + row * 128;
+        if constexpr (!kPTmem) {
+          // this thread's keys of its row of P: boxes of 64 keys, 16-byte units XOR-swizzled by the row
+          constexpr int PBOX_BYTES = BR * 128;
+          uint8_t* prow = smem + OFF_P + row * 128;
 #pragma unroll
-        for (int u = 0; u < HC / 8; ++u) {
-          const int unit = (h * HC) / 8 + u;  // 16-byte unit inside the row of BC keys
-          uint32_t w[4];
+          for (int u = 0; u < HC / 8; ++u) {
+            const int unit = (h * HC) / 8 + u;  // 16-byte unit inside the row of BC keys
+            uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            if constexpr (kBf16) {
-              __nv_bfloat162 v2 = __floats2bfloat162_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
-              w[e] = *reinterpret_cast<uint32_t*>(&v2);
-            } else {
-              __half2 v2 = __floats2half2_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
-              w[e] = *reinterpret_cast<uint32_t*>(&v2);
+            for (int e = 0; e < 4; ++e) {
+              if constexpr (kBf16) {
+                __nv_bfloat162 v2 = __floats2bfloat162_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&v2);
+              } else {
+                __half2 v2 = __floats2half2_rn(s[u * 8 + 2 * e], s[u * 8 + 2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&v2);
+              }
             }
+            *reinterpret_cast<uint4*>(prow + (unit / 8) * PBOX_BYTES + (((unit % 8) ^ (row & 7)) << 4)) =
+                make_uint4(w[0], w[1], w[2], w[3]);
           }
-          *reinterpret_cast<uint4*>(prow + (unit / 8) * PBOX_BYTES + (((unit % 8) ^ (row & 7)) << 4)) =
-              make_uint4(w[0], w[1], w[2], w[3]);
+          fence_proxy_async_smem();  // P visible to the tensor core's operand reads
         }
-        fence_proxy_async_smem();  // P visible to the tensor core's operand reads
-        // O <- alpha * O for this thread's columns; skipped by a warp none of whose rows saw a new maximum
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (rescale) {
+          // O <- alpha * O for this thread's columns
 #pragma unroll
           for (int c = 0; c < OC / 32; ++c) {
             uint32_t r[32];
@@ -362,8 +409,8 @@ struct AttnFwd {
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
             tmem_st_32x32b_x32(tmem_base + lane_addr + COL_O + h * OC + c * 32, r);
           }
-          tmem_st_wait();
         }
+        tmem_st_wait();  // P (when it lives in tensor memory) and the rescaled O are written
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->p_full);
@@ -428,17 +475,17 @@ struct AttnFwd {
   }
 };
 
-template <int kD, bool kBf16, int kBC, int kSplit>
+template <int kD, bool kBf16, int kBC, int kSplit, int kPTmem>
 __global__ void __launch_bounds__(64 + 128 * kSplit, (kBC == 64 && kSplit == 1) ? 2 : 1)
 kcg_attention_kernel(const __grid_constant__ AttnParams p) {
-  AttnFwd<kD, kBf16, kBC, kSplit>::run(p);
+  AttnFwd<kD, kBf16, kBC, kSplit, kPTmem>::run(p);
 }
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
-bool g_ready[16][8];  // [device][kernel instance]: dynamic shared memory opted in
+bool g_ready[16][16];  // [device][kernel instance]: dynamic shared memory opted in
 std::mutex g_mutex;
 
 int fail(int code, const std::string& msg) { return kcg_internal_fail(code, msg.c_str()); }
@@ -484,13 +531,13 @@ struct Problem {
   bool bf16;
 };
 
-template <int kD, bool kBf16, int kBC, int kSplit>
+template <int kD, bool kBf16, int kBC, int kSplit, int kPTmem>
 int launch(int device, int slot, cudaStream_t st, const Problem& pb) {
-  using Kern = AttnFwd<kD, kBf16, kBC, kSplit>;
+  using Kern = AttnFwd<kD, kBf16, kBC, kSplit, kPTmem>;
   {
     std::lock_guard<std::mutex> lock(g_mutex);
     if (!g_ready[device][slot]) {
-      const cudaError_t e = cudaFuncSetAttribute(kcg_attention_kernel<kD, kBf16, kBC, kSplit>,
+      const cudaError_t e = cudaFuncSetAttribute(kcg_attention_kernel<kD, kBf16, kBC, kSplit, kPTmem>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, Kern::SMEM_BYTES);
       if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
       g_ready[device][slot] = true;
@@ -505,20 +552,20 @@ int launch(int device, int slot, cudaStream_t st, const Problem& pb) {
   p.sk = pb.sk;
   p.scale_log2 = pb.scale * 1.4426950408889634f;
   const int grid = pb.heads * ((pb.sq + 127) / 128);
-  kcg_attention_kernel<kD, kBf16, kBC, kSplit><<<grid, Kern::NUM_THREADS, Kern::SMEM_BYTES, st>>>(p);
+  kcg_attention_kernel<kD, kBf16, kBC, kSplit, kPTmem><<<grid, Kern::NUM_THREADS, Kern::SMEM_BYTES, st>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "attention launch");
   kcg_internal_count_launch();
   return 0;
 }
 
-template <int kBC, int kSplit>
+template <int kBC, int kSplit, int kPTmem>
 int launch_shape(int device, int base_slot, cudaStream_t st, const Problem& pb) {
   if (pb.d == 128)
-    return pb.bf16 ? launch<128, true, kBC, kSplit>(device, base_slot, st, pb)
-                   : launch<128, false, kBC, kSplit>(device, base_slot + 1, st, pb);
-  return pb.bf16 ? launch<64, true, kBC, kSplit>(device, base_slot + 2, st, pb)
-                 : launch<64, false, kBC, kSplit>(device, base_slot + 3, st, pb);
+    return pb.bf16 ? launch<128, true, kBC, kSplit, kPTmem>(device, base_slot, st, pb)
+                   : launch<128, false, kBC, kSplit, kPTmem>(device, base_slot + 1, st, pb);
+  return pb.bf16 ? launch<64, true, kBC, kSplit, kPTmem>(device, base_slot + 2, st, pb)
+                 : launch<64, false, kBC, kSplit, kPTmem>(device, base_slot + 3, st, pb);
 }
 
 }  // namespace
@@ -551,13 +598,19 @@ extern "C" int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64
   }
   Problem pb{Q, K, V, O, heads, sq, sk, d, scale, dtype == KCG_DTYPE_BFLOAT16};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // Two CTAs of 64-key steps per SM by default; KCG_ATTN_WIDE=1 selects one CTA of 128-key steps with two
-  // threads per row (a comparison form).
-  static const bool wide = [] {
-    const char* v = getenv("KCG_ATTN_WIDE");
-    return v && v[0] == '1';
+  // Default: 128-key steps, two threads per row, P in tensor memory (the fastest of the four measured).
+  // KCG_ATTN_FORM picks a comparison form: bit 0 = two CTAs of 64-key steps per SM, one thread per row;
+  // bit 1 = P through shared memory instead of tensor memory.
+  static const int form = [] {
+    const char* v = getenv("KCG_ATTN_FORM");
+    return v ? atoi(v) & 3 : 0;
   }();
-  return wide ? launch_shape<128, 2>(device, 4, st, pb) : launch_shape<64, 1>(device, 0, st, pb);
+  switch (form) {
+    case 1: return launch_shape<64, 1, 1>(device, 4, st, pb);
+    case 2: return launch_shape<128, 2, 0>(device, 8, st, pb);
+    case 3: return launch_shape<64, 1, 0>(device, 12, st, pb);
+    default: return launch_shape<128, 2, 1>(device, 0, st, pb);
+  }
 }
 
 // Reads (and clears) the status word of the fused attention kernels on `device`: out = {code, block, detail,
