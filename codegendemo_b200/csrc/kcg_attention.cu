@@ -4,16 +4,18 @@
 // The three-launch form (matmul_op.attention: batched Q K^T with fp32 scores, row softmax, batched P V) stays as
 // the path whose parity is pinned to the composition; this kernel is checked against the same composition.
 //
-// One CTA per (head, 128 query rows), 320 threads:
+// One CTA per (head, 128 query rows); the default form has 320 threads:
 //   warp 0    TMA producer: the Q tile once, then K and V tiles of 128 keys through two-stage rings
 //   warp 1    tcgen05.mma issuer and TMEM owner: S_j = Q K_j^T (both K-major) into one of two TMEM buffers,
-//             O += P_j V_j (P from shared memory, V as the MN-major operand) into a third
+//             O += P_j V_j (P read from tensor memory, V as the MN-major operand) into a third
 //   warps 2-9 two threads per query row (64 keys of a step each): read S_j from TMEM, running maximum and sum
-//             in the exp2 domain, P_j (16-bit) into shared memory in the K-major operand layout, O rescaled in
-//             TMEM by exp2(m_old - m_new) once the previous P V has retired (only by warps that saw a new
-//             maximum); at the end O / sum to global memory
+//             in the exp2 domain, P_j as packed 16-bit pairs over the S columns just read, O rescaled in TMEM
+//             by exp2(m_old - m_new) once the previous P V has retired (only by warps that saw a new maximum);
+//             at the end O / sum to global memory
 // S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax warps work on
-// the current ones. Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word
+// the current ones (issuing S two steps ahead, with a third buffer, measured slower). Three comparison forms are
+// kept behind template parameters: P through shared memory, and 64-key steps with one thread per row and two
+// CTAs per SM. Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word
 // the host can read (kcg_attention_status), raises the CTA's abort flag and all roles fall through to the exit.
 #include <cuda.h>
 #include <cuda_bf16.h>
