@@ -175,11 +175,19 @@ BATCHED = [
 ]
 
 
+# the fused all-gather with the tile the 8-GPU sharded product runs (4096-row slabs): CTA pairs, 128-wide K blocks,
+# two accumulator buffers, push warps beside the epilogue; 2.25 waves of tiles here, so the stream-K tail runs too
+ALLGATHER_EXTRA = [
+    ("bf16_pair_256x256x128_streamk", 2304, 4096, 1024, E.bfloat16, "normal",
+     dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)),
+]
+
+
 def all_configs():
     out = [default_config(4096, 4096, 4096, E.bfloat16, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=3),
            default_config(256, 256, 256, E.bfloat16, KERNEL_VARIANT=101, BLOCK_SIZE_N=64),
            default_config(256, 256, 256, E.bfloat16)]
-    for (_, m, n, k, dt, _, keys) in SEEDED + FUSED:
+    for (_, m, n, k, dt, _, keys) in SEEDED + FUSED + ALLGATHER_EXTRA:
         out.append(default_config(m, n, k, dt, **keys))
     for (_, _, m, n, k, dt, _, keys) in BATCHED:
         out.append(default_config(m, n, k, dt, **keys))
@@ -195,6 +203,7 @@ def all_configs():
     for (_, m, n, k, dt, _) in TUNED_SHAPES:
         out.append(tuned_config(m, n, k, dt))
     # per-rank slabs of the two-GPU fused all-gather test (tests/helpers_allgather_ranks.py)
-    for keys in (dict(), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), dict(LOCAL_SPLIT_U=2)):
+    for keys in (dict(), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), dict(LOCAL_SPLIT_U=2),
+                 dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)):
         out.append(default_config(1024, 1024, 1024, E.bfloat16, **keys))
     return out

@@ -27,7 +27,8 @@ def main():
     A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=9)
     ref = oracle.host_matmul(A, B)
     for keys in (dict(), dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4),
-                 dict(LOCAL_SPLIT_U=2)):
+                 dict(LOCAL_SPLIT_U=2),
+                 dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)):
         r0, r1 = shard_rows(M, world, rank, keys.get("BLOCK_SIZE_M", 128))
         _, kern = build_kernel(default_config(r1 - r0, N, K, E.bfloat16, **keys), local)
         sym = SymmetricC(M, N, 2, rank, world, local)

@@ -179,7 +179,8 @@ def test_matmul_op_fuses_bias_relu_chain():
 
 
 @pytest.mark.parametrize("case", [c for c in gpu_cases.FUSED if c[0] in (
-    "bf16_tma_store", "fp16_tma_store", "bf16_pair", "bf16_splitk_reduce")], ids=lambda c: c[0])
+    "bf16_tma_store", "fp16_tma_store", "bf16_pair", "bf16_splitk_reduce")] + gpu_cases.ALLGATHER_EXTRA,
+    ids=lambda c: c[0])
 def test_fused_allgather_stores_reach_every_target(case):
     """The all-gather epilogue on one GPU: the 'peers' are three more buffers of this GPU, so the
     kernel's extra stores (staged path and K-split reduction) are checked without a second device."""
