@@ -4,19 +4,21 @@
 // The three-launch form (matmul_op.attention: batched Q K^T with fp32 scores, row softmax, batched P V) stays as
 // the path whose parity is pinned to the composition; this kernel is checked against the same composition.
 //
-// One CTA per (head, 128 query rows); the default form has 320 threads:
-//   warp 0    TMA producer: the Q tile once, then K and V tiles of 128 keys through two-stage rings
-//   warp 1    tcgen05.mma issuer and TMEM owner: S_j = Q K_j^T (both K-major) into one of two TMEM buffers,
-//             O += P_j V_j (P read from tensor memory, V as the MN-major operand) into a third
-//   warps 2-9 two threads per query row (64 keys of a step each): read S_j from TMEM, running maximum and sum
-//             in the exp2 domain, P_j as packed 16-bit pairs over the S columns just read, O rescaled in TMEM
-//             by exp2(m_old - m_new) once the previous P V has retired (only by warps that saw a new maximum);
-//             at the end O / sum to global memory
-// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax warps work on
-// the current ones (issuing S two steps ahead, with a third buffer, measured slower). Three comparison forms are
-// kept behind template parameters: P through shared memory, and 64-key steps with one thread per row and two
-// CTAs per SM. Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word
-// the host can read (kcg_attention_status), raises the CTA's abort flag and all roles fall through to the exit.
+// Default form (AttnFwd2): one CTA per (head, 256 query rows) = two query tiles of 128 rows, 320 threads:
+//   warp 0    TMA producer: both Q tiles once, then K and V tiles of 128 keys through two-stage rings, shared by
+//             the two query tiles
+//   warp 1    tcgen05.mma issuer and TMEM owner; per tile t: S_t = Q_t K_j^T (both K-major) into the tile's S
+//             buffer, O_t += P_t V_j with P_t read from tensor memory and V as the MN-major operand
+//   warps 2-5 softmax of tile 0, warps 6-9 of tile 1, one query row per thread: read S_t from TMEM, running
+//             maximum and sum in the exp2 domain, P_t as packed 16-bit pairs over the S columns just read, O_t
+//             rescaled in TMEM by exp2(m_old - m_new) only by warps that saw a new maximum; at the end O / sum to
+//             global memory
+// A tile's chain is serial (scores, softmax, P V, next scores) and the two tiles' chains interleave, so the tensor
+// pipe works for one tile while the other is in its softmax. Four single-tile forms are kept for comparison
+// (AttnFwd: one query tile per CTA with two S buffers, 64- or 128-key steps, one or two threads per row, P through
+// shared or tensor memory; S issued one step ahead - two steps ahead, with a third buffer, measured slower).
+// Every wait is bounded (ptx_sm100.cuh); a wait that runs out records a code in a status word the host can read
+// (kcg_attention_status), raises the CTA's abort flag and all roles fall through to the exit.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -477,6 +479,323 @@ struct AttnFwd {
   }
 };
 
+// Two query tiles per CTA. Tile 0 (rows q0 .. q0 + 127) and tile 1 (the next 128 rows) share the K and V tiles in
+// shared memory and take turns on the tensor pipe: while the softmax warps of one tile work on its scores, the
+// products of the other run. Each tile owns one S buffer (P is written over it) and one O accumulator in tensor
+// memory - S_t [128 t, 128 t + 128), O_t [256 + kD t, ...) - and four softmax warps, one thread per row and 128 keys
+// per thread and step. A tile's chain is serial (S, softmax, P V, next S: the next scores overwrite P, and the
+// tensor pipe runs its instructions in order), the two chains interleave. The MMA warp serves the tiles in a fixed
+// order (serving whichever P is ready first measured no faster).
+template <int kD, bool kBf16>
+struct AttnFwd2 {
+  static constexpr int BR = 128, BC = 128, TILES = 2;
+  static constexpr int K_STAGES = 2, V_STAGES = 2;
+  static constexpr int NUM_THREADS = 64 + TILES * 128;
+  static constexpr int BOXES = kD / 64;
+  static constexpr int QBOX_BYTES = BR * 128, KVBOX_BYTES = BC * 128;
+  static constexpr int Q_BYTES = BR * kD * 2, KV_BYTES = BC * kD * 2;
+  static constexpr int OFF_K = TILES * Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES;
+  static constexpr int RING_BYTES = OFF_V + V_STAGES * KV_BYTES;
+  static constexpr int SMEM_BYTES = RING_BYTES + 2048;  // 1 KB alignment slack + barriers
+  static constexpr uint32_t COL_O = TILES * BC, TMEM_COLS = 512;
+  static constexpr uint32_t FMT = kBf16 ? FMT_BF16 : FMT_F16;
+  static constexpr uint32_t IDESC_S = make_instr_desc(FMT, 0u, 0u, 128u, BC);
+  static constexpr uint32_t IDESC_O = make_instr_desc(FMT, 0u, 1u, 128u, kD);
+  using T = typename std::conditional<kBf16, __nv_bfloat16, __half>::type;
+
+  struct Barriers {
+    uint64_t q_full;
+    uint64_t k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
+    uint64_t s_full[TILES];   // S_t of the current step is complete
+    uint64_t p_full[TILES];   // P_t is in tensor memory and O_t is rescaled (4 warps arrive)
+    uint64_t pv_done[TILES];  // P_t V of the current step has retired
+    uint32_t tmem_base;
+    volatile uint32_t abort_flag;
+  };
+
+  __device__ static __forceinline__ void report(Barriers* bars, uint32_t code, uint32_t d0, uint32_t d1) {
+    bars->abort_flag = 1u;
+    if (atomicCAS(&g_attn_status[0], 0u, code) == 0u) {
+      g_attn_status[1] = blockIdx.x;
+      g_attn_status[2] = d0;
+      g_attn_status[3] = d1;
+    }
+  }
+
+  __device__ static void run(const AttnParams& p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    Barriers* bars = reinterpret_cast<Barriers*>(smem + RING_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q_groups = (p.sq + TILES * BR - 1) / (TILES * BR);
+    const int head = static_cast<int>(blockIdx.x) / q_groups;
+    const int q0 = (static_cast<int>(blockIdx.x) % q_groups) * (TILES * BR);
+    const int nkv = (p.sk + BC - 1) / BC;
+
+    if (threadIdx.x == 0) {
+      tma_prefetch_desc(&p.tmQ);
+      tma_prefetch_desc(&p.tmK);
+      tma_prefetch_desc(&p.tmV);
+      mbar_init(&bars->q_full, 1);
+      for (int s = 0; s < K_STAGES; ++s) {
+        mbar_init(&bars->k_full[s], 1);
+        mbar_init(&bars->k_empty[s], 1);
+      }
+      for (int s = 0; s < V_STAGES; ++s) {
+        mbar_init(&bars->v_full[s], 1);
+        mbar_init(&bars->v_empty[s], 1);
+      }
+      for (int t = 0; t < TILES; ++t) {
+        mbar_init(&bars->s_full[t], 1);
+        mbar_init(&bars->p_full[t], 4);
+        mbar_init(&bars->pv_done[t], 1);
+      }
+      bars->abort_flag = 0u;
+      fence_mbar_init();
+      fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+      tmem_alloc(&bars->tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------------ producer
+      if (lane == 0) {
+        mbar_expect_tx(&bars->q_full, TILES * Q_BYTES);
+#pragma unroll
+        for (int t = 0; t < TILES; ++t)
+#pragma unroll
+          for (int b = 0; b < BOXES; ++b)
+            tma_load_3d(smem + t * Q_BYTES + b * QBOX_BYTES, &p.tmQ, &bars->q_full, b * 64, q0 + t * BR, head);
+        for (int j = 0; j < nkv; ++j) {
+          const int ks = j % K_STAGES, vs = j % V_STAGES;
+          if (!mbar_wait(&bars->k_empty[ks], ((j / K_STAGES) & 1u) ^ 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_PRODUCER, j, 0u);
+            break;
+          }
+          mbar_expect_tx(&bars->k_full[ks], KV_BYTES);
+#pragma unroll
+          for (int b = 0; b < BOXES; ++b)
+            tma_load_3d(smem + OFF_K + ks * KV_BYTES + b * KVBOX_BYTES, &p.tmK, &bars->k_full[ks], b * 64, j * BC, head);
+          if (!mbar_wait(&bars->v_empty[vs], ((j / V_STAGES) & 1u) ^ 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_PRODUCER, j, 1u);
+            break;
+          }
+          mbar_expect_tx(&bars->v_full[vs], KV_BYTES);
+#pragma unroll
+          for (int b = 0; b < BOXES; ++b)
+            tma_load_3d(smem + OFF_V + vs * KV_BYTES + b * KVBOX_BYTES, &p.tmV, &bars->v_full[vs], b * 64, j * BC, head);
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------------------------------------------------------- MMA issuer
+      if (lane == 0) {
+        bool ok = mbar_wait(&bars->q_full, 0u, &bars->abort_flag);
+        if (!ok) report(bars, ATTN_TIMEOUT_MMA, 0u, 0u);
+        tc_fence_after_sync();
+        // S_t of step i. Issued after P_t V of step i - 1 (program order), which is what has read the P that
+        // these scores overwrite; the softmax warps of tile t have read the old scores before they wrote that P.
+        auto issue_s = [&](int t, int i) -> bool {
+          const int s = i % K_STAGES;
+          if (!mbar_wait(&bars->k_full[s], (i / K_STAGES) & 1u, &bars->abort_flag)) {
+            report(bars, ATTN_TIMEOUT_MMA, 1u, static_cast<uint32_t>(i));
+            return false;
+          }
+          tc_fence_after_sync();
+          const uint32_t sq_addr = smem_u32(smem + t * Q_BYTES);
+          const uint32_t sk_addr = smem_u32(smem + OFF_K + s * KV_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < kD / 16; ++ks) {
+            const uint32_t in_row = (ks * 32) % 128, box = (ks * 32) / 128;
+            const uint64_t adesc = make_smem_desc(sq_addr + box * QBOX_BYTES + in_row, 16, 1024, SWZ_128B);
+            const uint64_t bdesc = make_smem_desc(sk_addr + box * KVBOX_BYTES + in_row, 16, 1024, SWZ_128B);
+            umma_ss<false>(tmem_base + t * BC, adesc, bdesc, IDESC_S, ks > 0 ? 1u : 0u);
+          }
+          if (t == TILES - 1) umma_commit(&bars->k_empty[s]);  // both tiles have read this K tile
+          umma_commit(&bars->s_full[t]);
+          return true;
+        };
+        for (int t = 0; t < TILES && ok; ++t) ok = issue_s(t, 0);
+        for (int j = 0; j < nkv && ok; ++j) {
+          const int vs = j % V_STAGES;
+          for (int t = 0; t < TILES && ok; ++t) {
+            if (!mbar_wait(&bars->p_full[t], j & 1u, &bars->abort_flag) ||
+                !mbar_wait(&bars->v_full[vs], (j / V_STAGES) & 1u, &bars->abort_flag)) {
+              report(bars, ATTN_TIMEOUT_MMA, 2u, static_cast<uint32_t>(j));
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            const uint32_t sv_addr = smem_u32(smem + OFF_V + vs * KV_BYTES);
+#pragma unroll
+            for (int ks = 0; ks < BC / 16; ++ks) {
+              const uint64_t bdesc = make_smem_desc(sv_addr + ks * 16 * 128, KVBOX_BYTES, 1024, SWZ_128B);
+              umma_ts_f16(tmem_base + COL_O + t * kD, tmem_base + t * BC + ks * 8, bdesc, IDESC_O,
+                          (j > 0 || ks > 0) ? 1u : 0u);
+            }
+            if (t == TILES - 1) umma_commit(&bars->v_empty[vs]);
+            umma_commit(&bars->pv_done[t]);
+            if (j + 1 < nkv) ok = issue_s(t, j + 1);
+          }
+        }
+      }
+    } else {
+      // ------------------------------------------------- softmax, correction, epilogue
+      const int q = warp & 3;           // TMEM lane quarter this warp may access
+      const int t = (warp - 2) >> 2;    // query tile of this warp
+      const int row = q * 32 + lane;    // query row of this thread inside its tile
+      const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+      const uint32_t col_s = tmem_base + lane_addr + t * BC, col_o = tmem_base + lane_addr + COL_O + t * kD;
+      float m = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int j = 0; j < nkv; ++j) {
+        bool got = mbar_wait(&bars->s_full[t], j & 1u, &bars->abort_flag);
+        if (!named_bar_all(2 + t, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 0u, static_cast<uint32_t>(j));
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        float s[BC];
+#pragma unroll
+        for (int c = 0; c < BC / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(col_s + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+        }
+        const int valid = p.sk - j * BC;
+        if (valid < BC) {
+#pragma unroll
+          for (int i = 0; i < BC; ++i)
+            if (i >= valid) s[i] = -INFINITY;
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < BC; i += 4) {
+          mx4[0] = fmaxf(mx4[0], s[i]);
+          mx4[1] = fmaxf(mx4[1], s[i + 1]);
+          mx4[2] = fmaxf(mx4[2], s[i + 2]);
+          mx4[3] = fmaxf(mx4[3], s[i + 3]);
+        }
+        const float mx = fmaxf(m, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * p.scale_log2);
+        const float alpha = ex2(m - mx);  // 0 on the first step (m = -inf)
+        const bool rescale = j > 0 && __any_sync(0xffffffffu, alpha != 1.f);
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // exponentials and P, 64 keys at a time: packed pairs over the S columns this thread has read
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float e0 = ex2(fmaf(s[half * 64 + 2 * i], p.scale_log2, -mx));
+            const float e1 = ex2(fmaf(s[half * 64 + 2 * i + 1], p.scale_log2, -mx));
+            sum4[i & 3] += e0 + e1;
+            if constexpr (kBf16) {
+              __nv_bfloat162 v2 = __floats2bfloat162_rn(e0, e1);
+              w[i] = *reinterpret_cast<uint32_t*>(&v2);
+            } else {
+              __half2 v2 = __floats2half2_rn(e0, e1);
+              w[i] = *reinterpret_cast<uint32_t*>(&v2);
+            }
+          }
+          tmem_st_32x32b_x32(col_s + half * 32, w);
+        }
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m = mx;
+        if (rescale) {
+          // O_t <- alpha * O_t for this row: the previous P_t V has retired (the scores of this step were issued
+          // behind it), which the barrier confirms
+          got = mbar_wait(&bars->pv_done[t], (j & 1u) ^ 1u, &bars->abort_flag);
+          if (got) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int c = 0; c < kD / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(col_o + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32b_x32(col_o + c * 32, r);
+            }
+          }
+        }
+        tmem_st_wait();
+        if (!named_bar_all(2 + t, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 1u, static_cast<uint32_t>(j));
+          ok = false;
+          break;
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->p_full[t]);
+      }
+      if (ok) {
+        bool got = mbar_wait(&bars->pv_done[t], (nkv - 1) & 1u, &bars->abort_flag);
+        if (!named_bar_all(2 + t, 128, got)) {
+          if (!got) report(bars, ATTN_TIMEOUT_SOFTMAX, 2u, 0u);
+          ok = false;
+        }
+      }
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = 1.f / l;
+        const int grow = q0 + t * BR + row;
+        T* out = reinterpret_cast<T*>(p.O) + (static_cast<size_t>(head) * p.sq + grow) * kD;
+#pragma unroll
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(col_o + c * 32, r);
+          tmem_ld_wait();
+          if (grow < p.sq) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float a = __uint_as_float(r[u * 8 + 2 * e]) * inv, bb = __uint_as_float(r[u * 8 + 2 * e + 1]) * inv;
+                if constexpr (kBf16) {
+                  __nv_bfloat162 v2 = __floats2bfloat162_rn(a, bb);
+                  w[e] = *reinterpret_cast<uint32_t*>(&v2);
+                } else {
+                  __half2 v2 = __floats2half2_rn(a, bb);
+                  w[e] = *reinterpret_cast<uint32_t*>(&v2);
+                }
+              }
+              *reinterpret_cast<uint4*>(out + c * 32 + u * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    if (bars->abort_flag != 0u) {
+      const uint64_t t0 = global_timer_ns();
+      while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after_sync();
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+  }
+};
+
+template <int kD, bool kBf16>
+__global__ void __launch_bounds__(320, 1) kcg_attention2_kernel(const __grid_constant__ AttnParams p) {
+  AttnFwd2<kD, kBf16>::run(p);
+}
+
 template <int kD, bool kBf16, int kBC, int kSplit, int kPTmem>
 __global__ void __launch_bounds__(64 + 128 * kSplit, (kBC == 64 && kSplit == 1) ? 2 : 1)
 kcg_attention_kernel(const __grid_constant__ AttnParams p) {
@@ -487,7 +806,7 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn g_encode = nullptr;
-bool g_ready[16][16];  // [device][kernel instance]: dynamic shared memory opted in
+bool g_ready[16][20];  // [device][kernel instance]: dynamic shared memory opted in
 std::mutex g_mutex;
 
 int fail(int code, const std::string& msg) { return kcg_internal_fail(code, msg.c_str()); }
@@ -561,6 +880,34 @@ int launch(int device, int slot, cudaStream_t st, const Problem& pb) {
   return 0;
 }
 
+template <int kD, bool kBf16>
+int launch2(int device, int slot, cudaStream_t st, const Problem& pb) {
+  using Kern = AttnFwd2<kD, kBf16>;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_ready[device][slot]) {
+      const cudaError_t e = cudaFuncSetAttribute(kcg_attention2_kernel<kD, kBf16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, Kern::SMEM_BYTES);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+      g_ready[device][slot] = true;
+    }
+  }
+  AttnParams p{};
+  if (int r = encode3(&p.tmQ, kBf16, pb.Q, kD, pb.sq, pb.heads, 128)) return r;
+  if (int r = encode3(&p.tmK, kBf16, pb.K, kD, pb.sk, pb.heads, 128)) return r;
+  if (int r = encode3(&p.tmV, kBf16, pb.V, kD, pb.sk, pb.heads, 128)) return r;
+  p.O = reinterpret_cast<void*>(pb.O);
+  p.sq = pb.sq;
+  p.sk = pb.sk;
+  p.scale_log2 = pb.scale * 1.4426950408889634f;
+  const int grid = pb.heads * ((pb.sq + 255) / 256);
+  kcg_attention2_kernel<kD, kBf16><<<grid, Kern::NUM_THREADS, Kern::SMEM_BYTES, st>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "attention launch");
+  kcg_internal_count_launch();
+  return 0;
+}
+
 template <int kBC, int kSplit, int kPTmem>
 int launch_shape(int device, int base_slot, cudaStream_t st, const Problem& pb) {
   if (pb.d == 128)
@@ -600,18 +947,22 @@ extern "C" int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64
   }
   Problem pb{Q, K, V, O, heads, sq, sk, d, scale, dtype == KCG_DTYPE_BFLOAT16};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  // Default: 128-key steps, two threads per row, P in tensor memory (the fastest of the four measured).
-  // KCG_ATTN_FORM picks a comparison form: bit 0 = two CTAs of 64-key steps per SM, one thread per row;
-  // bit 1 = P through shared memory instead of tensor memory.
+  // Default: two query tiles per CTA that alternate on the tensor pipe (AttnFwd2; the fastest form measured).
+  // KCG_ATTN_FORM selects a comparison form with ONE query tile per CTA: 4 = 128-key steps, two threads per row,
+  // P in tensor memory; 5 = 64-key steps, one thread per row, two CTAs per SM; 6 and 7 = the same two with P
+  // through shared memory.
   static const int form = [] {
     const char* v = getenv("KCG_ATTN_FORM");
-    return v ? atoi(v) & 3 : 0;
+    return v ? atoi(v) & 7 : 0;
   }();
   switch (form) {
-    case 1: return launch_shape<64, 1, 1>(device, 4, st, pb);
-    case 2: return launch_shape<128, 2, 0>(device, 8, st, pb);
-    case 3: return launch_shape<64, 1, 0>(device, 12, st, pb);
-    default: return launch_shape<128, 2, 1>(device, 0, st, pb);
+    case 4: return launch_shape<128, 2, 1>(device, 0, st, pb);
+    case 5: return launch_shape<64, 1, 1>(device, 4, st, pb);
+    case 6: return launch_shape<128, 2, 0>(device, 8, st, pb);
+    case 7: return launch_shape<64, 1, 0>(device, 12, st, pb);
+    default:
+      if (pb.d == 128) return pb.bf16 ? launch2<128, true>(device, 16, st, pb) : launch2<128, false>(device, 17, st, pb);
+      return pb.bf16 ? launch2<64, true>(device, 18, st, pb) : launch2<64, false>(device, 19, st, pb);
   }
 }
 
