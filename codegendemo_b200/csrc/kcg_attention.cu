@@ -662,15 +662,16 @@ struct AttnFwd2 {
           break;
         }
         tc_fence_after_sync();
+        // all four 32-column reads of the row in flight, one wait
+        uint32_t sr[BC / 32][32];
+#pragma unroll
+        for (int c = 0; c < BC / 32; ++c) tmem_ld_32x32b_x32(col_s + c * 32, sr[c]);
+        tmem_ld_wait();
         float s[BC];
 #pragma unroll
-        for (int c = 0; c < BC / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(col_s + c * 32, r);
-          tmem_ld_wait();
+        for (int c = 0; c < BC / 32; ++c)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
-        }
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(sr[c][i]);
         const int valid = p.sk - j * BC;
         if (valid < BC) {
 #pragma unroll
@@ -716,14 +717,15 @@ struct AttnFwd2 {
           got = mbar_wait(&bars->pv_done[t], (j & 1u) ^ 1u, &bars->abort_flag);
           if (got) {
             tc_fence_after_sync();
+            uint32_t orr[kD / 32][32];
+#pragma unroll
+            for (int c = 0; c < kD / 32; ++c) tmem_ld_32x32b_x32(col_o + c * 32, orr[c]);
+            tmem_ld_wait();
 #pragma unroll
             for (int c = 0; c < kD / 32; ++c) {
-              uint32_t r[32];
-              tmem_ld_32x32b_x32(col_o + c * 32, r);
-              tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32b_x32(col_o + c * 32, r);
+              for (int i = 0; i < 32; ++i) orr[c][i] = __float_as_uint(__uint_as_float(orr[c][i]) * alpha);
+              tmem_st_32x32b_x32(col_o + c * 32, orr[c]);
             }
           }
         }
