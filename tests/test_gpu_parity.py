@@ -457,9 +457,10 @@ def test_attention_chain_matches_host_composition(shape):
 
 
 @pytest.mark.parametrize("shape", [(4, 256, 256, 64, "bf16"), (16, 2048, 2048, 128, "bf16"), (3, 128, 384, 128, "fp16"),
-                                   (2, 200, 328, 64, "fp16"), (5, 77, 1000, 128, "bf16"), (1, 128, 128, 128, "bf16")],
+                                   (2, 200, 328, 64, "fp16"), (5, 77, 1000, 128, "bf16"), (1, 128, 128, 128, "bf16"),
+                                   (96, 640, 384, 64, "bf16"), (2, 257, 129, 128, "fp16")],
                          ids=["4x256x256x64", "16x2048x2048x128", "3x128x384x128-fp16", "ragged-2x200x328x64-fp16",
-                              "ragged-5x77x1000x128", "one-step"])
+                              "ragged-5x77x1000x128", "one-step", "many-heads-96x640x384x64", "ragged-2x257x129x128-fp16"])
 def test_fused_attention_kernel_matches_host_composition(shape):
     """The same chain as one kernel (scores and probabilities stay on the SM): checked against the same host
     composition, every head, with ragged row and key counts (tiles clipped at the end of a head, keys masked), a
