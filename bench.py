@@ -15,7 +15,8 @@ Outside the timed region every rank checks its result against the CPU oracle (``
 code. At N=1 the line also carries, under ``other_workloads``, the other single-GPU configs - fp32 1024^3 and
 4096^3 (3xTF32 and FFMA SIMT), bf16 8192^3 and the rectangular sweep M in {128, 512, 2048} x N, K in {4096, 11008}
 x {fp32, bf16} (24 points) - each with its roofline and the same shape through cuBLAS (``torch.matmul`` on the device) timed
-the same way.
+the same way, and the operators around the product (batched, strided, the attention-shaped chain as three launches
+and as one fused kernel), each beside its PyTorch library call and checked against the host composition at fp32.
 
 Prints ONE JSON line on rank 0 (metric: GEMM TFLOP/s, device-timed with CUDA events, max over ranks).
 ``--impl reference`` times the reference's CPU path for the same metric: ``torch.matmul`` on host tensors (the
