@@ -632,11 +632,11 @@ def main():
     peak_kind = "bf16_tflops_sustained" if timed_s > 0.1 else "bf16_tflops"
     peak = peaks[peak_kind]
     # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum, one-pass ncu captures, see
-    # profiles/): 4.29 GB for the full 32768-row launch of the 512x256 pair tile; 275.0 MB for a 2048-row launch
+    # profiles/): 5.76 GB for the full 32768-row launch of the 512x256 pair tile; 275.0 MB for a 2048-row launch
     # of the 256x256x128 pair tile (the tile of the 4096-row slabs); 227.4 MB for a 2048-row launch of the
     # single-CTA kernel. Other slab heights are scaled by their rows (the traffic grows in proportion).
     if inc.kernelInfo["kernel"] == 4 and kpm.BLOCK_SIZE_M == 512:
-        traffic = 4.29e9 * rows / 32768.0
+        traffic = 5.76e9 * rows / 32768.0
     elif inc.kernelInfo["kernel"] == 4:
         traffic = 275.0e6 * rows / 2048.0
     else:
