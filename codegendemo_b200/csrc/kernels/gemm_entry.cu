@@ -28,9 +28,6 @@
 #ifndef KCG_OUT_F32
 #define KCG_OUT_F32 0
 #endif
-#ifndef KCG_CORR16  // fp32 data: 1 = the two correction products of the 3-product split run as bf16 MMAs
-#define KCG_CORR16 0
-#endif
 
 #if KCG_DTYPE == KCG_DT_F32
 #define KCG_T float
@@ -47,7 +44,7 @@
 #ifndef KCG_CHUNK  // K blocks multiplied into one TMEM accumulator before promotion to registers
 #define KCG_CHUNK ((128 / KCG_BK) > 0 ? (128 / KCG_BK) : 1)
 #endif
-using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK, 0, KCG_CORR16>;
+using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);
@@ -64,7 +61,7 @@ KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
 #ifndef KCG_CHUNK
 #define KCG_CHUNK ((128 / KCG_BK) > 0 ? (128 / KCG_BK) : 1)
 #endif
-using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK, 1, KCG_CORR16>;
+using Gemm = kcg::TcGemmF32x3<KCG_BM, KCG_BN, KCG_BK, KCG_STAGES, KCG_ATRANS, KCG_SPLITK, KCG_GROUP, KCG_CHUNK, 1>;
 extern "C" __global__ void __launch_bounds__(Gemm::NUM_THREADS, 1)
 KCG_KERNEL_NAME(const __grid_constant__ KcgGemmParams p) {
   Gemm::run(p);

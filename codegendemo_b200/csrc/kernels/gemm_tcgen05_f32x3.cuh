@@ -23,7 +23,6 @@
 // Same work decomposition, raster, split-K reduction and bounded waits as
 // gemm_tcgen05.cuh.
 #pragma once
-#include <cuda_bf16.h>
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
@@ -37,14 +36,8 @@ namespace kcg {
 // MMAs once the splitters of BOTH CTAs have arrived, and frees stages / publishes
 // accumulators in both CTAs with one commit each. Halving the B operand traffic per SM
 // lifts the shared-memory bound of the single-CTA form.
-//
-// kCorr16 = 1 computes the two correction products on the 16-bit path instead: the splitter writes, in place
-// of the tf32 lo twin, bf16 copies of lo AND of x for both operands (same bytes in total), laid out as the
-// 16-bit kernel lays out its tiles, and each K step issues hi*hi as kind::tf32 plus lo16*x16 + x16*lo16 as
-// kind::f16. The corrections are 2^-11 of the result, so their bf16 rounding (2^-9 relative) costs ~2^-20,
-// while they take half the tensor time and half the shared-memory reads of tf32 passes.
 template <int kBM, int kBN, int kBK, int kStages, int kATrans, int kSplitK, int kGroup, int kChunk,
-          int kPair = 0, int kCorr16 = 0>
+          int kPair = 0>
 struct TcGemmF32x3 {
   static constexpr int kDType = KCG_DT_F32;
   static constexpr int NCTA = kPair ? 2 : 1;
@@ -76,15 +69,6 @@ struct TcGemmF32x3 {
   static_assert(ACC_PER_THREAD <= 128, "register accumulators per thread");
   static constexpr int SMEM_BYTES = tc_smem_bytes(kDType, R, BNL, kBK, kStages, 1);
   static constexpr uint32_t IDESC = make_instr_desc(FMT_TF32, kATrans ? 1u : 0u, 1u, kPair ? 256u : 128u, kBN);
-  // 16-bit twins (kCorr16): [A lo16][A x16][B lo16][B x16] in the slot of one lo stage
-  static constexpr TcLayout L16 = make_tc_layout(KCG_DT_BF16, R, BNL, kBK, kATrans);
-  static constexpr int A16_BYTES = L16.a_bytes;
-  static constexpr int B16_BYTES = L16.b_bytes;
-  static constexpr int KSTEPS16 = kBK / 16;
-  static constexpr uint32_t IDESC16 = make_instr_desc(FMT_BF16, kATrans ? 1u : 0u, 1u, kPair ? 256u : 128u, kBN);
-  static_assert(!kCorr16 || (kBK % 16 == 0 && BNL % 64 == 0 && 2 * A16_BYTES + 2 * B16_BYTES == STAGE_HI &&
-                             A16_BYTES % 1024 == 0 && B16_BYTES % 1024 == 0 && STAGE_HI <= 65536),
-                "the 16-bit twins must tile the slot of a lo stage in 1 KB aligned pieces");
 
   struct Barriers {
     uint64_t full[kStages];
@@ -265,13 +249,7 @@ struct TcGemmF32x3 {
                   const uint64_t adesc_lo = make_smem_desc(sa_lo + a_t + a_off, L.a_lbo,
                                                            L.a_sbo, L.a_desc_swizzle);
                   const uint32_t d = tmem_acc + t * kBN;
-                  if constexpr (kCorr16) {
-                    if constexpr (kPair) {
-                      umma_ss_pair<true>(d, adesc, bdesc, IDESC, first);
-                    } else {
-                      umma_ss<true>(d, adesc, bdesc, IDESC, first);
-                    }
-                  } else if constexpr (kPair) {
+                  if constexpr (kPair) {
                     umma_ss_pair<true>(d, adesc_lo, bdesc, IDESC, first);
                     umma_ss_pair<true>(d, adesc, bdesc_lo, IDESC, 1u);
                     umma_ss_pair<true>(d, adesc, bdesc, IDESC, 1u);
@@ -279,41 +257,6 @@ struct TcGemmF32x3 {
                     umma_ss<true>(d, adesc_lo, bdesc, IDESC, first);
                     umma_ss<true>(d, adesc, bdesc_lo, IDESC, 1u);
                     umma_ss<true>(d, adesc, bdesc, IDESC, 1u);
-                  }
-                }
-              }
-              if constexpr (kCorr16) {
-                // the two correction products of this K block from the 16-bit twins
-                const uint32_t a_lo16 = sa_lo, a_x16 = sa_lo + A16_BYTES;
-                const uint32_t b_lo16 = sa_lo + 2 * A16_BYTES, b_x16 = b_lo16 + B16_BYTES;
-#pragma unroll
-                for (int ks = 0; ks < KSTEPS16; ++ks) {
-                  uint32_t a_off;
-                  if constexpr (kATrans) {
-                    a_off = ks * 16 * 128;
-                  } else {
-                    constexpr int swb = (kBK * 2 < 128) ? kBK * 2 : 128;
-                    a_off = ((ks * 32) / swb) * L16.a_box_bytes + ((ks * 32) % swb);
-                  }
-                  const uint32_t b_off = ks * 16 * 128;
-                  const uint64_t bdesc_x = make_smem_desc(b_x16 + b_off, L16.b_lbo, L16.b_sbo, L16.b_desc_swizzle);
-                  const uint64_t bdesc_l = make_smem_desc(b_lo16 + b_off, L16.b_lbo, L16.b_sbo, L16.b_desc_swizzle);
-#pragma unroll
-                  for (int t = 0; t < MT; ++t) {
-                    const uint32_t a_t = kATrans ? t * (128 / L16.atom) * L16.a_box_bytes
-                                                 : t * 128 * (L16.a_box_bytes / R);
-                    const uint64_t adesc_l =
-                        make_smem_desc(a_lo16 + a_t + a_off, L16.a_lbo, L16.a_sbo, L16.a_desc_swizzle);
-                    const uint64_t adesc_x =
-                        make_smem_desc(a_x16 + a_t + a_off, L16.a_lbo, L16.a_sbo, L16.a_desc_swizzle);
-                    const uint32_t d = tmem_acc + t * kBN;
-                    if constexpr (kPair) {
-                      umma_ss_pair<false>(d, adesc_l, bdesc_x, IDESC16, 1u);
-                      umma_ss_pair<false>(d, adesc_x, bdesc_l, IDESC16, 1u);
-                    } else {
-                      umma_ss<false>(d, adesc_l, bdesc_x, IDESC16, 1u);
-                      umma_ss<false>(d, adesc_x, bdesc_l, IDESC16, 1u);
-                    }
                   }
                 }
               }
@@ -341,41 +284,6 @@ struct TcGemmF32x3 {
       // --------------------------------------------------------------- splitter
       reg_dec<56>();
       const int stid = threadIdx.x - 128;
-      // kCorr16: which 16-byte units of a stage this thread converts and where their four values go in the
-      // 16-bit twins - the same for every stage, so worked out once (two 16-bit offsets per register). Units of a
-      // K-major tile are taken in storage order (a warp then writes four whole 64-byte rows of the twin); units of
-      // an MN-major tile so that a warp covers two K rows of two neighbouring 32-value boxes = two whole 128-byte
-      // rows of the twin (in storage order four K rows of ONE box would fall on the same half of the banks).
-      constexpr int NV = STAGE_HI / 16 / NUM_SPLIT_THREADS;   // units per thread per stage
-      constexpr int NVA = L.a_bytes / 16 / NUM_SPLIT_THREADS;  // of which in the A tile
-      static_assert(!kCorr16 || (NV % 4 == 0), "units are converted four at a time");
-      uint32_t spack[kCorr16 ? NV / 2 : 1], dpack[kCorr16 ? NV / 2 : 1];
-      if constexpr (kCorr16) {
-#pragma unroll
-        for (int j = 0; j < NV; ++j) {
-          const bool in_a = j < NVA;
-          const int v = stid + (in_a ? j : j - NVA) * NUM_SPLIT_THREADS;  // index inside its tile
-          const bool mn_major = !in_a || kATrans;
-          int o;
-          if (mn_major) {
-            const int lane32 = v % 32, grp = v / 32;
-            const int unit = lane32 % 8, boxpar = (lane32 / 8) % 2, krow = lane32 / 16;
-            const int box = 2 * (grp / (kBK / 2)) + boxpar, k = 2 * (grp % (kBK / 2)) + krow;
-            o = box * (kBK * 128) + k * 128 + unit * 16;
-          } else {
-            o = v * 16;
-          }
-          const int so = in_a ? o : L.a_bytes + o;
-          const int dst = in_a ? twin_offset<kATrans != 0, R>(o) : twin_offset<true, BNL>(o) + 2 * A16_BYTES;
-          if (j & 1) {
-            spack[j / 2] |= static_cast<uint32_t>(so) << 16;
-            dpack[j / 2] |= static_cast<uint32_t>(dst) << 16;
-          } else {
-            spack[j / 2] = static_cast<uint32_t>(so);
-            dpack[j / 2] = static_cast<uint32_t>(dst);
-          }
-        }
-      }
       uint32_t it = 0;
       bool ok = true;
       Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
@@ -401,44 +309,16 @@ struct TcGemmF32x3 {
             break;
           }
           const uint4* hi = reinterpret_cast<const uint4*>(smem + s * STAGE_HI);
-          if constexpr (kCorr16) {
-            const uint8_t* src = smem + s * STAGE_HI;
-            uint8_t* tw = smem + LO_RING + sl * STAGE_HI;
-            // groups of four units: their loads first (the compiler cannot move a load across the stores of
-            // the unit before it - both go to shared memory - so the order is written out)
-#pragma unroll
-            for (int j0 = 0; j0 < NV; j0 += 4) {
-              uint4 x[4];
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int j = j0 + u;
-                const uint32_t so = (j & 1) ? (spack[j / 2] >> 16) : (spack[j / 2] & 0xffffu);
-                x[u] = *reinterpret_cast<const uint4*>(src + so);
-              }
-#pragma unroll
-              for (int u = 0; u < 4; ++u) {
-                const int j = j0 + u;
-                const uint32_t dst = (j & 1) ? (dpack[j / 2] >> 16) : (dpack[j / 2] & 0xffffu);
-                const int other = (j < NVA) ? A16_BYTES : B16_BYTES;  // the x16 copy lies behind the lo16 copy
-                uint2 l16, x16;
-                split16(x[u].x, x[u].y, l16.x, x16.x);
-                split16(x[u].z, x[u].w, l16.y, x16.y);
-                *reinterpret_cast<uint2*>(tw + dst) = l16;
-                *reinterpret_cast<uint2*>(tw + dst + other) = x16;
-              }
-            }
-          } else {
-            uint4* lo = reinterpret_cast<uint4*>(smem + LO_RING + sl * STAGE_HI);
+          uint4* lo = reinterpret_cast<uint4*>(smem + LO_RING + sl * STAGE_HI);
 #pragma unroll 4
-            for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
-              const uint4 x = hi[i];
-              uint4 l;
-              l.x = lo_part(x.x);
-              l.y = lo_part(x.y);
-              l.z = lo_part(x.z);
-              l.w = lo_part(x.w);
-              lo[i] = l;
-            }
+          for (int i = stid; i < STAGE_HI / 16; i += NUM_SPLIT_THREADS) {
+            const uint4 x = hi[i];
+            uint4 l;
+            l.x = lo_part(x.x);
+            l.y = lo_part(x.y);
+            l.z = lo_part(x.z);
+            l.w = lo_part(x.w);
+            lo[i] = l;
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -622,45 +502,6 @@ struct TcGemmF32x3 {
         tmem_dealloc(tmem_base, TMEM_COLS);
       }
     }
-  }
-
-  // Byte offset, inside a 16-bit tile of the same shape, of the four values that one 16-byte unit of a landed
-  // fp32 operand tile holds (`o` = the unit's byte offset in the fp32 tile). Both tiles are in the layouts TMA
-  // and the UMMA descriptors use (make_tc_layout), so this undoes one swizzle and applies the other.
-  //   MN-major (B; A stored K x M): fp32 boxes of {32 values = 128 B along MN, kBK rows of K}, 32-byte units of a
-  //   row XORed with (k & 3); 16-bit boxes of {64 values = 128 B, kBK rows}, 16-byte units XORed with (k & 7).
-  //   K-major (A stored M x K): rows of min(128, kBK * elt) bytes of K, `kRows` rows per box, 16-byte units
-  //   XORed with the row's index inside the 8-row (1024 / 512 / 256 B) swizzle atom.
-  template <bool kMnMajor, int kRows>
-  __device__ static __forceinline__ int twin_offset(int o) {
-    if constexpr (kMnMajor) {
-      const int j = o / (kBK * 128);                 // 32-value chunk along MN
-      const int k = (o % (kBK * 128)) / 128;
-      const int unit = ((o % 128) / 32) ^ (k & 3);   // logical 32-byte unit
-      const int n0 = j * 32 + unit * 8 + ((o % 32) / 16) * 4;
-      return (n0 / 64) * (kBK * 128) + k * 128 + ((((n0 % 64) / 8) ^ (k & 7)) << 4) + (n0 % 8) * 2;
-    } else {
-      constexpr int swb = (kBK * 4 < 128) ? kBK * 4 : 128;    // fp32 row bytes
-      constexpr int swb16 = (kBK * 2 < 128) ? kBK * 2 : 128;  // 16-bit row bytes
-      const int j = o / (kRows * swb);
-      const int r = (o % (kRows * swb)) / swb;
-      const int sw = (swb == 128) ? (r & 7) : (swb == 64) ? ((r >> 1) & 3) : ((r >> 2) & 1);
-      const int k0 = j * (swb / 4) + ((((o % swb) / 16) ^ sw) << 2);
-      const int sw16 = (swb16 == 128) ? (r & 7) : (swb16 == 64) ? ((r >> 1) & 3) : ((r >> 2) & 1);
-      const int kb2 = k0 * 2;  // byte position of k0 in the 16-bit K extent
-      return (kb2 / swb16) * (kRows * swb16) + r * swb16 + ((((kb2 % swb16) / 16) ^ sw16) << 4) + (kb2 % 16);
-    }
-  }
-
-  // bf16 pairs of (x - trunc_tf32(x)) and of x itself for two consecutive values
-  __device__ static __forceinline__ void split16(uint32_t x0, uint32_t x1, uint32_t& lo16, uint32_t& x16) {
-    const float f0 = __uint_as_float(x0), f1 = __uint_as_float(x1);
-    const float l0 = f0 - __uint_as_float(x0 & 0xffffe000u);
-    const float l1 = f1 - __uint_as_float(x1 & 0xffffe000u);
-    __nv_bfloat162 l = __floats2bfloat162_rn(l0, l1);
-    __nv_bfloat162 h = __floats2bfloat162_rn(f0, f1);
-    lo16 = *reinterpret_cast<uint32_t*>(&l);
-    x16 = *reinterpret_cast<uint32_t*>(&h);
   }
 
   // tf32_rn(x - trunc_tf32(x)) on raw bits; the subtraction is exact in fp32.
