@@ -474,6 +474,17 @@ def test_strided_and_softmax_entries_validate_their_arguments_without_a_gpu():
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 4, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # ld below the row length
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 8, 0, ctypes.c_float(1.0), 8) == _lib.E_BAD_ARG     # float64
     assert lib.kcg_softmax_rows(0, 0, 4096, 4, 6, 0, ctypes.c_float(1.0), 62) == _lib.E_BAD_ARG    # 12-byte rows
+    # the fused attention entry checks its shape, type, scale and alignment before it touches the device
+    p = ctypes.c_uint64(4096)
+    one = ctypes.c_float(1.0)
+    assert lib.kcg_attention_fwd(0, 0, 0, p, p, p, 62, 2, 128, 128, 128, one) == _lib.E_BAD_ARG        # null Q
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 62, 2, 128, 128, 96, one) == _lib.E_BAD_CONFIG     # head dimension
+    assert b"64 or 128" in lib.kcg_last_error()
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 4, 2, 128, 128, 128, one) == _lib.E_BAD_ARG         # float32 data
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 62, 0, 128, 128, 128, one) == _lib.E_BAD_ARG        # no heads
+    assert lib.kcg_attention_fwd(0, 0, p, p, p, p, 62, 2, 128, 128, 128, ctypes.c_float(-1.0)) == _lib.E_BAD_ARG
+    assert lib.kcg_attention_fwd(0, 0, ctypes.c_uint64(4100), p, p, p, 62, 2, 128, 128, 128, one) == _lib.E_BAD_ARG
+    assert lib.kcg_attention_status(0, None) == _lib.E_BAD_ARG
 
 
 def test_cost_model_prefilter_drops_configs_that_idle_most_sms(tmp_path):
