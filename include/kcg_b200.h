@@ -200,8 +200,10 @@ int kcg_softmax_rows_ex(int device, uint64_t stream, uint64_t X, int dtype_in, i
  * O[h] = softmax(scale * Q[h] K[h]^T) V[h] for h in [0, heads): Q and O are heads x sq x d, K and V
  * heads x sk x d, all contiguous, float16 or bfloat16 (`dtype`), d = 64 or 128. Scores and
  * probabilities stay in tensor memory and shared memory (tcgen05.mma for both products, running
- * maximum and sum per query row); nothing of size sq x sk is written. Asynchronous on `stream`. No
- * counterpart in the reference (see the note on kcg_softmax_rows). */
+ * maximum and sum per query row); nothing of size sq x sk is written. Asynchronous on `stream`;
+ * allocates nothing. `scale` must be positive. The first call per device and data type opts the kernel in
+ * to its dynamic shared memory (a function attribute): make it before capturing the stream into a graph.
+ * No counterpart in the reference (see the note on kcg_softmax_rows). */
 int kcg_attention_fwd(int device, uint64_t stream, uint64_t Q, uint64_t K, uint64_t V, uint64_t O, int dtype,
                       int heads, int sq, int sk, int d, float scale);
 /* Synchronises `device` and reads (and clears) the status word of the kernel above: out = {code, block,
