@@ -700,33 +700,43 @@ int encode_map(DeviceState* s, CUtensorMap* out, int dtype, uint64_t ptr, uint64
 
 // How a tcgen05 launch cuts its tiles into work units (see kernels/work_iter.cuh).
 struct SplitPlan {
-  int tiles, first, factor, sk_per, sk_ranges, units_at_once;
+  int tiles, first, factor, sk_per, sk_ranges, units_at_once, units_first;
 };
 
 SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch = 1) {
   const int M = info->m * batch, N = info->n, K = info->k;  // a batched product is one tall problem
   const bool pair = info->kernel == KCG_KERNEL_TCGEN05_PAIR;
   const bool x3 = info->dtype == KCG_DTYPE_FLOAT32 && info->kernel != KCG_KERNEL_TF32X1;
-  // K splitting. LOCAL_SPLIT_U > 1 splits every tile evenly. Otherwise the tail of the persistent
-  // grid - the last, partially filled wave, together with the full wave before it when it is less
-  // than half full - runs as stream-K: the K blocks of those tiles, laid end to end, are cut into
-  // one contiguous range per CTA (pair), so that every SM works for the same time; tiles that fall
-  // into several ranges are reduced like an even split. KCG_TAIL_SPLIT=0 turns it off, =2 selects
-  // the even split of the last wave's tiles by floor(G / remainder) instead.
+  // K splitting. LOCAL_SPLIT_U > 1 splits every tile evenly. Otherwise the tiles that do not fill
+  // a wave of the persistent grid (the remainder) can be split over the CTAs so that every SM works
+  // for about the same time:
+  //  * even split (the default): each remainder tile is cut into floor(G / remainder) K ranges. In
+  //    the single-pass kernels these split units run FIRST and the whole tiles after them: all
+  //    contributors of a tile start with the kernel and finish together, their partial tiles are
+  //    written, summed (a share each) and stored by the epilogue warps while the main loops of the
+  //    whole tiles run, and the kernel ends with ordinary tiles. The 3xTF32 kernel, whose epilogue
+  //    warps are busy during the main loop, keeps the split units last.
+  //  * stream-K (KCG_TAIL_SPLIT=1): the remainder's K blocks - together with the full wave before
+  //    it when it is less than half a wave - laid end to end and cut into one contiguous range per
+  //    CTA (pair), after the whole tiles; tiles that fall into several ranges are reduced like an
+  //    even split. Measured slower than the even split on every benchmarked shape (ranges straddle
+  //    tile borders, so contributors finish at different times); kept for comparison.
+  // KCG_TAIL_SPLIT=0 turns the split off, =2 selects the even split, =3 / =4 stream-K / the even
+  // split without the cost gate.
   const int T = (M / info->bm) * (N / info->bn);
   const int num_kb = K / info->bk;
   const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
   const int G = pair ? nsm / 2 : nsm;  // work units that run at once (CTAs, or CTA pairs)
   int first = T, factor = 1, sk_per = 0, sk_ranges = 0;
+  int units_first = 0;
   if (info->splitk > 1) {
     first = 0;
     factor = info->splitk;
   } else {
     const char* e = getenv("KCG_TAIL_SPLIT");
-    // Default: stream-K for the single-pass kernel, whose partials move as full lines; the 3xTF32
-    // kernel stores its partials straight from registers and does better with the even split of
-    // the last wave only.
-    const int mode = (e && e[0] == '0') ? 0 : (e && e[0] == '2') ? 2 : (e && e[0] == '1') ? 1 : (x3 ? 2 : 1);
+    const bool ungated = e && (e[0] == '3' || e[0] == '4');
+    const int mode = (e && e[0] == '0') ? 0 : (e && (e[0] == '1' || e[0] == '3')) ? 1 : 2;
+    units_first = (!x3 && mode == 2) ? 1 : 0;
     const int rem = T % G;
     if (mode != 0 && rem > 0) {
       // Worth it only when the time saved exceeds the cost of the split. A tile's main-loop time is
@@ -737,35 +747,54 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
                                                                                                            : 10.0;
       const double tile_us =
           2.0 * (info->bm / (pair ? 2 : 1)) * info->bn * static_cast<double>(K) / 1e6 / mflop_per_us;
-      // What a split costs a CTA: its fp32 partial goes to the workspace once, the reducing CTA
-      // reads two or three of them back and writes C, and each extra unit refills the pipeline:
-      // 5 us plus 0.18 us per KB of partial tile (fitted to measurements). The saving has to beat
-      // that with a margin.
       const double partial_kb = (info->bm / (pair ? 2 : 1)) * static_cast<double>(info->bn) * 4.0 / 1024.0;
-      const double overhead_us = 5.0 + 0.18 * partial_kb;
-      const double gate_us = 1.25 * overhead_us;
+      // What a split costs, fitted to in-kernel timelines (128 KB partials: 3.4 us to write one,
+      // ~4.6 us for a contributor to sum its share of a tile straight from L2, ~12 us for the whole
+      // exchange at the end of a kernel when the contributors sum their shares out of their idle
+      // operand rings; ~4.6 us per partial when the last arriver sums a tile alone):
+      //  * hidden (whole tiles follow, single-pass kernels): a pipeline refill, plus whatever of
+      //    the write + shared sum does not fit behind one whole tile's main loop;
+      //  * exposed, shared (no whole tiles follow): 6 us + 0.05 us per KB of partial;
+      //  * exposed, summed by the last arriver (3xTF32): 5 us + 0.18 us per KB of partial.
+      const bool hidden = units_first != 0 && T > G;
+      auto overhead_us = [&](int contrib) {
+        if (hidden) {
+          const double fix = 1.5 + partial_kb * (contrib <= 8 ? 0.063 : 0.027 + 0.036 * contrib);
+          return 3.0 + (fix > tile_us ? fix - tile_us : 0.0);
+        }
+        return !x3 ? 6.0 + 0.05 * partial_kb : 5.0 + 0.18 * partial_kb;
+      };
+      const double margin = ungated ? 0.0 : 1.25;
       if (mode == 2) {
         int f = G / rem;
         if (f > 8) f = 8;
         if (f > num_kb) f = num_kb;
-        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= gate_us) {
+        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= margin * overhead_us(f)) {
           first = T - rem;
           factor = f;
         }
       } else {
-        const int R = (T > G && 2 * rem < G) ? rem + G : rem;  // tiles handed to stream-K
-        long long ranges = G;
-        if (ranges > 8LL * R) ranges = 8LL * R;  // at most ~8 contributors per tile
+        // Tiles handed to stream-K: the remainder, together with the full wave before it when the
+        // remainder is less than half a wave.
+        const int R = (T > G && 2 * rem < G) ? rem + G : rem;
         const long long blocks = static_cast<long long>(R) * num_kb;
-        if (ranges > blocks) ranges = blocks;
-        const long long per = (blocks + ranges - 1) / ranges;
-        ranges = (blocks + per - 1) / per;  // no empty range
         const double waves_without = static_cast<double>((R + G - 1) / G);
-        const double saved_us = tile_us * (waves_without - static_cast<double>(R) / static_cast<double>(ranges));
-        if (saved_us >= gate_us) {
-          first = T - R;
-          sk_per = static_cast<int>(per);
-          sk_ranges = static_cast<int>(ranges);
+        double best_gain = 0.0;
+        for (int cap = 7; cap >= 2; --cap) {  // at most cap + 1 contributors per tile (eight can share a sum)
+          long long ranges = G;
+          if (ranges > static_cast<long long>(cap) * R) ranges = static_cast<long long>(cap) * R;
+          if (ranges > blocks) ranges = blocks;
+          const long long per = (blocks + ranges - 1) / ranges;
+          ranges = (blocks + per - 1) / per;  // no empty range
+          const int contrib = static_cast<int>((num_kb + per - 1) / per) + 1;
+          const double saved_us = tile_us * (waves_without - static_cast<double>(R) / static_cast<double>(ranges));
+          const double gain = saved_us - margin * overhead_us(contrib < cap + 1 ? contrib : cap + 1);
+          if (gain > best_gain || (ungated && sk_per == 0)) {
+            best_gain = gain > best_gain ? gain : best_gain;
+            first = T - R;
+            sk_per = static_cast<int>(per);
+            sk_ranges = static_cast<int>(ranges);
+          }
         }
       }
     }
@@ -779,7 +808,7 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
     factor = 1;
     sk_per = 0;
   }
-  return SplitPlan{T, first, factor, sk_per, sk_ranges, G};
+  return SplitPlan{T, first, factor, sk_per, sk_ranges, G, units_first};
 }
 
 }  // namespace
@@ -792,8 +821,8 @@ extern "C" {
 int kcg_internal_fail(int code, const char* msg) { return fail(code, "%s", msg); }
 void kcg_internal_count_launch(void) { g_launches.fetch_add(1); }
 // Internal (tests): the work decomposition a launch of `info` would use:
-// {tiles, split_first_tile, split_factor, sk_per, stream-K ranges, units that run at once}.
-int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int batch, int out[6]) {
+// {tiles, split_first_tile, split_factor, sk_per, stream-K ranges, units that run at once, split units first}.
+int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int batch, int out[7]) {
   if (!info || !out || batch < 1) return fail(KCG_E_BAD_ARG, "null argument");
   const SplitPlan pl = plan_split(info, fused_epilogue != 0, batch);
   out[0] = pl.tiles;
@@ -802,6 +831,7 @@ int kcg_internal_plan_split(const kcg_kernel_info* info, int fused_epilogue, int
   out[3] = pl.sk_per;
   out[4] = pl.sk_ranges;
   out[5] = pl.units_at_once;
+  out[6] = pl.units_first;
   return 0;
 }
 
@@ -1137,6 +1167,7 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
     p.split_first_tile = first;
     p.split_factor = factor;
     p.sk_per = sk_per;
+    p.split_units_first = plan.units_first;
     if (factor > 1 || ws_epilogue || sk_per > 0) {
       // slots: one per (tile, split) of an even split; range index + tile index under stream-K
       const size_t slots = sk_per > 0 ? static_cast<size_t>(sk_ranges) + (T - first)

@@ -68,6 +68,11 @@ struct alignas(64) KcgGemmParams {
   // batch's, B holds the batches' K x N matrices one under the other (an A stored K x M likewise),
   // and batch_rows is the M of one batch, a multiple of the tile height.
   int batch_rows;
+  // Order of a CTA's units when a launch has both whole tiles and K-split tiles: 1 = the split
+  // units (even split or stream-K ranges) come first and the whole tiles after them, so that the
+  // partial tiles are written, summed and stored by the epilogue warps while the whole tiles' main
+  // loops run, and a CTA ends with an ordinary tile; 0 = whole tiles first, split units last.
+  int split_units_first;
   // Fused epilogue, in force when epi_flags != 0: D = act(alpha * (A.B) + beta * C + bias[col]),
   // computed in fp32 before the rounding to C's type. beta * C reads C in place (skipped when
   // beta == 0, so C may then hold anything); bias has N values of C's type.

@@ -30,12 +30,21 @@
 // where TMEM is freed.
 #pragma once
 #include <cuda_bf16.h>
+#ifdef KCG_TIMELINE_PRINT
+#include <cstdio>
+#endif
 #include <cuda_fp16.h>
 
 #include "epilogue.cuh"
 #include "gemm_params.h"
 #include "ptx_sm100.cuh"
 #include "work_iter.cuh"
+
+// How long a CTA waits for the other partial tiles of a shared K-split reduction before it hands
+// its share to the last arriver.
+#ifndef KCG_SHARE_WAIT_NS
+#define KCG_SHARE_WAIT_NS 20000ull
+#endif
 
 namespace kcg {
 
@@ -104,12 +113,13 @@ struct TcGemm {
     uint64_t empty[kStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
+    uint64_t red_full;  // partial tiles of a shared reduction have landed in the (idle) operand ring
     uint32_t tmem_base;
     volatile uint32_t abort_flag;
     uint32_t last_flag;
     uint32_t push_count;  // epilogue warps that have finished (and completed the stores of) a whole-K tile
 #ifdef KCG_TIMELINE
-    uint64_t tl[16];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
+    uint64_t tl[20];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
 #endif
   };
 #ifdef KCG_TIMELINE
@@ -146,7 +156,7 @@ struct TcGemm {
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
 #ifdef KCG_TIMELINE
     if (threadIdx.x == 0) {
-      for (int i = 10; i < 16; ++i) bars->tl[i] = 0;
+      for (int i = 10; i < 20; ++i) bars->tl[i] = 0;
     }
     __syncthreads();
 #endif
@@ -171,6 +181,7 @@ struct TcGemm {
         mbar_init(&bars->tmem_full[a], 1);
         mbar_init(&bars->tmem_empty[a], 4 * NCTA);  // one arrival per epilogue warp of each CTA
       }
+      mbar_init(&bars->red_full, 1);
       bars->abort_flag = 0u;
       bars->last_flag = 0u;
       bars->push_count = 0u;
@@ -476,6 +487,7 @@ struct TcGemm {
       OutT* Cout = reinterpret_cast<OutT*>(p.C);
       uint8_t* stg = smem + kStages * STAGE_BYTES + 1024 + (warp - 2) * (2 * STG_BYTES);
       uint32_t stg_it = 0;  // staging buffers this warp has filled
+      uint32_t red_phase = 0;  // parity of red_full
       if (warp == 2 && lane == 0) tma_prefetch_desc(&p.tmC);
       Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
       Unit w;
@@ -621,93 +633,275 @@ struct TcGemm {
         if (warp == 2 && lane == 0 && acc_it == 0) KCG_TL(6);
 
         if (w.nsplit > 1) {
-          // Publish this split's partial tile; the last split to arrive sums all
-          // partials in split order (bitwise reproducible) and writes C.
+          // Publish this split's partial tile; then the partials are summed, always in split order
+          // (bitwise reproducible), by one of two protocols on the tile's counter word
+          // (arrivals in bits 0-7, shares given up in bits 8-15, shares done in bits 16-23):
+          //  * w.share = 0: the last contributor to arrive sums the whole tile;
+          //  * w.share > 0: contributors 0 .. share-1 wait a short while for all partials and sum one
+          //    share-th of the CTA's rows each, so the reduction runs on several SMs at once
+          //    (out of the operand ring when this is the CTA's last unit and the ring is idle,
+          //    straight from L2 while the next unit's main loop runs otherwise). A waiter that runs
+          //    out of patience (the other CTAs may not be running: another kernel can hold their
+          //    SMs while this one holds theirs) records its share as given up and goes on; the last
+          //    contributor to arrive - who never waits - sums the shares given up before it came.
+          // Whoever finishes the last share zeroes the word for the next launch.
           const int ctr = (w.tile - first_split) * NCTA + static_cast<int>(rank);  // per CTA half
           if (lane == 0) tma_store_wait_all<0>();  // this warp's blocks of the partial are written
           fence_proxy_async_all();                 // ... and ordered before the generic-proxy release below
           __threadfence();
           named_bar_sync(1, NUM_EPI_THREADS);
+          const bool sharer = w.split < w.share;
           if (epi_tid == 0) {
+            const unsigned int all = static_cast<unsigned int>(w.nsplit);
             const unsigned int old = atomicAdd(&p.tile_counters[ctr], 1u);
-            bars->last_flag = (old == static_cast<unsigned int>(w.nsplit - 1)) ? 1u : 0u;
-            if (old == static_cast<unsigned int>(w.nsplit - 1)) p.tile_counters[ctr] = 0u;
+            const bool came_last = (old & 0xffu) == all - 1u;
+            unsigned int mine = 0u;  // bit s: this CTA sums share s
+            if (w.share == 0) {
+              if (came_last) {
+                mine = 1u;
+                p.tile_counters[ctr] = 0u;
+              }
+            } else {
+              if (came_last) mine = (old >> 8) & 0xffu;
+              if (sharer) {
+                bool go = came_last;
+                if (!go) {
+                  const uint64_t t0 = global_timer_ns();
+                  for (;;) {
+                    if ((ld_acquire_gpu(&p.tile_counters[ctr]) & 0xffu) == all) {
+                      go = true;
+                      break;
+                    }
+                    if (bars->abort_flag != 0u || global_timer_ns() - t0 > KCG_SHARE_WAIT_NS) break;
+                    __nanosleep(40);
+                  }
+                  if (!go) {
+                    // give the share up - unless the last partial came in the meantime: then nobody
+                    // has seen the bit, and the share is still this CTA's
+                    const unsigned int seen = atomicOr(&p.tile_counters[ctr], 1u << (8 + w.split));
+                    go = (seen & 0xffu) == all;
+                  }
+                }
+                if (go) mine |= 1u << w.split;
+              }
+            }
+            bars->last_flag = mine;
           }
           named_bar_sync(1, NUM_EPI_THREADS);
-          const bool last = bars->last_flag != 0u;
-          if (last) {
+          const unsigned int mine = bars->last_flag;
+          if (warp == 2 && lane == 0 && acc_it == 0) KCG_TL(14);
+          bool ok = true;
+          if (mine != 0u) {
             __threadfence();
-            // Cooperative reduction of this CTA's R rows of the tile: they are contiguous in every
-            // partial, so consecutive threads read consecutive 16-byte pieces (whole 128-byte lines
-            // per quarter warp) and write C the same way. Eight pieces of up to four partials are
-            // fetched before any is added, so that the L2 round trips overlap; the adds run in K order.
+            // This CTA's R rows of the tile are contiguous in every partial. 16-byte pieces are
+            // summed in K order and written to C by consecutive threads (whole 128-byte lines per
+            // quarter warp).
             constexpr int F4_PER_ROW = kBN / 4;
-            constexpr int TOTAL = R * F4_PER_ROW;
-            constexpr int UNR = 8;
             const size_t slot0 = static_cast<size_t>(w.slot - w.split);
-            for (int base = epi_tid; base < TOTAL; base += NUM_EPI_THREADS * UNR) {
-              float4 acc[UNR];
-#pragma unroll
-              for (int u = 0; u < UNR; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int s0 = 0; s0 < w.nsplit; s0 += 4) {
-                float4 x[4][UNR];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (s0 + j < w.nsplit) {
-                    const float4* src = reinterpret_cast<const float4*>(
-                        p.splitk_ws + ((slot0 + s0 + j) * kBM + row_base) * kBN);
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) {
-                      const int idx = base + u * NUM_EPI_THREADS;
-                      if (idx < TOTAL) x[j][u] = __ldcg(src + idx);
-                    }
-                  }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (s0 + j < w.nsplit) {
-#pragma unroll
-                    for (int u = 0; u < UNR; ++u) {
-                      acc[u].x += x[j][u].x;
-                      acc[u].y += x[j][u].y;
-                      acc[u].z += x[j][u].z;
-                      acc[u].w += x[j][u].w;
-                    }
-                  }
-                }
-              }
-#pragma unroll
-              for (int u = 0; u < UNR; ++u) {
-                const int idx = base + u * NUM_EPI_THREADS;
-                if (idx >= TOTAL) continue;
-                const int row = w.m0 + row_base + idx / F4_PER_ROW;
-                const int col = w.n0 + (idx % F4_PER_ROW) * 4;
-                if (row >= p.M || col >= p.N) continue;
-                float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
-                if (p.epi_flags != 0u) epi_span<OutT, 4>(p, o, row, col);
-                const size_t off = static_cast<size_t>(row) * p.ldc + col;
-                if constexpr (sizeof(OutT) == 4) {
-                  const float4 out = make_float4(o[0], o[1], o[2], o[3]);
-                  *reinterpret_cast<float4*>(Cout + off) = out;
-                  for (int pe = 0; pe < p.n_peers; ++pe)
-                    *reinterpret_cast<float4*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+            auto emit = [&](int idx, const float4& sum) {  // idx: piece within this CTA's rows of the tile
+              const int row = w.m0 + row_base + idx / F4_PER_ROW;
+              const int col = w.n0 + (idx % F4_PER_ROW) * 4;
+              if (row >= p.M || col >= p.N) return;
+              float o[4] = {sum.x, sum.y, sum.z, sum.w};
+              if (p.epi_flags != 0u) epi_span<OutT, 4>(p, o, row, col);
+              const size_t off = static_cast<size_t>(row) * p.ldc + col;
+              if constexpr (sizeof(OutT) == 4) {
+                const float4 out = make_float4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<float4*>(Cout + off) = out;
+                for (int pe = 0; pe < p.n_peers; ++pe)
+                  *reinterpret_cast<float4*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+              } else {
+                uint2 out;
+                if constexpr (kDType == KCG_DT_BF16) {
+                  __nv_bfloat162 l2 = __floats2bfloat162_rn(o[0], o[1]), h2 = __floats2bfloat162_rn(o[2], o[3]);
+                  out = make_uint2(*reinterpret_cast<uint32_t*>(&l2), *reinterpret_cast<uint32_t*>(&h2));
                 } else {
-                  uint2 out;
-                  if constexpr (kDType == KCG_DT_BF16) {
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(o[0], o[1]), hi = __floats2bfloat162_rn(o[2], o[3]);
-                    out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                  } else {
-                    __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
-                    out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                  __half2 l2 = __floats2half2_rn(o[0], o[1]), h2 = __floats2half2_rn(o[2], o[3]);
+                  out = make_uint2(*reinterpret_cast<uint32_t*>(&l2), *reinterpret_cast<uint32_t*>(&h2));
+                }
+                *reinterpret_cast<uint2*>(Cout + off) = out;
+                for (int pe = 0; pe < p.n_peers; ++pe)
+                  *reinterpret_cast<uint2*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+              }
+            };
+            const int nshares = w.share > 0 ? w.share : 1;
+            const int rows_per = (R + nshares - 1) / nshares;
+            for (int s = 0; s < nshares && ok; ++s) {
+              if (!((mine >> s) & 1u)) continue;
+              const int r_lo = s * rows_per;
+              const int r_hi = r_lo + rows_per < R ? r_lo + rows_per : R;
+              if (sharer && w.last) {
+                // This is the CTA's last unit, so its operand ring is idle (every load has landed
+                // and every MMA that read it has retired: the accumulator was seen full). The rows
+                // of all partials come in as bulk copies, as many rows at a time as the ring
+                // holds - far more bytes in flight than registers could hold, which is what the L2
+                // round trip asks for - and are summed out of shared memory.
+                constexpr int ROW_BYTES = kBN * 4;
+                constexpr int OUT_ROW_BYTES = kBN * static_cast<int>(sizeof(OutT));
+                constexpr int RING_BYTES = kStages * STAGE_BYTES;
+                const int max_rows = RING_BYTES / (ROW_BYTES * w.nsplit + OUT_ROW_BYTES);
+                ok = max_rows > 0;
+                // The sums leave as one bulk copy per row of the tile (plain stores from 128 threads
+                // reach only a few GB/s: too few of them are in flight for an L2 round trip each):
+                // they are packed into the ring behind the partials first. Not for the fused
+                // all-gather (the peers get plain stores) nor for a tile that hangs over C's edge.
+                const bool bulk_out = p.n_peers == 0 && w.n0 + kBN <= p.N;
+                for (int r0 = r_lo; r0 < r_hi && ok; r0 += max_rows) {
+                  const int nr = r_hi - r0 < max_rows ? r_hi - r0 : max_rows;
+                  const uint32_t bytes = static_cast<uint32_t>(nr) * ROW_BYTES;
+                  if (lane == 0) tma_store_wait_read<0>();  // ... also by the bulk copies of the sums
+                  named_bar_sync(1, NUM_EPI_THREADS);  // earlier rows have been read out of the ring
+                  if (epi_tid == 0) {
+                    fence_proxy_async_all();  // the acquire above, before the async-proxy reads of the partials
+                    mbar_expect_tx(&bars->red_full, bytes * static_cast<uint32_t>(w.nsplit));
+                    for (int j = 0; j < w.nsplit; ++j)
+                      bulk_load_1d(smem + static_cast<size_t>(j) * bytes,
+                                   p.splitk_ws + ((slot0 + j) * kBM + row_base + r0) * kBN, bytes, &bars->red_full);
                   }
-                  *reinterpret_cast<uint2*>(Cout + off) = out;
-                  for (int pe = 0; pe < p.n_peers; ++pe)
-                    *reinterpret_cast<uint2*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
+                  const bool got = mbar_wait(&bars->red_full, red_phase, &bars->abort_flag);
+                  red_phase ^= 1u;
+                  ok = named_bar_all(2, NUM_EPI_THREADS, got);
+                  if (!ok) break;
+                  if (warp == 2 && lane == 0 && acc_it == 0) KCG_TL(16);
+                  const int pieces = nr * F4_PER_ROW;
+                  // four pieces per thread at a time: their loads from shared memory are independent,
+                  // so a step of the sum costs one load latency, not four
+                  constexpr int U = 4;
+                  const uint32_t ring = smem_u32(smem);
+                  for (int i0 = epi_tid; i0 < pieces; i0 += NUM_EPI_THREADS * U) {
+                    float4 sum[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) sum[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j = 0; j < w.nsplit; ++j) {
+                      const uint32_t src = ring + static_cast<uint32_t>(j) * bytes;
+                      float4 x[U];
+#pragma unroll
+                      for (int u = 0; u < U; ++u) {
+                        const int i = i0 + u * NUM_EPI_THREADS;
+                        x[u] = ld_shared_f4(src + static_cast<uint32_t>(i < pieces ? i : i0) * 16u);
+                      }
+#pragma unroll
+                      for (int u = 0; u < U; ++u) {
+                        sum[u].x += x[u].x;
+                        sum[u].y += x[u].y;
+                        sum[u].z += x[u].z;
+                        sum[u].w += x[u].w;
+                      }
+                    }
+                    if (bulk_out) {
+                      const uint32_t out = ring + static_cast<uint32_t>(w.nsplit) * bytes;
+#pragma unroll
+                      for (int u = 0; u < U; ++u) {
+                        const int i = i0 + u * NUM_EPI_THREADS;
+                        if (i >= pieces) continue;
+                        float o[4] = {sum[u].x, sum[u].y, sum[u].z, sum[u].w};
+                        if (p.epi_flags != 0u) {
+                          const int idx = r0 * F4_PER_ROW + i;
+                          epi_span<OutT, 4>(p, o, w.m0 + row_base + idx / F4_PER_ROW, w.n0 + (idx % F4_PER_ROW) * 4);
+                        }
+                        if constexpr (sizeof(OutT) == 4) {
+                          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(out + static_cast<uint32_t>(i) * 16u),
+                                       "f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3])
+                                       : "memory");
+                        } else {
+                          uint32_t lo2, hi2;
+                          if constexpr (kDType == KCG_DT_BF16) {
+                            __nv_bfloat162 a2 = __floats2bfloat162_rn(o[0], o[1]), b2 = __floats2bfloat162_rn(o[2], o[3]);
+                            lo2 = *reinterpret_cast<uint32_t*>(&a2);
+                            hi2 = *reinterpret_cast<uint32_t*>(&b2);
+                          } else {
+                            __half2 a2 = __floats2half2_rn(o[0], o[1]), b2 = __floats2half2_rn(o[2], o[3]);
+                            lo2 = *reinterpret_cast<uint32_t*>(&a2);
+                            hi2 = *reinterpret_cast<uint32_t*>(&b2);
+                          }
+                          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(out + static_cast<uint32_t>(i) * 8u), "r"(lo2),
+                                       "r"(hi2)
+                                       : "memory");
+                        }
+                      }
+                    } else {
+#pragma unroll
+                      for (int u = 0; u < U; ++u) {
+                        const int i = i0 + u * NUM_EPI_THREADS;
+                        if (i < pieces) emit(r0 * F4_PER_ROW + i, sum[u]);
+                      }
+                    }
+#ifdef KCG_TIMELINE
+                    if (warp == 2 && lane == 0 && acc_it == 0 && bars->tl[17] == 0) KCG_TL(17);
+                    else if (warp == 2 && lane == 0 && acc_it == 0 && bars->tl[18] == 0) KCG_TL(18);
+#endif
+                  }
+                  if (bulk_out) {
+                    fence_proxy_async_smem();  // the packed sums, before the async-proxy reads of the copies
+                    named_bar_sync(1, NUM_EPI_THREADS);
+                    if (lane == 0) {
+                      const uint32_t out = ring + static_cast<uint32_t>(w.nsplit) * bytes;
+                      for (int r = warp - 2; r < nr; r += 4) {
+                        const int row = w.m0 + row_base + r0 + r;
+                        if (row < p.M)
+                          bulk_store_1d(Cout + static_cast<size_t>(row) * p.ldc + w.n0,
+                                        out + static_cast<uint32_t>(r) * OUT_ROW_BYTES, OUT_ROW_BYTES);
+                      }
+                      tma_store_commit();
+                    }
+                  }
+                }
+              } else {
+                // Straight from L2 (the ring may be loading the next unit): eight pieces of up to
+                // four partials are fetched before any is added, so that the round trips overlap.
+                constexpr int UNR = 8;
+                const int hi = r_hi * F4_PER_ROW;
+                for (int base = r_lo * F4_PER_ROW + epi_tid; base < hi; base += NUM_EPI_THREADS * UNR) {
+                  float4 acc[UNR];
+#pragma unroll
+                  for (int u = 0; u < UNR; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  for (int s0 = 0; s0 < w.nsplit; s0 += 4) {
+                    float4 x[4][UNR];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      if (s0 + j < w.nsplit) {
+                        const float4* src = reinterpret_cast<const float4*>(
+                            p.splitk_ws + ((slot0 + s0 + j) * kBM + row_base) * kBN);
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                          const int idx = base + u * NUM_EPI_THREADS;
+                          if (idx < hi) x[j][u] = __ldcg(src + idx);
+                        }
+                      }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                      if (s0 + j < w.nsplit) {
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                          acc[u].x += x[j][u].x;
+                          acc[u].y += x[j][u].y;
+                          acc[u].z += x[j][u].z;
+                          acc[u].w += x[j][u].w;
+                        }
+                      }
+                    }
+                  }
+#pragma unroll
+                  for (int u = 0; u < UNR; ++u) {
+                    const int idx = base + u * NUM_EPI_THREADS;
+                    if (idx < hi) emit(idx, acc[u]);
+                  }
                 }
               }
             }
           }
-          named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit
+          if (!ok) {
+            if (epi_tid == 0) report(p, bars, KCG_ST_TIMEOUT_EPILOGUE, 0x300u + w.split, w.tile);
+            break;
+          }
+          named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit; every read of the partials is done
+          if (warp == 2 && lane == 0 && acc_it == 0 && mine != 0u) KCG_TL(15);
+          if (w.share > 0 && mine != 0u && epi_tid == 0) {
+            const unsigned int n = static_cast<unsigned int>(__popc(mine));
+            const unsigned int old = atomicAdd(&p.tile_counters[ctr], n << 16);
+            if (((old >> 16) & 0xffu) + n == static_cast<unsigned int>(w.share)) p.tile_counters[ctr] = 0u;
+          }
         }
       }
       // The staging buffers must have been read before the CTA gives its shared memory back; the
@@ -748,6 +942,15 @@ struct TcGemm {
     __syncthreads();
     if (threadIdx.x == 0 && blockIdx.x == 0)
       for (int i = 0; i < 16; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
+#ifdef KCG_TIMELINE_PRINT  // K-split launches: another CTA's reduction may overwrite the dump in C
+    if (threadIdx.x == 0 && blockIdx.x < 4)
+      printf("KCG_TL cta %d: bar %.2f tma %.2f landed %.2f mma_done %.2f acc_full %.2f written %.2f published %.2f partials_in %.2f it1 %.2f it2 %.2f reduced %.2f "
+             "stores_read %.2f exit %.2f\n", static_cast<int>(blockIdx.x), (bars->tl[1] - bars->tl[0]) * 1e-3,
+             (bars->tl[2] - bars->tl[0]) * 1e-3, (bars->tl[3] - bars->tl[0]) * 1e-3, (bars->tl[4] - bars->tl[0]) * 1e-3,
+             (bars->tl[5] - bars->tl[0]) * 1e-3, (bars->tl[6] - bars->tl[0]) * 1e-3,
+             bars->tl[14] ? (bars->tl[14] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[16] ? (bars->tl[16] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[17] ? (bars->tl[17] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[18] ? (bars->tl[18] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[15] ? (bars->tl[15] - bars->tl[0]) * 1e-3 : 0.0,
+             (bars->tl[7] - bars->tl[0]) * 1e-3, (bars->tl[8] - bars->tl[0]) * 1e-3);
+#endif
 #endif
   }
 };

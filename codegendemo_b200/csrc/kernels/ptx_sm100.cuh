@@ -72,6 +72,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Acquire load at GPU scope: polls a counter that other CTAs bump after publishing data.
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int* ptr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+
 // Bounded wait on a phase parity. `abort_flag` is a CTA-shared word any role
 // sets when it gave up; once set every other wait returns false at once.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
@@ -335,6 +342,30 @@ __device__ __forceinline__ void st_cluster_v4(uint32_t cluster_addr, uint32_t a,
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b),
                "r"(c), "r"(d)
                : "memory");
+}
+// Bulk asynchronous copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from this CTA's
+// shared memory to contiguous global memory; joins the thread's current bulk group (tma_store_commit /
+// tma_store_wait_*).
+__device__ __forceinline__ void bulk_store_1d(void* dst_global, uint32_t src_smem_addr, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                   reinterpret_cast<uint64_t>(dst_global)),
+               "r"(src_smem_addr), "r"(bytes)
+               : "memory");
+}
+// 16-byte load from this CTA's shared memory by its 32-bit shared address.
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+// Bulk asynchronous copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) of contiguous
+// global memory into this CTA's shared memory; completion is counted as transaction bytes on `bar`.
+__device__ __forceinline__ void bulk_load_1d(void* dst_smem, const void* src_global, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(reinterpret_cast<uint64_t>(src_global)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
 }
 // Bulk asynchronous copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) from this CTA's
 // shared memory into the shared memory of a CTA of the cluster; completion is counted as transaction

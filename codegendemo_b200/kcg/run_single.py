@@ -33,6 +33,9 @@ def print_timeline(C, variant: int) -> None:
         extra = {9: "ring-idle signals sent", 10: "blocks staged", 12: "warp 1's copies issued", 15: "own block read",
                  11: "first block summed", 13: "first block stored"}
         print("  " + "  ".join(f"{name} +{(t[i] - t[0]) / 1e3:.2f}" for i, name in extra.items() if t[i] > t[0]))
+    if variant != 5 and t[14] > t[0]:
+        print(f"  K-split unit 0: partial published +{(t[14] - t[0]) / 1e3:.2f}"
+              + (f"  tile reduced and stored +{(t[15] - t[0]) / 1e3:.2f}" if t[15] > t[0] else "  (not the reducer)"))
     if variant != 5:
         print(f"  cycles over the K loop: producer waiting {t[10]}, producer issuing {t[11]}, "
               f"MMA thread waiting {t[12]}, MMA thread issuing {t[13]}")

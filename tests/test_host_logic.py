@@ -222,49 +222,60 @@ def test_fused_allgather_targets_and_argument_checks():
 
 
 WORK_PLANS = [
-    # (M, N, K, dtype, keys, expected layer: "whole" | "even" | "streamk")
+    # (M, N, K, dtype, keys, expected layer: "whole" | "even" | "streamk"[, batch]); "streamk" cases select
+    # stream-K through KCG_TAIL_SPLIT=1 (the default for a remainder is the even split)
     (8192, 8192, 8192, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
-    # 50 of 74 pairs busy in the last of 28 waves: the saving is below the cost of 256 KB partials
+    # 50 of 74 pairs busy in the last of 28 waves: floor(74 / 50) = 1, nothing to split evenly
     (32768, 8192, 8192, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
     (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, NUM_STAGES=4), "whole"),
-    # 86 pair tiles on 74 pairs: all of them go to stream-K (1.16 waves become one)
+    # 86 pair tiles on 74 pairs: the 12 remainder tiles are cut six ways and run first, the 74 whole tiles after them
+    (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=4), "even"),
+    # ... or, as stream-K, all 86 go into 74 ranges (1.16 waves become one)
     (512, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, NUM_STAGES=4), "streamk"),
-    # 224 tiles of 256x256: the 76-tile tail is cut into 147 ranges, one fewer than the 148 CTAs that walk the whole tiles
+    # 224 tiles of 256x256 on 148 CTAs: 76 left over, floor(148 / 76) = 1; stream-K cuts that tail into 147 ranges,
+    # one fewer than the 148 CTAs that walk the whole tiles
+    (1792, 8192, 11008, E.bfloat16, dict(BLOCK_SIZE_M=256, NUM_STAGES=3), "whole"),
     (1792, 8192, 11008, E.bfloat16, dict(BLOCK_SIZE_M=256, NUM_STAGES=3), "streamk"),
-    (2048, 4096, 4096, E.bfloat16, dict(), "whole"),      # 108 tiles in the last wave: the saving is below the gate
-    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk"),  # small tiles: cheap partials
+    (2048, 4096, 4096, E.bfloat16, dict(), "whole"),      # 108 tiles in the last wave
+    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "even"),  # 44 left over of 1376: cut three ways, first
+    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk"),
     (128, 4096, 4096, E.bfloat16, dict(BLOCK_SIZE_N=128), "whole"),   # too little work per tile to pay for a reduction
     (128, 11008, 11008, E.bfloat16, dict(LOCAL_SPLIT_U=4, BLOCK_SIZE_N=256), "even"),
-    # 3xTF32 kernel: even split of the last wave's 68 tiles by two, not stream-K
+    # 3xTF32 kernel: even split of the last wave's 68 tiles by two, after the whole tiles
     (4096, 4096, 4096, E.float32, dict(BLOCK_SIZE_N=256, BLOCK_SIZE_K=16, NUM_STAGES=4), "even"),
     (256, 512, 1280, E.bfloat16, dict(LOCAL_SPLIT_U=3), "even"),
-    # serpentine raster inside the groups of four tile rows (RASTER_SERPENTINE), with a stream-K tail
+    # serpentine raster inside the groups of four tile rows (RASTER_SERPENTINE), with a split remainder
+    (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128, BLOCK_MAPPING=4, RASTER_SERPENTINE=1), "even"),
     (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128, BLOCK_MAPPING=4, RASTER_SERPENTINE=1), "streamk"),
-    # batched: 40 products of 256x512x16384 walked as one tall problem (320 tiles: the tail goes to stream-K)
+    # batched: 40 products of 256x512x16384 walked as one tall problem (320 tiles, 24 left over)
+    (256, 512, 16384, E.bfloat16, dict(BLOCK_SIZE_N=128), "even", 40),
     (256, 512, 16384, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk", 40),
     (128, 256, 2048, E.bfloat16, dict(LOCAL_SPLIT_U=2), "even", 4),
 ]
 
 
 @pytest.mark.parametrize("case", WORK_PLANS, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-{c[5]}" + (f"-b{c[6]}" if len(c) > 6 else ""))
-def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
-    """The launcher's plan (whole tiles / even K split / stream-K over the tail) fed to the kernels' own
-    iterator, compiled for the host: every CTA's unit sequence is walked and coverage, contributor numbering
-    and workspace slots are checked (tests/work_iter_check.cpp)."""
+def test_work_decomposition_covers_every_k_block_once(case, tmp_path, monkeypatch):
+    """The launcher's plan (whole tiles / even K split, split units first / stream-K over the tail) fed to the
+    kernels' own iterator, compiled for the host: every CTA's unit sequence is walked and coverage, contributor
+    numbering, workspace slots, who sums and the order of split units are checked (tests/work_iter_check.cpp)."""
     import ctypes
     from codegendemo_b200 import _lib
     from codegendemo_b200.kcg.KCGCompiler import compile_info
     M, N, K, dt, keys, layer = case[:6]
     batch = case[6] if len(case) > 6 else 1
+    monkeypatch.delenv("KCG_TAIL_SPLIT", raising=False)
+    if layer == "streamk":
+        monkeypatch.setenv("KCG_TAIL_SPLIT", "1")
     kpm = default_config(M, N, K, dt, **keys)
     info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT,
                         serpentine=kpm.RASTER_SERPENTINE)
-    out = (ctypes.c_int * 6)()
+    out = (ctypes.c_int * 7)()
     lib = _lib.get_lib()
     lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.c_int,
                                             ctypes.POINTER(ctypes.c_int)]
     assert lib.kcg_internal_plan_split(ctypes.byref(info), 0, batch, out) == 0
-    tiles, first, factor, sk_per, ranges, at_once = list(out)
+    tiles, first, factor, sk_per, ranges, at_once, units_first = list(out)
     got = "streamk" if sk_per > 0 else "even" if factor > 1 else "whole"
     assert got == layer, (got, list(out))
     if sk_per > 0:
@@ -279,7 +290,8 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path):
     subprocess.run(["g++", "-O1", "-std=c++17", "-I/usr/local/cuda/include", "-I" + kdir, f"-DWIC_BM={info.bm}",
                     f"-DWIC_BN={info.bn}", f"-DWIC_BK={info.bk}", f"-DWIC_GROUP={info.group}", f"-DKCG_SERPENTINE={int(info.reserved[2])}", "-o", str(exe),
                     os.path.join(ROOT, "tests", "work_iter_check.cpp")], check=True)
-    args = [str(exe), str(M * batch), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots)]
+    args = [str(exe), str(M * batch), str(N), str(K), str(first), str(factor), str(sk_per), str(grid), str(slots),
+            str(units_first)]
     if batch > 1:
         args.append(str(M))  # rows of one batch: the iterator's batch offsets are checked too
     r = subprocess.run(args, capture_output=True, text=True)
