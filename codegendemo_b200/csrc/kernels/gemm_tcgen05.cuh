@@ -826,10 +826,6 @@ struct TcGemm {
                         if (i < pieces) emit(r0 * F4_PER_ROW + i, sum[u]);
                       }
                     }
-#ifdef KCG_TIMELINE
-                    if (warp == 2 && lane == 0 && acc_it == 0 && bars->tl[17] == 0) KCG_TL(17);
-                    else if (warp == 2 && lane == 0 && acc_it == 0 && bars->tl[18] == 0) KCG_TL(18);
-#endif
                   }
                   if (bulk_out) {
                     fence_proxy_async_smem();  // the packed sums, before the async-proxy reads of the copies
@@ -943,13 +939,12 @@ struct TcGemm {
     if (threadIdx.x == 0 && blockIdx.x == 0)
       for (int i = 0; i < 16; ++i) reinterpret_cast<uint64_t*>(p.C)[i] = bars->tl[i];
 #ifdef KCG_TIMELINE_PRINT  // K-split launches: another CTA's reduction may overwrite the dump in C
-    if (threadIdx.x == 0 && blockIdx.x < 4)
-      printf("KCG_TL cta %d: bar %.2f tma %.2f landed %.2f mma_done %.2f acc_full %.2f written %.2f published %.2f partials_in %.2f it1 %.2f it2 %.2f reduced %.2f "
-             "stores_read %.2f exit %.2f\n", static_cast<int>(blockIdx.x), (bars->tl[1] - bars->tl[0]) * 1e-3,
-             (bars->tl[2] - bars->tl[0]) * 1e-3, (bars->tl[3] - bars->tl[0]) * 1e-3, (bars->tl[4] - bars->tl[0]) * 1e-3,
-             (bars->tl[5] - bars->tl[0]) * 1e-3, (bars->tl[6] - bars->tl[0]) * 1e-3,
-             bars->tl[14] ? (bars->tl[14] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[16] ? (bars->tl[16] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[17] ? (bars->tl[17] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[18] ? (bars->tl[18] - bars->tl[0]) * 1e-3 : 0.0, bars->tl[15] ? (bars->tl[15] - bars->tl[0]) * 1e-3 : 0.0,
-             (bars->tl[7] - bars->tl[0]) * 1e-3, (bars->tl[8] - bars->tl[0]) * 1e-3);
+    if (threadIdx.x == 0 && blockIdx.x < 4) {
+      auto us = [&](int i) { return bars->tl[i] ? (bars->tl[i] - bars->tl[0]) * 1e-3 : 0.0; };
+      printf("KCG_TL cta %d (us after entry, first unit): accumulator full %.2f  written %.2f  published / others awaited %.2f  "
+             "partials in the ring %.2f  summed %.2f  stores read %.2f  exit %.2f\n",
+             static_cast<int>(blockIdx.x), us(5), us(6), us(14), us(16), us(15), us(7), us(8));
+    }
 #endif
 #endif
   }

@@ -372,6 +372,63 @@ def test_two_streams_run_split_k_launches_side_by_side():
         assert torch.equal(out, c)
 
 
+# (M, N, K, keys): remainders of a persistent grid's waves, small enough for the host product.
+#  - 80 / 160 tiles on 74 pairs / 148 CTAs: the few left-over tiles are cut eight ways and run first,
+#    their partial tiles summed (a share per contributor, straight from L2) under the whole tiles' main loops;
+#  - 22 tiles on 74 pairs: no whole tiles follow, the contributors sum their shares out of the idle operand ring.
+REMAINDER_CASES = [
+    (1280, 4096, 1024, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64)),
+    (1280, 4096, 1024, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64)),
+    (512, 2816, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)),
+    (640, 2816, 1536, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64)),
+]
+
+
+@pytest.mark.parametrize("plan", ["3", "4"], ids=["stream-k", "even-split"])
+@pytest.mark.parametrize("case", REMAINDER_CASES, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-V{c[3]['KERNEL_VARIANT']}")
+def test_remainder_split_plans_match_oracle_and_repeat_bitwise(case, plan, monkeypatch):
+    """Both ways of splitting the tiles that do not fill a wave (KCG_TAIL_SPLIT: 3 = stream-K, 4 = even split, each
+    without its cost gate so that these small problems take it): the product matches the host oracle, every element
+    of C is written, and a second launch gives the same bits (partials are summed in K order whoever sums them)."""
+    M, N, K, keys = case
+    monkeypatch.setenv("KCG_TAIL_SPLIT", plan)
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=M + int(plan))
+    c, kern, (a, b) = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
+    assert not torch.isnan(c).any().item(), "kernel left part of C unwritten"
+    assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.TOL_16BIT
+    again = torch.full_like(c, float("nan"))
+    for _ in range(3):
+        kern.run(a, b, again)
+    kern.checkStatus()
+    assert torch.equal(again, c)
+    monkeypatch.setenv("KCG_TAIL_SPLIT", "0")  # whole tiles only: same values up to the order of the fp32 sums
+    whole = torch.full_like(c, float("nan"))
+    kern.run(a, b, whole)
+    kern.checkStatus()
+    assert (whole.float() - c.float()).abs().max().item() <= 2e-2 * c.float().abs().max().item()
+
+
+def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(monkeypatch, tmp_path):
+    """A contributor that gives up waiting for the other partial tiles hands its share of the sum to the last
+    arriver. Built with a waiting time of zero (KCG_SHARE_WAIT_NS=0, private cubin cache) every contributor that
+    is not last gives up at once, so the hand-over runs on every split tile; the sum order does not change, so
+    the result must equal the normal build's bit for bit."""
+    M, N, K = 512, 2816, 2048
+    keys = dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)
+    monkeypatch.setenv("KCG_TAIL_SPLIT", "4")
+    A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=77)
+    c, _, (a, b) = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
+    monkeypatch.setenv("KCG_NVCC_FLAGS", "-DKCG_SHARE_WAIT_NS=0")
+    monkeypatch.setenv("KCG_CACHE_DIR", str(tmp_path))
+    c2, kern2, _ = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
+    assert torch.equal(c2, c)
+    for _ in range(5):  # the counters are left at zero every time
+        out = torch.full_like(c, float("nan"))
+        kern2.run(a, b, out)
+        kern2.checkStatus()
+        assert torch.equal(out, c)
+
+
 def test_strided_operands_are_read_and_written_in_place():
     """kcg_launch_gemm_strided: A, B and C as column blocks of wider row-major arrays (leading dimension > row
     length); what lies outside the C block is left untouched."""
