@@ -734,9 +734,10 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
     factor = info->splitk;
   } else {
     const char* e = getenv("KCG_TAIL_SPLIT");
-    const bool ungated = e && (e[0] == '3' || e[0] == '4');
-    const int mode = (e && e[0] == '0') ? 0 : (e && (e[0] == '1' || e[0] == '3')) ? 1 : 2;
-    units_first = (!x3 && mode == 2) ? 1 : 0;
+    const bool sk_first = e && e[0] == '5' && !x3;  // stream-K ranges before the whole tiles, no gate
+    const bool ungated = e && (e[0] == '3' || e[0] == '4' || e[0] == '5');
+    const int mode = (e && e[0] == '0') ? 0 : (e && (e[0] == '1' || e[0] == '3' || e[0] == '5')) ? 1 : 2;
+    units_first = (!x3 && (mode == 2 || sk_first)) ? 1 : 0;
     const int rem = T % G;
     if (mode != 0 && rem > 0) {
       // Worth it only when the time saved exceeds the cost of the split. A tile's main-loop time is
@@ -776,7 +777,7 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
       } else {
         // Tiles handed to stream-K: the remainder, together with the full wave before it when the
         // remainder is less than half a wave.
-        const int R = (T > G && 2 * rem < G) ? rem + G : rem;
+        const int R = (!sk_first && T > G && 2 * rem < G) ? rem + G : rem;
         const long long blocks = static_cast<long long>(R) * num_kb;
         const double waves_without = static_cast<double>((R + G - 1) / G);
         double best_gain = 0.0;

@@ -119,7 +119,7 @@ struct TcGemm {
     uint32_t last_flag;
     uint32_t push_count;  // epilogue warps that have finished (and completed the stores of) a whole-K tile
 #ifdef KCG_TIMELINE
-    uint64_t tl[20];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
+    uint64_t tl[24];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
 #endif
   };
 #ifdef KCG_TIMELINE
@@ -156,7 +156,7 @@ struct TcGemm {
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
 #ifdef KCG_TIMELINE
     if (threadIdx.x == 0) {
-      for (int i = 10; i < 20; ++i) bars->tl[i] = 0;
+      for (int i = 10; i < 24; ++i) bars->tl[i] = 0;
     }
     __syncthreads();
 #endif
@@ -529,12 +529,17 @@ struct TcGemm {
 #pragma unroll 1
             for (int g = 0; g < kBN / SCOLS; ++g, ++stg_it) {
               uint8_t* buf = stg + (stg_it & 1u) * STG_BYTES;
+              KCG_TLC(c_e0);
               if (lane == 0) tma_store_wait_read<1>();  // the store that last read `buf` is done
               __syncwarp();
+              if (warp == 2 && lane == 0) KCG_TLC_ADD(20, c_e0);
+              KCG_TLC(c_e1);
               uint32_t ra[32], rb[32];  // rb: columns 32..63 of a 16-bit block
               tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS, ra);
               if constexpr (SCOLS == 64) tmem_ld_32x32b_x32(tmem_acc + t * kBN + g * SCOLS + 32, rb);
               tmem_ld_wait();
+              if (warp == 2 && lane == 0) KCG_TLC_ADD(21, c_e1);
+              KCG_TLC(c_e2);
               float va[32], vb[32];
 #pragma unroll
               for (int i = 0; i < 32; ++i) {
@@ -570,6 +575,8 @@ struct TcGemm {
                 }
                 *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = o;
               }
+              if (warp == 2 && lane == 0) KCG_TLC_ADD(22, c_e2);
+              KCG_TLC(c_e3);
               fence_proxy_async_smem();  // generic-proxy writes visible to the TMA engine
               __syncwarp();
               const int col0 = w.n0 + g * SCOLS;
@@ -577,6 +584,7 @@ struct TcGemm {
                 tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
                 tma_store_commit();
               }
+              if (warp == 2 && lane == 0) KCG_TLC_ADD(23, c_e3);
             }
             if constexpr (HALF) release(static_cast<uint32_t>(t));
           }
@@ -724,13 +732,107 @@ struct TcGemm {
                   *reinterpret_cast<uint2*>(reinterpret_cast<OutT*>(p.peerC[pe]) + off) = out;
               }
             };
+            // Sum of blocks [b_lo, b_hi) of the CTA's rows of the tile - 32 rows x one staging buffer's
+            // width each, dealt to the four warps in turn - straight from L2, leaving like a whole
+            // tile's C: packed into the warp's swizzled staging buffers and written by TMA stores.
+            // Used while the operand ring is busy with the next unit.
+            constexpr int BLK_PER_ROWBLOCK = kBN / SCOLS;
+            constexpr int NBLK = (R / 32) * BLK_PER_ROWBLOCK;
+            auto sum_blocks = [&](int b_lo, int b_hi) {
+              constexpr int PPR = SCOLS / 4;               // 16-byte pieces of a partial per block row
+              constexpr int PIECES = 32 * PPR;             // ... per block
+              constexpr int UNR = 8, JB = 2;  // pieces per lane and partials fetched before any is added
+              for (int blk = b_lo + (warp - 2); blk < b_hi; blk += 4, ++stg_it) {
+                const int rb = blk / BLK_PER_ROWBLOCK, g = blk - rb * BLK_PER_ROWBLOCK;
+                uint8_t* buf = stg + (stg_it & 1u) * STG_BYTES;
+                if (lane == 0) tma_store_wait_read<1>();  // the store that last read `buf` is done
+                __syncwarp();
+                const uint32_t buf_s = smem_u32(buf);
+#pragma unroll 1
+                for (int q0 = 0; q0 < PIECES; q0 += 32 * UNR) {
+                  float4 acc[UNR];
+#pragma unroll
+                  for (int u = 0; u < UNR; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  for (int s0 = 0; s0 < w.nsplit; s0 += JB) {
+                    float4 x[JB][UNR];
+#pragma unroll
+                    for (int j = 0; j < JB; ++j) {
+                      if (s0 + j < w.nsplit) {
+                        const float* src = p.splitk_ws + ((slot0 + s0 + j) * kBM + row_base + rb * 32) * kBN + g * SCOLS;
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                          const int q = q0 + u * 32 + lane;
+                          x[j][u] = __ldcg(reinterpret_cast<const float4*>(src + (q / PPR) * kBN + (q % PPR) * 4));
+                        }
+                      }
+                    }
+#pragma unroll
+                    for (int j = 0; j < JB; ++j) {
+                      if (s0 + j < w.nsplit) {
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                          acc[u].x += x[j][u].x;
+                          acc[u].y += x[j][u].y;
+                          acc[u].z += x[j][u].z;
+                          acc[u].w += x[j][u].w;
+                        }
+                      }
+                    }
+                  }
+#pragma unroll
+                  for (int u = 0; u < UNR; ++u) {
+                    const int q = q0 + u * 32 + lane;
+                    const int r = q / PPR, k = q % PPR;
+                    float o[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+                    if (p.epi_flags != 0u) {
+                      const int row = w.m0 + row_base + rb * 32 + r;
+                      if (row < p.M) epi_span<OutT, 4>(p, o, row, w.n0 + g * SCOLS + k * 4);
+                    }
+                    const uint32_t rowp = buf_s + static_cast<uint32_t>(r) * 128u;
+                    if constexpr (sizeof(OutT) == 4) {
+                      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(rowp + ((static_cast<uint32_t>(k) ^ (r & 7)) << 4)),
+                                   "f"(o[0]), "f"(o[1]), "f"(o[2]), "f"(o[3])
+                                   : "memory");
+                    } else {
+                      uint32_t lo2, hi2;
+                      if constexpr (kDType == KCG_DT_BF16) {
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[0], o[1]), b2 = __floats2bfloat162_rn(o[2], o[3]);
+                        lo2 = *reinterpret_cast<uint32_t*>(&a2);
+                        hi2 = *reinterpret_cast<uint32_t*>(&b2);
+                      } else {
+                        __half2 a2 = __floats2half2_rn(o[0], o[1]), b2 = __floats2half2_rn(o[2], o[3]);
+                        lo2 = *reinterpret_cast<uint32_t*>(&a2);
+                        hi2 = *reinterpret_cast<uint32_t*>(&b2);
+                      }
+                      asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(rowp + ((static_cast<uint32_t>(k >> 1) ^ (r & 7)) << 4) +
+                                                                         static_cast<uint32_t>(k & 1) * 8u),
+                                   "r"(lo2), "r"(hi2)
+                                   : "memory");
+                    }
+                  }
+                }
+                fence_proxy_async_smem();  // generic-proxy writes visible to the TMA engine
+                __syncwarp();
+                const int row0 = w.m0 + row_base + rb * 32, col0 = w.n0 + g * SCOLS;
+                if (lane == 0 && row0 < p.M && col0 < p.N) {
+                  tma_store_2d(&p.tmC, buf, col0, row0);  // rows / columns past the edge are clipped
+                  tma_store_commit();
+                }
+              }
+            };
+            // Shares are runs of such blocks when every split unit of the launch is followed by whole
+            // tiles (even split, split units first), else runs of rows (contiguous in a partial: what
+            // the bulk copies into the ring want).
+            const bool by_blocks = p.split_units_first != 0 && p.sk_per == 0 && first_split > 0;
             const int nshares = w.share > 0 ? w.share : 1;
             const int rows_per = (R + nshares - 1) / nshares;
             for (int s = 0; s < nshares && ok; ++s) {
               if (!((mine >> s) & 1u)) continue;
               const int r_lo = s * rows_per;
               const int r_hi = r_lo + rows_per < R ? r_lo + rows_per : R;
-              if (sharer && w.last) {
+              if (p.n_peers == 0 && (by_blocks || w.share == 0)) {
+                sum_blocks(w.share == 0 ? 0 : s * NBLK / nshares, w.share == 0 ? NBLK : (s + 1) * NBLK / nshares);
+              } else if (sharer && w.last) {
                 // This is the CTA's last unit, so its operand ring is idle (every load has landed
                 // and every MMA that read it has retired: the accumulator was seen full). The rows
                 // of all partials come in as bulk copies, as many rows at a time as the ring
@@ -843,9 +945,10 @@ struct TcGemm {
                   }
                 }
               } else {
-                // Straight from L2 (the ring may be loading the next unit): eight pieces of up to
-                // four partials are fetched before any is added, so that the round trips overlap.
-                constexpr int UNR = 8;
+                // Rows straight from L2 with plain stores of C (and of the peers' copies of it): the
+                // slow way, for the fused all-gather's split tiles and for row shares handed to a
+                // last arriver whose ring is busy.
+                constexpr int UNR = 2;
                 const int hi = r_hi * F4_PER_ROW;
                 for (int base = r_lo * F4_PER_ROW + epi_tid; base < hi; base += NUM_EPI_THREADS * UNR) {
                   float4 acc[UNR];
@@ -944,6 +1047,8 @@ struct TcGemm {
       printf("KCG_TL cta %d (us after entry, first unit): accumulator full %.2f  written %.2f  published / others awaited %.2f  "
              "partials in the ring %.2f  summed %.2f  stores read %.2f  exit %.2f\n",
              static_cast<int>(blockIdx.x), us(5), us(6), us(14), us(16), us(15), us(7), us(8));
+      printf("KCG_TL cta %d epilogue cycles (warp 2, all whole tiles): staging buffer free %llu  TMEM read %llu  convert + st.shared %llu  "
+             "fence + TMA store issue %llu\n", static_cast<int>(blockIdx.x), bars->tl[20], bars->tl[21], bars->tl[22], bars->tl[23]);
     }
 #endif
 #endif
