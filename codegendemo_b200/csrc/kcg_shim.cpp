@@ -722,7 +722,8 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
   //    even split. Measured slower than the even split on every benchmarked shape (ranges straddle
   //    tile borders, so contributors finish at different times); kept for comparison.
   // KCG_TAIL_SPLIT=0 turns the split off, =2 selects the even split, =3 / =4 stream-K / the even
-  // split without the cost gate.
+  // split without the cost gate, =5 stream-K over the remainder alone BEFORE the whole tiles (the
+  // last arriver sums a tile; no gate; an experiment that measured no consistent gain).
   const int T = (M / info->bm) * (N / info->bn);
   const int num_kb = K / info->bk;
   const int nsm = info->reserved[0] > 0 ? info->reserved[0] : 148;
