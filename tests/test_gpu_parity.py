@@ -384,12 +384,13 @@ REMAINDER_CASES = [
 ]
 
 
-@pytest.mark.parametrize("plan", ["3", "4"], ids=["stream-k", "even-split"])
+@pytest.mark.parametrize("plan", ["3", "4", "5"], ids=["stream-k", "even-split", "stream-k-first"])
 @pytest.mark.parametrize("case", REMAINDER_CASES, ids=lambda c: f"{c[0]}x{c[1]}x{c[2]}-V{c[3]['KERNEL_VARIANT']}")
 def test_remainder_split_plans_match_oracle_and_repeat_bitwise(case, plan, monkeypatch):
-    """Both ways of splitting the tiles that do not fill a wave (KCG_TAIL_SPLIT: 3 = stream-K, 4 = even split, each
-    without its cost gate so that these small problems take it): the product matches the host oracle, every element
-    of C is written, and a second launch gives the same bits (partials are summed in K order whoever sums them)."""
+    """The ways of splitting the tiles that do not fill a wave (KCG_TAIL_SPLIT: 3 = stream-K after the whole tiles,
+    4 = even split before them, 5 = stream-K before them; each without its cost gate so that these small problems
+    take it): the product matches the host oracle, every element of C is written, and a second launch gives the
+    same bits (partials are summed in K order whoever sums them)."""
     M, N, K, keys = case
     monkeypatch.setenv("KCG_TAIL_SPLIT", plan)
     A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=M + int(plan))
