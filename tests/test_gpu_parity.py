@@ -409,6 +409,38 @@ def test_remainder_split_plans_match_oracle_and_repeat_bitwise(case, plan, monke
     assert (whole.float() - c.float()).abs().max().item() <= 2e-2 * c.float().abs().max().item()
 
 
+def test_two_full_grids_with_shared_reductions_side_by_side():
+    """Two persistent launches that each want every SM, queued on two streams without ordering, both with a split
+    remainder whose contributors wait for each other's partial tiles: whichever way the hardware deals the SMs - a
+    contributor may not be running while its partners wait - the waits are bounded and abandoned shares are taken
+    over, so both products complete and equal their serial runs bit for bit."""
+    shapes = [(512, 11008, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)),
+              (1280, 4096, 2048, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64))]
+    os.environ["KCG_TAIL_SPLIT"] = "4"
+    try:
+        kerns, ops, serial = [], [], []
+        for i, (M, N, K, keys) in enumerate(shapes):
+            A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=50 + i)
+            c, kern, (a, b) = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
+            assert oracle.rel_errors(c, oracle.host_matmul(A, B))["max_rel"] <= oracle.TOL_16BIT
+            kerns.append(kern), ops.append((a, b)), serial.append(c)
+        streams = [torch.cuda.Stream(device=0) for _ in shapes]
+        outs = [torch.full_like(c, float("nan")) for c in serial]
+        torch.cuda.synchronize()
+        for _ in range(30):
+            for st, kern, (a, b), out in zip(streams, kerns, ops, outs):
+                with torch.cuda.stream(st):
+                    kern.run(a, b, out)
+        for st, kern in zip(streams, kerns):
+            with torch.cuda.stream(st):
+                kern.checkStatus()
+        torch.cuda.synchronize()
+        for out, c in zip(outs, serial):
+            assert torch.equal(out, c)
+    finally:
+        os.environ.pop("KCG_TAIL_SPLIT", None)
+
+
 def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(monkeypatch, tmp_path):
     """A contributor that gives up waiting for the other partial tiles hands its share of the sum to the last
     arriver. Built with a waiting time of zero (KCG_SHARE_WAIT_NS=0, private cubin cache) every contributor that
