@@ -666,6 +666,13 @@ int fill_info(const Cfg& c, const Resolved& r, const std::string& name, const st
   out->reserved[1] = r.btrans;
   out->reserved[2] = r.serpentine;
   out->reserved[3] = r.out_f32 ? KCG_DTYPE_FLOAT32 : 0;
+  {
+    // accumulator buffers of the single-pass tcgen05 kernels: two when REG_PREFETCH is on and two
+    // copies of a CTA's accumulator fit the 512 TMEM columns (gemm_tcgen05.cuh: NACC)
+    const int rows = bm / (r.kernel == KCG_KERNEL_TCGEN05_PAIR ? 2 : 1);
+    const int acc_cols = (rows / 128 > 0 ? rows / 128 : 1) * bn;
+    out->reserved[4] = (c[KCG_CFG_REG_PREFETCH] && 2 * acc_cols <= 512) ? 2 : 1;
+  }
   return 0;
 }
 
@@ -768,12 +775,32 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
       };
       const double margin = ungated ? 0.0 : 1.25;
       if (mode == 2) {
-        int f = G / rem;
-        if (f > 8) f = 8;
-        if (f > num_kb) f = num_kb;
-        if (f >= 2 && tile_us * (1.0 - 1.0 / f) >= margin * overhead_us(f)) {
-          first = T - rem;
-          factor = f;
+        // Cut each remainder tile into f K ranges; the rem * f units take ceil(rem * f / G) rounds
+        // of 1/f of a tile's time. One round (f <= G / rem) always qualifies; several rounds - a
+        // remainder of more than half a wave cut into quarters runs as three rounds, 3/4 of a
+        // tile instead of a whole one - only when the units run first, whole tiles follow and the
+        // kernel has two accumulator buffers (the MMAs of the next unit must not wait for the
+        // epilogue warps, who are busy with the previous unit's partial tile): every unit's
+        // write-and-sum (with the waits for partners a round apart, ~1.5 us + 0.14 us per KB
+        // on the timelines) must fit behind the main loops that are still to come.
+        double best_gain = 0.0;
+        for (int f = 2; f <= 8 && f <= num_kb; ++f) {
+          const int rounds = (rem * f + G - 1) / G;
+          if (rounds > 1 && (!hidden || info->reserved[4] < 2)) break;  // needs a spare accumulator to run ahead
+          double cost;
+          if (hidden) {
+            const double fix = rounds * (1.5 + 0.14 * partial_kb);
+            const double room = tile_us * (1.0 + static_cast<double>(rounds - 1) / f);
+            cost = 3.0 * rounds + (fix > room ? fix - room : 0.0);
+          } else {
+            cost = overhead_us(f);
+          }
+          const double gain = tile_us * (1.0 - static_cast<double>(rounds) / f) - margin * cost;
+          if (gain > best_gain || (ungated && factor == 1 && rounds == 1)) {
+            best_gain = gain > best_gain ? gain : best_gain;
+            first = T - rem;
+            factor = f;
+          }
         }
       } else {
         // Tiles handed to stream-K: the remainder, together with the full wave before it when the

@@ -83,7 +83,8 @@ typedef struct kcg_kernel_info {
   int32_t atrans;     /* IS_ATRANS */
   int32_t m, n, k;
   int32_t reserved[8]; /* [0] persistent grid cap (SMs), [1] b_trans, [2] serpentine,
-                          [3] DATATYPE_C when it differs from DATATYPE_A (float32 C over 16-bit operands) */
+                          [3] DATATYPE_C when it differs from DATATYPE_A (float32 C over 16-bit operands),
+                          [4] accumulator buffers in tensor memory (single-pass tcgen05 kernels: 1 or 2) */
 } kcg_kernel_info;
 
 typedef struct kcg_compile_opts {

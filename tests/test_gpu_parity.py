@@ -381,6 +381,8 @@ REMAINDER_CASES = [
     (1280, 4096, 1024, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64)),
     (512, 2816, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)),
     (640, 2816, 1536, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64)),
+    # 128 pair tiles on 74 pairs: the even split cuts the 54 left-over tiles into quarters, three rounds of units
+    (2048, 4096, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)),
 ]
 
 
