@@ -52,7 +52,7 @@ class KernelInfo(ctypes.Structure):
 
     _SCALARS = ("smem_bytes", "kernel", "dtype", "bm", "bn", "bk", "stages", "splitk", "group",
                 "atrans", "m", "n", "k")
-    _RESERVED = {"num_sms": 0, "b_trans": 1, "serpentine": 2, "dtype_c": 3}  # named slots of `reserved`
+    _RESERVED = {"num_sms": 0, "b_trans": 1, "serpentine": 2, "dtype_c": 3, "acc_buffers": 4}  # named slots of `reserved`
 
     def to_dict(self) -> dict:
         """Plain, picklable form (compile workers hand it to the process that owns the GPU)."""

@@ -788,6 +788,10 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
           const int rounds = (rem * f + G - 1) / G;
           if (rounds > 1 && (!hidden || info->reserved[4] < 2)) break;  // needs a spare accumulator to run ahead
           double cost;
+          // several rounds: a unit's write-and-sum must be over before the next unit's accumulator is
+          // full, or the epilogue warps fall behind (1024x8192x8192 in quarters, 12 us units against
+          // ~19 us: 4 % slower than unsplit; 2048x11008x11008 in thirds, 21 us units: 5 % faster)
+          if (!ungated && rounds > 1 && tile_us / f < 1.5 + 0.14 * partial_kb) continue;
           if (hidden) {
             const double fix = rounds * (1.5 + 0.14 * partial_kb);
             const double room = tile_us * (1.0 + static_cast<double>(rounds - 1) / f);

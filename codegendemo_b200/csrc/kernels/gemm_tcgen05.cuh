@@ -119,7 +119,7 @@ struct TcGemm {
     uint32_t last_flag;
     uint32_t push_count;  // epilogue warps that have finished (and completed the stores of) a whole-K tile
 #ifdef KCG_TIMELINE
-    uint64_t tl[24];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
+    uint64_t tl[32];  // %globaltimer stamps of CTA 0's phases (experiments only; dumped over C[0, 0..])
 #endif
   };
 #ifdef KCG_TIMELINE
@@ -156,7 +156,7 @@ struct TcGemm {
     Barriers* bars = reinterpret_cast<Barriers*>(smem + kStages * STAGE_BYTES);
 #ifdef KCG_TIMELINE
     if (threadIdx.x == 0) {
-      for (int i = 10; i < 24; ++i) bars->tl[i] = 0;
+      for (int i = 10; i < 32; ++i) bars->tl[i] = 0;
     }
     __syncthreads();
 #endif
@@ -412,6 +412,7 @@ struct TcGemm {
             KCG_TLC_ADD(13, c_issue);
           }
           if (acc_it == 0) KCG_TL(4);
+          if (acc_it < 4) KCG_TL(24 + acc_it);  // MMAs of the CTA's first four units issued
           if (ok) {
             if constexpr (kPair) {
               umma_commit_pair(smem_u32(&bars->tmem_full[ab]));
@@ -996,6 +997,7 @@ struct TcGemm {
           }
           named_bar_sync(1, NUM_EPI_THREADS);  // last_flag is rewritten next unit; every read of the partials is done
           if (warp == 2 && lane == 0 && acc_it == 0 && mine != 0u) KCG_TL(15);
+          if (warp == 2 && lane == 0 && acc_it < 4) KCG_TL(28 + acc_it);  // epilogue of the unit (write, wait, sum) done
           if (w.share > 0 && mine != 0u && epi_tid == 0) {
             const unsigned int n = static_cast<unsigned int>(__popc(mine));
             const unsigned int old = atomicAdd(&p.tile_counters[ctr], n << 16);
@@ -1047,6 +1049,8 @@ struct TcGemm {
       printf("KCG_TL cta %d (us after entry, first unit): accumulator full %.2f  written %.2f  published / others awaited %.2f  "
              "partials in the ring %.2f  summed %.2f  stores read %.2f  exit %.2f\n",
              static_cast<int>(blockIdx.x), us(5), us(6), us(14), us(16), us(15), us(7), us(8));
+      printf("KCG_TL cta %d first four units: MMAs issued %.2f %.2f %.2f %.2f  split-unit epilogues done %.2f %.2f %.2f %.2f\n",
+             static_cast<int>(blockIdx.x), us(24), us(25), us(26), us(27), us(28), us(29), us(30), us(31));
       printf("KCG_TL cta %d epilogue cycles (warp 2, all whole tiles): staging buffer free %llu  TMEM read %llu  convert + st.shared %llu  "
              "fence + TMA store issue %llu\n", static_cast<int>(blockIdx.x), bars->tl[20], bars->tl[21], bars->tl[22], bars->tl[23]);
     }

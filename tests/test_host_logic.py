@@ -237,9 +237,11 @@ WORK_PLANS = [
     (1792, 8192, 11008, E.bfloat16, dict(BLOCK_SIZE_M=256, NUM_STAGES=3), "whole"),
     (1792, 8192, 11008, E.bfloat16, dict(BLOCK_SIZE_M=256, NUM_STAGES=3), "streamk"),
     (2048, 4096, 4096, E.bfloat16, dict(), "whole"),      # 108 tiles in the last wave
-    # 128 pair tiles on 74 pairs, long K: the 54 left over are cut into quarters, 216 units = three rounds before the
-    # whole tiles (3/4 of a tile's time instead of a whole one); the kernel has two accumulator buffers
-    (2048, 4096, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128), "even"),
+    # 344 pair tiles on 74 pairs, long K: the 48 left over are cut into thirds, 144 units = two rounds before the
+    # whole tiles (2/3 of a tile's time instead of a whole one); the kernel has two accumulator buffers and a unit
+    # lasts longer than its write-and-sum. With K = 4096 the units would be too short: whole tiles only.
+    (2048, 11008, 11008, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128), "even"),
+    (2048, 11008, 4096, E.bfloat16, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128), "whole"),
     (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "even"),  # 44 left over of 1376: cut three ways, first
     (2048, 11008, 11008, E.bfloat16, dict(BLOCK_SIZE_N=128), "streamk"),
     (128, 4096, 4096, E.bfloat16, dict(BLOCK_SIZE_N=128), "whole"),   # too little work per tile to pay for a reduction
