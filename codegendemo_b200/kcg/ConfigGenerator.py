@@ -236,7 +236,7 @@ def estimate_us(cfg: Dict) -> float:
     unit_us = max(2.0 * rows * bn * (K / split) / 1e6 / rate, unit_kb / SM_LOAD_KB_PER_US)
     waves = units / at_once
     if waves > 1.0 and split == 1:
-        waves = max(1.0, waves)                               # the stream-K tail levels the last wave
+        waves = max(1.0, waves)                               # at best the remainder split levels the last wave
     else:
         waves = float(-(-units // at_once))
     ctas = units * (2 if pair else 1) * (split if variant == 5 else 1)

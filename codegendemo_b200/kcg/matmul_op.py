@@ -67,7 +67,7 @@ def tuned_config(M: int, N: int, K: int, dtype: EnumKernelDType, isATranspose: i
                               NUM_STAGES=4, isATranspose=isATranspose)
     if K % 128 == 0 and tiles256 >= pairs:
         # one to twelve waves of 256x256 pair tiles: CTA pairs with 128-wide K blocks (half as many stage
-        # hand-offs per byte as 64-wide ones, two accumulator buffers, stream-K tail); best or within 2 % of
+        # hand-offs per byte as 64-wide ones, two accumulator buffers, remainder split run first); best or within 2 % of
         # the best on every such shape measured, from 512 x 11008 x 4096 to 4096 x 8192 x 8192
         return default_config(M, N, K, dtype, KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256,
                               BLOCK_SIZE_K=128, isATranspose=isATranspose)
