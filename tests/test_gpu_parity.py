@@ -443,13 +443,17 @@ def test_two_full_grids_with_shared_reductions_side_by_side():
         os.environ.pop("KCG_TAIL_SPLIT", None)
 
 
-def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(monkeypatch, tmp_path):
+@pytest.mark.parametrize("shape", [(512, 2816, 2048, 128), (1280, 4096, 1024, 64)],
+                         ids=["shares-of-rows-through-the-ring", "shares-of-blocks-from-l2"])
+def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(shape, monkeypatch, tmp_path):
     """A contributor that gives up waiting for the other partial tiles hands its share of the sum to the last
     arriver. Built with a waiting time of zero (KCG_SHARE_WAIT_NS=0, private cubin cache) every contributor that
     is not last gives up at once, so the hand-over runs on every split tile; the sum order does not change, so
-    the result must equal the normal build's bit for bit."""
-    M, N, K = 512, 2816, 2048
-    keys = dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128)
+    the result must equal the normal build's bit for bit. Two plans: no whole tiles follow (22 tiles on 74 pairs:
+    shares are rows, summed out of the idle operand ring) and whole tiles follow (80 tiles: shares are blocks,
+    summed straight from L2 under the next unit's main loop)."""
+    M, N, K, bk = shape
+    keys = dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=bk)
     monkeypatch.setenv("KCG_TAIL_SPLIT", "4")
     A, B = oracle.make_inputs(M, N, K, torch.bfloat16, "normal", seed=77)
     c, _, (a, b) = run_config(default_config(M, N, K, E.bfloat16, **keys), A, B)
