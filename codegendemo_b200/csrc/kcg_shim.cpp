@@ -1242,15 +1242,33 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
   cfg.blockDimZ = info->block[2];
   cfg.sharedMemBytes = info->smem_bytes;
   cfg.hStream = reinterpret_cast<CUstream>(stream);
-  CUlaunchAttribute attr[1];
+  CUlaunchAttribute attr[2];
   cfg.numAttrs = 0;
+  cfg.attrs = attr;
   if (info->cluster[0] * info->cluster[1] * info->cluster[2] > 1) {
-    attr[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-    attr[0].value.clusterDim.x = info->cluster[0];
-    attr[0].value.clusterDim.y = info->cluster[1];
-    attr[0].value.clusterDim.z = info->cluster[2];
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    attr[cfg.numAttrs].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    attr[cfg.numAttrs].value.clusterDim.x = info->cluster[0];
+    attr[cfg.numAttrs].value.clusterDim.y = info->cluster[1];
+    attr[cfg.numAttrs].value.clusterDim.z = info->cluster[2];
+    ++cfg.numAttrs;
+  }
+  // Programmatic dependent launch for the kernels that guard their global-memory accesses with
+  // griddepcontrol.wait (the single-pass tcgen05 kernels and cluster split-K): after another such
+  // launch in the same stream, the CTAs of this one are brought onto SMs as that kernel's CTAs leave,
+  // set themselves up and wait there for its completion, instead of being launched only then.
+  // KCG_PDL=0 turns it off.
+  {
+    static const bool pdl_on = [] {
+      const char* e = getenv("KCG_PDL");
+      return !(e && e[0] == '0');
+    }();
+    const bool single_pass = (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TCGEN05_PAIR) &&
+                             info->dtype != KCG_DTYPE_FLOAT32;
+    if (pdl_on && (single_pass || info->kernel == KCG_KERNEL_TF32X1 || info->kernel == KCG_KERNEL_TCGEN05_CLUSTERK)) {
+      attr[cfg.numAttrs].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+      attr[cfg.numAttrs].value.programmaticStreamSerializationAllowed = 1;
+      ++cfg.numAttrs;
+    }
   }
   DRV(cuLaunchKernelEx(&cfg, reinterpret_cast<CUfunction>(function), args, nullptr));
   g_launches.fetch_add(1);

@@ -275,6 +275,7 @@ struct TcGemm {
       }
     };
     if (threadIdx.x == 0) {
+      griddep_wait();  // the kernel before this one in the stream may have written A or B
       p_have = p_units.next(p_w);
       if constexpr (!kPair) produce(1u);
     }
@@ -297,7 +298,13 @@ struct TcGemm {
 
     if (warp == 0) {
       // ------------------------------------------------------------ producer
-      if (lane == 0) produce(0xffffffffu);
+      if (lane == 0) {
+        produce(0xffffffffu);
+        // Every load of this CTA is issued: the next kernel of the stream may be brought in as SMs
+        // fall free (not earlier: a kernel that took SMs while CTAs of this one still waited for
+        // theirs would keep waiting for this one in vain).
+        griddep_launch_dependents();
+      }
     } else if (warp == 1) {
       // -------------------------- MMA issuer (in a pair: the leader CTA only)
       if (lane == 0 && rank == 0u) {
@@ -424,6 +431,7 @@ struct TcGemm {
         }
       }
     } else if (warp >= 6) {
+      griddep_wait();
       // ------------------------------------- push warps (fused all-gather only)
       // They walk the same unit sequence; for every whole-K tile they wait until the four epilogue
       // warps have completed its stores, then copy this CTA's rows of the tile from this GPU's C
@@ -482,6 +490,7 @@ struct TcGemm {
       }
     } else {
       // ------------------------------------------------------------ epilogue
+      griddep_wait();  // C, the workspace and the counters may still be in use by the kernel before
       const int q = warp & 3;  // TMEM lane quarter this warp may read
       const int epi_tid = (warp - 2) * 32 + lane;
       uint32_t acc_it = 0;

@@ -209,6 +209,7 @@ struct TcGemmClusterK {
     if (warp == 0) {
       // ------------------------------------------------------------ producer
       if (lane == 0) {
+        griddep_wait();  // the kernel before this one in the stream may have written A or B
         for (int kb = 0; kb < kbn; ++kb) {
           const uint32_t s = kb % kStages;
           const uint32_t ph = (kb / kStages) & 1u;
@@ -237,6 +238,7 @@ struct TcGemmClusterK {
         }
       }
       __syncwarp();
+      if (lane == 0) griddep_launch_dependents();  // every load is issued: the stream's next kernel may be brought in
       cluster_wait();  // set-up phase of the cluster barrier: the other CTAs' barriers exist
       if (lane == 0) {
         ship(0);
@@ -288,6 +290,7 @@ struct TcGemmClusterK {
       cluster_arrive_relaxed();
     } else {
       // ------------------------------------------ epilogue: exchange, add, store
+      griddep_wait();  // C may still be in use by the kernel before this one in the stream
       const int q = warp & 3;  // TMEM lane quarter this warp may read
       const int epi_tid = (warp - 2) * 32 + lane;
       const int row = q * 32 + lane;  // row of the tile this thread holds in TMEM

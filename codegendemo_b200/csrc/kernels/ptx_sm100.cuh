@@ -136,6 +136,15 @@ __device__ __forceinline__ bool named_bar_all(uint32_t id, uint32_t nthreads, bo
   return out != 0;
 }
 
+// Programmatic dependent launch. A launch that carries the programmatic-stream-serialization
+// attribute may start while the kernel before it in the stream is still running: griddep_wait()
+// blocks until that kernel has completed and its memory operations are visible (and returns at once
+// in a launch without the attribute), so it must precede the first access to global memory;
+// griddep_launch_dependents() tells the scheduler that, as far as this CTA is concerned, the next
+// kernel of the stream may be brought onto the GPU.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
