@@ -468,6 +468,44 @@ def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(sh
         assert torch.equal(out, c)
 
 
+@pytest.mark.parametrize("shape", [
+    (256, 2048, dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=4)),
+    (2048, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64)),
+    (1024, 1024, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64, LOCAL_SPLIT_U=2)),
+], ids=["cluster-split-k", "cta-pairs", "single-cta-split-k"])
+def test_back_to_back_dependent_launches_see_each_others_results(shape):
+    """Launches of the single-pass and cluster split-K kernels carry the programmatic-dependent-launch attribute:
+    the next kernel of a stream is brought onto the GPU while the one before it drains, and waits
+    (griddepcontrol.wait) before it touches global memory. A chain X1 = A.B, X2 = X1.B, X3 = X2.B queued without any
+    synchronisation, repeated over the same buffers (each round overwrites what the round before still reads last),
+    must give the bits of the same chain run with a device synchronisation after every launch."""
+    M, K, keys = shape
+    A, B = oracle.make_inputs(M, K, K, torch.bfloat16, "normal", seed=5)
+    _, kern = build_kernel(default_config(M, K, K, E.bfloat16, **keys), 0)
+    a, b = A.cuda(), (B * (K ** 0.5) * 0.9).to(torch.bfloat16).cuda()   # keeps the chain's magnitude level
+    xs = [torch.zeros(M, K, dtype=torch.bfloat16, device="cuda:0") for _ in range(3)]
+
+    def chain(sync):
+        src = a
+        for x in xs:
+            kern.run(src, b, x)
+            if sync:
+                torch.cuda.synchronize()
+            src = x
+
+    chain(True)
+    kern.checkStatus()
+    want = [x.clone() for x in xs]
+    assert torch.isfinite(want[2].float()).all().item() and want[2].float().abs().max().item() > 0
+    for x in xs:
+        x.zero_()
+    for _ in range(20):
+        chain(False)
+    kern.checkStatus()
+    for x, w_ in zip(xs, want):
+        assert torch.equal(x, w_)
+
+
 def test_strided_operands_are_read_and_written_in_place():
     """kcg_launch_gemm_strided: A, B and C as column blocks of wider row-major arrays (leading dimension > row
     length); what lies outside the C block is left untouched."""
