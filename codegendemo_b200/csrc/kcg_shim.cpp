@@ -1253,7 +1253,7 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
     ++cfg.numAttrs;
   }
   // Programmatic dependent launch for the kernels that guard their global-memory accesses with
-  // griddepcontrol.wait (the single-pass tcgen05 kernels and cluster split-K): after another such
+  // griddepcontrol.wait (every tcgen05 kernel; not the SIMT comparison kernel): after another such
   // launch in the same stream, the CTAs of this one are brought onto SMs as that kernel's CTAs leave,
   // set themselves up and wait there for its completion, instead of being launched only then.
   // KCG_PDL=0 turns it off.
@@ -1262,9 +1262,9 @@ static int launch_impl(uint64_t function, const kcg_kernel_info* info, int devic
       const char* e = getenv("KCG_PDL");
       return !(e && e[0] == '0');
     }();
-    const bool single_pass = (info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TCGEN05_PAIR) &&
-                             info->dtype != KCG_DTYPE_FLOAT32;
-    if (pdl_on && (single_pass || info->kernel == KCG_KERNEL_TF32X1 || info->kernel == KCG_KERNEL_TCGEN05_CLUSTERK)) {
+    const bool guarded = info->kernel == KCG_KERNEL_TCGEN05 || info->kernel == KCG_KERNEL_TCGEN05_PAIR ||
+                         info->kernel == KCG_KERNEL_TF32X1 || info->kernel == KCG_KERNEL_TCGEN05_CLUSTERK;
+    if (pdl_on && guarded) {
       attr[cfg.numAttrs].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
       attr[cfg.numAttrs].value.programmaticStreamSerializationAllowed = 1;
       ++cfg.numAttrs;

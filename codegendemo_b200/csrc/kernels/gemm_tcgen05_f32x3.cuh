@@ -159,6 +159,7 @@ struct TcGemmF32x3 {
         // ---------------------------------------------------------- producer
         tma_prefetch_desc(&p.tmA);
         tma_prefetch_desc(&p.tmB);
+        griddep_wait();  // the kernel before this one in the stream may have written A or B
         uint32_t it = 0;
         bool ok = true;
         Iter units(p, unit0, unit_stride, tiles_m, tiles_n, num_kb);
@@ -193,6 +194,7 @@ struct TcGemmF32x3 {
             }
           }
         }
+        griddep_launch_dependents();  // every load is issued: the stream's next kernel may be brought in
       } else if (warp == 1 && lane == 0 && rank == 0u) {
         // ---------------------------- MMA issuer (in a pair: the leader CTA only)
         uint32_t it = 0, chunk_it = 0;
@@ -334,6 +336,7 @@ struct TcGemmF32x3 {
     } else {
       // --------------------------------------------------- accumulate + epilogue
       reg_inc<200>();
+      griddep_wait();  // C, the workspace and the counters may still be in use by the kernel before
       const int q = warp & 3;
       const int half = (warp - 8) >> 2;
       const int epi_tid = threadIdx.x - 256;

@@ -472,18 +472,22 @@ def test_abandoned_shares_of_a_split_reduction_are_summed_by_the_last_arriver(sh
     (256, 2048, dict(KERNEL_VARIANT=5, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128, LOCAL_SPLIT_U=4)),
     (2048, 2048, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64)),
     (1024, 1024, dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64, LOCAL_SPLIT_U=2)),
-], ids=["cluster-split-k", "cta-pairs", "single-cta-split-k"])
+    (512, 1024, dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=32, dtype=E.float32)),
+], ids=["cluster-split-k", "cta-pairs", "single-cta-split-k", "fp32-3xtf32-pairs"])
 def test_back_to_back_dependent_launches_see_each_others_results(shape):
-    """Launches of the single-pass and cluster split-K kernels carry the programmatic-dependent-launch attribute:
+    """Launches of the tcgen05 kernels carry the programmatic-dependent-launch attribute:
     the next kernel of a stream is brought onto the GPU while the one before it drains, and waits
     (griddepcontrol.wait) before it touches global memory. A chain X1 = A.B, X2 = X1.B, X3 = X2.B queued without any
     synchronisation, repeated over the same buffers (each round overwrites what the round before still reads last),
     must give the bits of the same chain run with a device synchronisation after every launch."""
     M, K, keys = shape
-    A, B = oracle.make_inputs(M, K, K, torch.bfloat16, "normal", seed=5)
-    _, kern = build_kernel(default_config(M, K, K, E.bfloat16, **keys), 0)
-    a, b = A.cuda(), (B * (K ** 0.5) * 0.9).to(torch.bfloat16).cuda()   # keeps the chain's magnitude level
-    xs = [torch.zeros(M, K, dtype=torch.bfloat16, device="cuda:0") for _ in range(3)]
+    keys = dict(keys)
+    dt = keys.pop("dtype", E.bfloat16)
+    tdt = ToTorchType(dt)
+    A, B = oracle.make_inputs(M, K, K, tdt, "normal", seed=5)
+    _, kern = build_kernel(default_config(M, K, K, dt, **keys), 0)
+    a, b = A.cuda(), (B * (K ** 0.5) * 0.9).to(tdt).cuda()   # keeps the chain's magnitude level
+    xs = [torch.zeros(M, K, dtype=tdt, device="cuda:0") for _ in range(3)]
 
     def chain(sync):
         src = a
