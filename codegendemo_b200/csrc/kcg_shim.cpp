@@ -785,6 +785,7 @@ SplitPlan plan_split(const kcg_kernel_info* info, bool fused_epilogue, int batch
         // on the timelines) must fit behind the main loops that are still to come.
         double best_gain = 0.0;
         for (int f = 2; f <= 8 && f <= num_kb; ++f) {
+          if (((num_kb + f - 1) / f) * (f - 1) >= num_kb) continue;  // the last range would be empty
           const int rounds = (rem * f + G - 1) / G;
           if (rounds > 1 && (!hidden || info->reserved[4] < 2)) break;  // needs a spare accumulator to run ahead
           double cost;

@@ -303,6 +303,63 @@ def test_work_decomposition_covers_every_k_block_once(case, tmp_path, monkeypatc
     assert r.returncode == 0 and r.stdout.startswith("OK"), r.stdout + r.stderr
 
 
+@pytest.mark.parametrize("tile", [
+    dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128),   # CTA pairs, two accumulator buffers
+    dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=4),  # one buffer, in halves
+    dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64),    # single CTAs, 148 at once
+], ids=["pair-256x256x128", "pair-512x256x64", "single-128x256x64"])
+def test_random_shapes_through_every_remainder_plan(tile, tmp_path, monkeypatch):
+    """Seeded random problem sizes (1 to ~6 waves of tiles, short and long K) through the launcher's planner in every
+    mode of KCG_TAIL_SPLIT - default, stream-K, even split and stream-K first without their gates - and the plan
+    through the kernels' iterator compiled for the host (tests/work_iter_check.cpp): whatever the planner picks,
+    every K block of every tile is covered once, split tiles come in order, `last` is the last, and the workspace
+    slots the launcher would allocate suffice."""
+    import ctypes
+    import random
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    lib = _lib.get_lib()
+    lib.kcg_internal_plan_split.argtypes = [ctypes.POINTER(_lib.KernelInfo), ctypes.c_int, ctypes.c_int,
+                                            ctypes.POINTER(ctypes.c_int)]
+    bm, bn, bk = tile["BLOCK_SIZE_M"], tile["BLOCK_SIZE_N"], tile["BLOCK_SIZE_K"]
+    exe = tmp_path / "work_iter_check"
+    kdir = os.path.join(ROOT, "codegendemo_b200", "csrc", "kernels")
+    subprocess.run(["g++", "-O1", "-std=c++17", "-I/usr/local/cuda/include", "-I" + kdir, f"-DWIC_BM={bm}",
+                    f"-DWIC_BN={bn}", f"-DWIC_BK={bk}", "-DWIC_GROUP=8", "-DKCG_SERPENTINE=0", "-o", str(exe),
+                    os.path.join(ROOT, "tests", "work_iter_check.cpp")], check=True)
+    rng = random.Random(bm * 7 + bn)
+    layers = set()
+    for _ in range(14):
+        M = bm * rng.randint(1, 12)
+        N = bn * rng.randint(1, 48)
+        K = bk * rng.choice([2, 5, 16, 32, 64, 86, 172])
+        for mode in (None, "1", "3", "4", "5"):
+            if mode is None:
+                monkeypatch.delenv("KCG_TAIL_SPLIT", raising=False)
+            else:
+                monkeypatch.setenv("KCG_TAIL_SPLIT", mode)
+            kpm = default_config(M, N, K, E.bfloat16, **tile)
+            info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT,
+                                serpentine=kpm.RASTER_SERPENTINE)
+            assert (info.bm, info.bn, info.bk, info.group) == (bm, bn, bk, 8)
+            out = (ctypes.c_int * 7)()
+            assert lib.kcg_internal_plan_split(ctypes.byref(info), 0, 1, out) == 0
+            tiles, first, factor, sk_per, ranges, at_once, units_first = list(out)
+            assert tiles == (M // bm) * (N // bn) and 0 <= first <= tiles and factor >= 1
+            if sk_per > 0:
+                grid, slots = (at_once if first > 0 else ranges), ranges + (tiles - first)
+                assert 0 < ranges <= at_once and first % at_once == 0
+            else:
+                grid, slots = min(first + (tiles - first) * factor, at_once), (tiles - first) * factor
+                if factor > 1:
+                    assert first % at_once == 0 or first == 0
+            layers.add("streamk" if sk_per > 0 else "even" if factor > 1 else "whole")
+            r = subprocess.run([str(exe), str(M), str(N), str(K), str(first), str(factor), str(sk_per), str(grid),
+                                str(slots), str(units_first)], capture_output=True, text=True)
+            assert r.returncode == 0 and r.stdout.startswith("OK"), (M, N, K, mode, list(out), r.stdout + r.stderr)
+    assert layers == {"whole", "even", "streamk"}, layers
+
+
 def test_symmetric_c_bookkeeping_with_a_fake_peer_library(monkeypatch):
     """SymmetricC's handle exchange, mapping order and close/free bookkeeping, on a stand-in for the four
     kcg_peer_* entries (no GPU): rank r's own buffer is never opened, every other rank's is opened once, the slab
