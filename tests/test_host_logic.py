@@ -360,6 +360,28 @@ def test_random_shapes_through_every_remainder_plan(tile, tmp_path, monkeypatch)
     assert layers == {"whole", "even", "streamk"}, layers
 
 
+def test_kernel_info_reports_the_accumulator_buffers_the_planner_relies_on():
+    """`kcg_kernel_info.reserved[4]` = accumulator buffers of a single-pass tcgen05 kernel in tensor memory: two when
+    REG_PREFETCH is on and two copies of a CTA's accumulator fit the 512 columns, else one. The launcher cuts a
+    remainder into several rounds of split units only for kernels with two (the MMAs of the next unit must not wait
+    for the epilogue warps); the value also survives the dict form the compile workers hand back."""
+    from codegendemo_b200 import _lib
+    from codegendemo_b200.kcg.KCGCompiler import compile_info
+    cases = [
+        (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128), 2),   # 128 rows x 256 columns per CTA
+        (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=512, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=4), 1),  # 2 x 256 columns
+        (dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64), 2),
+        (dict(KERNEL_VARIANT=2, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, NUM_STAGES=3), 1),
+        (dict(KERNEL_VARIANT=4, BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, REG_PREFETCH=0), 1),
+    ]
+    for keys, want in cases:
+        kpm = default_config(2048, 4096, 4096, E.bfloat16, **keys)
+        info = compile_info(kpm.compileArgs(), num_stages=kpm.NUM_STAGES, kernel=kpm.KERNEL_VARIANT,
+                            serpentine=kpm.RASTER_SERPENTINE)
+        assert info.reserved[4] == want, (keys, info.reserved[4])
+        assert _lib.KernelInfo.from_dict(info.to_dict()).reserved[4] == want
+
+
 def test_symmetric_c_bookkeeping_with_a_fake_peer_library(monkeypatch):
     """SymmetricC's handle exchange, mapping order and close/free bookkeeping, on a stand-in for the four
     kcg_peer_* entries (no GPU): rank r's own buffer is never opened, every other rank's is opened once, the slab
