@@ -632,11 +632,12 @@ def main():
     peak_kind = "bf16_tflops_sustained" if timed_s > 0.1 else "bf16_tflops"
     peak = peaks[peak_kind]
     # DRAM traffic of one launch (dram__bytes_read.sum + dram__bytes_write.sum, one-pass ncu captures, see
-    # profiles/): 5.76 GB for the full 32768-row launch of the 512x256 pair tile; 275.0 MB for a 2048-row launch
+    # profiles/): 512x256 pair tile 5.76 GB for the full 32768-row launch and 1.95 GB for a 16384-row launch (the
+    # re-reads grow faster than the rows: more raster groups stream B through L2); 275.0 MB for a 2048-row launch
     # of the 256x256x128 pair tile (the tile of the 4096-row slabs); 227.4 MB for a 2048-row launch of the
-    # single-CTA kernel. Other slab heights are scaled by their rows (the traffic grows in proportion).
+    # single-CTA kernel. Other slab heights are scaled by their rows from the nearest measured one.
     if inc.kernelInfo["kernel"] == 4 and kpm.BLOCK_SIZE_M == 512:
-        traffic = 5.76e9 * rows / 32768.0
+        traffic = 5.76e9 * rows / 32768.0 if rows > 16384 else 1.95e9 * rows / 16384.0
     elif inc.kernelInfo["kernel"] == 4:
         traffic = 275.0e6 * rows / 2048.0
     else:
